@@ -1,0 +1,158 @@
+"""Compiles the CUDA sources of this folder for sm_100a into shared libraries.
+
+The libraries export plain C entry points (no Python or torch headers), so a
+file compiles in seconds and the result is loaded with ``ctypes``.  A library
+is rebuilt when the hash of its sources and flags changes; it is written next
+to the package (``chibillm_b200/_lib``) or, when that folder cannot be written,
+under the system's temporary folder.  The compile runs at the first call that
+needs the library and prints a line per file while it works.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Dict, List, Optional, Sequence
+
+CSRC = os.path.dirname(os.path.abspath(__file__))
+PACKAGE = os.path.dirname(CSRC)
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
+                "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-cudart", "static"]
+
+# name of library -> sources (relative to this folder)
+LIBRARIES: Dict[str, List[str]] = {
+    "chibi_kernels": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling.cu"],
+}
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _say(msg: str) -> None:
+    print(f"[chibillm_b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("CHIBILLM_NVCC"), shutil.which("nvcc"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                 "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("nvcc was not found (looked at CHIBILLM_NVCC, PATH, CUDA_HOME, /usr/local/cuda); "
+                     "the CUDA kernels of chibillm_b200 cannot be compiled")
+
+
+def _writable_dir(path: str) -> bool:
+    try:
+        os.makedirs(path, exist_ok=True)
+        probe = tempfile.NamedTemporaryFile(dir=path, delete=True)
+        probe.close()
+        return True
+    except OSError:
+        return False
+
+
+def library_dir() -> str:
+    override = os.environ.get("CHIBILLM_LIB_DIR")
+    if override:
+        os.makedirs(override, exist_ok=True)
+        return override
+    in_tree = os.path.join(PACKAGE, "_lib")
+    if _writable_dir(in_tree):
+        return in_tree
+    fallback = os.path.join(tempfile.gettempdir(), f"chibillm_b200-lib-{os.getuid()}")
+    if _writable_dir(fallback):
+        return fallback
+    raise BuildError(f"neither {in_tree} nor {fallback} can be written")
+
+
+def _headers() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+
+
+def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
+    h = hashlib.sha256()
+    for name in list(sources) + _headers():
+        h.update(name.encode())
+        with open(os.path.join(CSRC, name), "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()[:12]
+
+
+def library_path(name: str, defines: Sequence[str] = ()) -> str:
+    sources = LIBRARIES[name]
+    flags = ARCH_FLAGS + COMMON_FLAGS + [f"-D{d}" for d in defines]
+    tag = _digest(sources, flags)
+    suffix = ("_" + "_".join(d.replace("=", "") for d in defines)) if defines else ""
+    return os.path.join(library_dir(), f"lib{name}{suffix}_{tag}.so")
+
+
+def _run(cmd: List[str]) -> None:
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"command failed ({proc.returncode}): {' '.join(cmd)}\n{proc.stdout}")
+
+
+def ensure_library(name: str, defines: Sequence[str] = (), verbose: bool = True) -> str:
+    """Build library ``name`` if its current version is not there; return its path."""
+    target = library_path(name, defines)
+    if os.path.isfile(target):
+        return target
+    nvcc = find_nvcc()
+    sources = LIBRARIES[name]
+    flags = ARCH_FLAGS + COMMON_FLAGS + [f"-D{d}" for d in defines]
+    out_dir = os.path.dirname(target)
+    work = tempfile.mkdtemp(prefix=f"build-{name}-", dir=out_dir)
+    started = time.time()
+    try:
+        if verbose:
+            _say(f"compiling {name} ({len(sources)} files) for sm_100a with {nvcc}")
+
+        def compile_one(src: str) -> str:
+            obj = os.path.join(work, os.path.splitext(src)[0] + ".o")
+            t0 = time.time()
+            _run([nvcc] + flags + ["-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj])
+            if verbose:
+                _say(f"  {src} done in {time.time() - t0:.1f} s")
+            return obj
+
+        with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+            objects = list(pool.map(compile_one, sources))
+        tmp_so = os.path.join(work, "out.so")
+        _run([nvcc] + ARCH_FLAGS + ["-shared", "-cudart", "static", "-Xcompiler", "-fPIC",
+                                    "-o", tmp_so] + objects)
+        os.replace(tmp_so, target)
+        if verbose:
+            _say(f"{os.path.basename(target)} ready in {time.time() - started:.1f} s")
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    # older versions of the same library are of no use any more
+    prefix = f"lib{name}" + (("_" + "_".join(d.replace("=", "") for d in defines)) if defines else "") + "_"
+    for f in os.listdir(out_dir):
+        full = os.path.join(out_dir, f)
+        if f.startswith(prefix) and f.endswith(".so") and full != target:
+            rest = f[len(prefix):-3]
+            if len(rest) == 12 and all(c in "0123456789abcdef" for c in rest):
+                try:
+                    os.remove(full)
+                except OSError:
+                    pass
+    return target
+
+
+def build_all(verbose: bool = True) -> List[str]:
+    return [ensure_library(name, verbose=verbose) for name in LIBRARIES]
+
+
+if __name__ == "__main__":
+    for p in build_all():
+        print(p)

@@ -1,0 +1,310 @@
+// Row-wise kernels: embedding gather, RMSNorm, the fused per-head norm +
+// rotation + cache append, SwiGLU, row gather, casts.  All statistics, angles
+// and activations are computed in 32-bit; element types of inputs, weights and
+// outputs are template parameters so the same code serves the bfloat16 and the
+// 32-bit engine.
+#include "common.cuh"
+
+namespace chibi {
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = float(table[token[t], :]).  Ids outside the table leave zeros and
+// raise the error word (the host checks ids before the launch; this guard only
+// keeps a bad id from reading outside the table).
+template <typename TW, typename TO>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             TO* __restrict__ out, int hidden, int vocab, int* __restrict__ error)
+{
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0 && error)
+        atomicExch(error, 1);
+    const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+    TO* dst = out + (size_t)t * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+        dst[j] = from_f32<TO>(ok ? to_f32(row[j]) : 0.f);
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per group of n features: inv = rsqrt(sum(x^2)/n + eps);
+// y = (x * inv) * (w + offset).
+template <typename TX, typename TW, typename TO>
+__global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
+                               TO* __restrict__ out, int n, long long x_stride,
+                               long long out_stride, float eps, float offset)
+{
+    __shared__ float scratch[33];
+    const TX* row = x + (size_t)blockIdx.x * x_stride;
+    TO* dst = out + (size_t)blockIdx.x * out_stride;
+    float s = 0.f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const float v = to_f32(row[j]);
+        s = fmaf(v, v, s);
+    }
+    s = block_sum(s, scratch);
+    const float inv = rsqrtf(s / (float)n + eps);
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const float v = to_f32(row[j]);
+        dst[j] = from_f32<TO>((v * inv) * (to_f32(w[j]) + offset));
+    }
+}
+
+// ------------------------------------------- per-head norm + rotation + append
+// One block per token, one warp per head job.  Jobs 0..nq-1 are query heads,
+// nq..nq+nkv-1 key heads, the rest value heads.  Query and key heads are
+// normalised over their d features (when a norm weight is given), rotated
+// (split-half pairs (j, j + rot/2), angle = float(pos) * inv_freq[j]) and
+// written to q_out or to the key cache; value heads are copied to the value
+// cache.  Cache layout: [page][kv_head][slot][d]; page = block_table[seq][pos /
+// page_size], slot = pos % page_size.
+template <typename TX, typename TW, typename TC>
+__global__ void qk_norm_rope_append_kernel(
+    const TX* __restrict__ qkv, long long qkv_stride, TX* __restrict__ q_out,
+    TC* __restrict__ k_cache, TC* __restrict__ v_cache, const TW* __restrict__ q_norm_w,
+    const TW* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int table_stride, int nq, int nkv, int d, int rot,
+    int page_size, int num_pages, float eps, float norm_offset, int append,
+    int* __restrict__ error)
+{
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    float* buf = smem + (size_t)warp * d;
+    const int pos = positions[t];
+    const int jobs = append ? nq + 2 * nkv : nq;
+    const TX* row = qkv + (size_t)t * qkv_stride;
+
+    long long cache_base = -1;
+    if (append) {
+        const int seq = seq_of_token[t];
+        const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && error)
+                atomicExch(error, 2);
+        } else {
+            cache_base = ((long long)page * nkv * page_size + (pos % page_size)) * d;
+        }
+    }
+
+    for (int job = warp; job < jobs; job += warps) {
+        const bool is_q = job < nq;
+        const bool is_k = !is_q && job < nq + nkv;
+        const int head = is_q ? job : (is_k ? job - nq : job - nq - nkv);
+        const TX* src = row + (size_t)job * d; // q | k | v are consecutive columns
+        if (!is_q && !is_k) {
+            if (cache_base >= 0) {
+                TC* dst = v_cache + cache_base + (long long)head * page_size * d;
+                for (int j = lane; j < d; j += 32)
+                    dst[j] = from_f32<TC>(to_f32(src[j]));
+            }
+            continue;
+        }
+        const TW* w = is_q ? q_norm_w : k_norm_w;
+        float s = 0.f;
+        for (int j = lane; j < d; j += 32) {
+            const float v = to_f32(src[j]);
+            buf[j] = v;
+            s = fmaf(v, v, s);
+        }
+        s = warp_sum(s);
+        __syncwarp();
+        if (w) {
+            const float inv = rsqrtf(s / (float)d + eps);
+            for (int j = lane; j < d; j += 32)
+                buf[j] = (buf[j] * inv) * (to_f32(w[j]) + norm_offset);
+            __syncwarp();
+        }
+        const int half = rot >> 1;
+        // Every lane reads its pair before any lane writes.
+        float lo[4], hi[4]; // d <= 256 -> at most 4 pairs per lane
+        int cnt = 0;
+        for (int j = lane; j < half; j += 32, ++cnt) {
+            const float a = (float)pos * inv_freq[j];
+            const float c = cosf(a), sn = sinf(a);
+            const float x0 = buf[j], x1 = buf[j + half];
+            lo[cnt] = x0 * c - x1 * sn;
+            hi[cnt] = x1 * c + x0 * sn;
+        }
+        __syncwarp();
+        cnt = 0;
+        for (int j = lane; j < half; j += 32, ++cnt) {
+            buf[j] = lo[cnt];
+            buf[j + half] = hi[cnt];
+        }
+        __syncwarp();
+        if (is_q) {
+            TX* dst = q_out + ((size_t)t * nq + head) * d;
+            for (int j = lane; j < d; j += 32)
+                dst[j] = from_f32<TX>(buf[j]);
+        } else if (cache_base >= 0) {
+            TC* dst = k_cache + cache_base + (long long)head * page_size * d;
+            for (int j = lane; j < d; j += 32)
+                dst[j] = from_f32<TC>(buf[j]);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gate_up[t, 0:I] = gate, gate_up[t, I:2I] = up; out = gate / (1 + exp(-gate)) * up.
+template <typename TX, typename TO>
+__global__ void swiglu_kernel(const TX* __restrict__ gate_up, TO* __restrict__ out, long long rows,
+                              int inter)
+{
+    const long long total = rows * inter;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / inter;
+        const int c = (int)(i - r * inter);
+        const float g = to_f32(gate_up[r * 2 * inter + c]);
+        const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
+        out[i] = from_f32<TO>((g / (1.f + expf(-g))) * u);
+    }
+}
+
+// ---------------------------------------------------------------- row gather
+template <typename TX, typename TO>
+__global__ void gather_rows_kernel(const TX* __restrict__ x, const int* __restrict__ rows,
+                                   TO* __restrict__ out, int n, long long x_rows)
+{
+    const int r = rows[blockIdx.x];
+    const bool ok = r >= 0 && r < x_rows;
+    for (int j = threadIdx.x; j < n; j += blockDim.x)
+        out[(size_t)blockIdx.x * n + j] = from_f32<TO>(ok ? to_f32(x[(size_t)r * n + j]) : 0.f);
+}
+
+// ---------------------------------------------------------------- cast / add
+template <typename TX, typename TO>
+__global__ void cast_kernel(const TX* __restrict__ x, TO* __restrict__ out, long long total)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32(x[i]));
+}
+
+// acc (32-bit) += x
+template <typename TX>
+__global__ void add_into_kernel(float* __restrict__ acc, const TX* __restrict__ x, long long total)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        acc[i] += to_f32(x[i]);
+}
+
+static int grid_for(long long total, int block)
+{
+    long long g = (total + block - 1) / block;
+    if (g > 148LL * 32)
+        g = 148LL * 32;
+    if (g < 1)
+        g = 1;
+    return (int)g;
+}
+
+} // namespace chibi
+
+using namespace chibi;
+
+CHIBI_API int chibi_embed(const int* tokens, const void* table, int table_type, void* out,
+                          int out_type, long long rows, int hidden, int vocab, int* error,
+                          cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    const int block = hidden >= 1024 ? 256 : 128;
+    CHIBI_DISPATCH_TYPE(table_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        embed_kernel<TW, TO><<<(unsigned)rows, block, 0, stream>>>(
+            tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_rmsnorm(const void* x, int x_type, const void* w, int w_type, void* out,
+                            int out_type, long long groups, int n, long long x_stride,
+                            long long out_stride, float eps, float offset, cudaStream_t stream)
+{
+    if (groups <= 0)
+        return CHIBI_OK;
+    int block = 32;
+    while (block < n && block < 512)
+        block <<= 1;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        rmsnorm_kernel<TX, TW, TO><<<(unsigned)groups, block, 0, stream>>>(
+            (const TX*)x, (const TW*)w, (TO*)out, n, x_stride, out_stride, eps, offset);
+    })));
+    return launch_status();
+}
+
+CHIBI_API int chibi_qk_norm_rope_append(
+    const void* qkv, int x_type, long long qkv_stride, void* q_out, void* k_cache, void* v_cache,
+    int cache_type, const void* q_norm_w, const void* k_norm_w, int w_type, const float* inv_freq,
+    const int* positions, const int* seq_of_token, const int* block_table, int table_stride,
+    long long tokens, int nq, int nkv, int d, int rot, int page_size, int num_pages, float eps,
+    float norm_offset, int append, int* error, cudaStream_t stream)
+{
+    if (tokens <= 0)
+        return CHIBI_OK;
+    if (d <= 0 || d > 256 || rot < 0 || rot > d || (rot & 1))
+        return CHIBI_ERR_UNSUPPORTED;
+    const int jobs = append ? nq + 2 * nkv : nq;
+    int warps = jobs < 8 ? jobs : 8;
+    const size_t smem = (size_t)warps * d * sizeof(float);
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
+        qk_norm_rope_append_kernel<TX, TW, TC><<<(unsigned)tokens, warps * 32, smem, stream>>>(
+            (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
+            (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token,
+            block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
+            append, error);
+    })));
+    return launch_status();
+}
+
+CHIBI_API int chibi_swiglu(const void* gate_up, int x_type, void* out, int out_type,
+                           long long rows, int inter, cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        swiglu_kernel<TX, TO><<<grid_for(rows * inter, 256), 256, 0, stream>>>(
+            (const TX*)gate_up, (TO*)out, rows, inter);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_gather_rows(const void* x, int x_type, const int* rows, void* out,
+                                int out_type, long long count, int n, long long x_rows,
+                                cudaStream_t stream)
+{
+    if (count <= 0)
+        return CHIBI_OK;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        gather_rows_kernel<TX, TO><<<(unsigned)count, 256, 0, stream>>>(
+            (const TX*)x, rows, (TO*)out, n, x_rows);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_cast(const void* x, int x_type, void* out, int out_type, long long total,
+                         cudaStream_t stream)
+{
+    if (total <= 0)
+        return CHIBI_OK;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        cast_kernel<TX, TO><<<grid_for(total, 256), 256, 0, stream>>>((const TX*)x, (TO*)out, total);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_add_into(float* acc, const void* x, int x_type, long long total,
+                             cudaStream_t stream)
+{
+    if (total <= 0)
+        return CHIBI_OK;
+    CHIBI_DISPATCH_TYPE(x_type, TX, {
+        add_into_kernel<TX><<<grid_for(total, 256), 256, 0, stream>>>(acc, (const TX*)x, total);
+    });
+    return launch_status();
+}

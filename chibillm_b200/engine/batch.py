@@ -1,0 +1,128 @@
+"""A step's batch: what is fed, flattened into the arrays the kernels read.
+
+The reference flattens scheduled items into ``tokens``, ``positions`` and
+per-row table offsets (src/model_batch.cc:34-125, 127-204) and runs prompt
+chunks and decode tokens in separate batches.  Here one batch holds any mix:
+every entry is (request, its next tokens, the places whose logits are wanted);
+a decode token is an entry of one token.  Metadata is per sequence
+(``q_start``, ``ctx_len``, one block-table row per group) plus per token
+(``positions``, ``seq_of_token``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places (indices into ``tokens``)
+    whose logits are wanted."""
+
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class BatchError(ValueError):
+    pass
+
+
+class Workspace:
+    """Named scratch arrays that live across steps, so a step of a size seen
+    before allocates nothing."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = (name, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < count:
+            grow = max(count, 1)
+            if buf is not None:
+                grow = max(grow, 2 * buf.numel()) if count < (1 << 28) else count
+            buf = torch.empty(grow, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:count].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the running batch."""
+
+    num_tokens: int
+    num_seqs: int
+    tokens: torch.Tensor                 # int32 [T]
+    positions: torch.Tensor              # int32 [T]
+    seq_of_token: torch.Tensor           # int32 [T]
+    q_start: torch.Tensor                # int32 [S + 1]
+    ctx_len: torch.Tensor                # int32 [S]  (tokens held after this step)
+    state_slots: torch.Tensor            # int32 [S]
+    logit_rows: torch.Tensor             # int32 [R]
+    tables: Dict[str, torch.Tensor]      # group -> int32 [S, blocks]
+    workspace: Workspace
+    # host copies, for sizing launches and for mixers that walk sequences
+    request_ids: List[Hashable] = field(default_factory=list)
+    q_lens: List[int] = field(default_factory=list)
+    ctx_lens: List[int] = field(default_factory=list)
+    slot_list: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_ctx_len: int = 0
+
+    @property
+    def decode_only(self) -> bool:
+        return self.max_q_len == 1
+
+
+def flatten_entries(entries: Sequence[StepEntry], lengths: Dict[Hashable, int], vocab_size: int,
+                    max_positions: int):
+    """Host-side flattening and checks (the checks of src/model_batch.cc:52-85,
+    148-203 that apply here): no request twice, at least one token each, ids
+    inside the vocabulary, positions below the model's limit, wanted places
+    inside the entry."""
+    seen = set()
+    tokens: List[int] = []
+    positions: List[int] = []
+    seq_of_token: List[int] = []
+    q_start = [0]
+    ctx_lens: List[int] = []
+    q_lens: List[int] = []
+    logit_rows: List[int] = []
+    for s, e in enumerate(entries):
+        if e.request_id in seen:
+            raise BatchError(f"request {e.request_id!r} appears twice in one step")
+        seen.add(e.request_id)
+        n = len(e.tokens)
+        if n == 0:
+            raise BatchError(f"request {e.request_id!r} brings no tokens")
+        start = lengths[e.request_id]
+        if start + n > max_positions:
+            raise BatchError(f"request {e.request_id!r} would reach position {start + n - 1}; "
+                             f"the model's limit is {max_positions - 1}")
+        for i, tok in enumerate(e.tokens):
+            tok = int(tok)
+            if not (0 <= tok < vocab_size):
+                raise BatchError(f"request {e.request_id!r}: token id {tok} is outside the vocabulary "
+                                 f"of {vocab_size}")
+            tokens.append(tok)
+            positions.append(start + i)
+            seq_of_token.append(s)
+        for w in e.want:
+            w = int(w)
+            if not (0 <= w < n):
+                raise BatchError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
+            logit_rows.append(q_start[-1] + w)
+        q_start.append(q_start[-1] + n)
+        q_lens.append(n)
+        ctx_lens.append(start + n)
+    return tokens, positions, seq_of_token, q_start, q_lens, ctx_lens, logit_rows

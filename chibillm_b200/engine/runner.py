@@ -1,0 +1,191 @@
+"""The step function: runs a batch of (request, its next tokens) from the cache
+and returns the logits at the wanted places.
+
+The reference's counterpart is ``qwen_model_runner::execute``
+(src/qwen/qwen_model_runner.cc:198-239): metadata, embedding, layers, output on
+the sampled rows, one wait.  Differences: a batch may mix portions of prompts
+with single decoded tokens, any place of an entry may be wanted, and the
+logits themselves are returned (the reference returns only the arg max).
+
+A step runs only the tokens it is given.  Everything earlier comes from the
+pages that former steps wrote.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheError, CacheManager
+from ..cache.storage import CacheStorage, plan_cache
+from ..config.registry import load_config
+from ..parts.base import Runtime
+from ..weights.loader import load_weights
+from .batch import BatchError, StepContext, StepEntry, Workspace, flatten_entries
+from .model import DecoderModel
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {name} is not supported (bfloat16 or float32)")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype '{name}' is not supported (bfloat16 or float32)") from None
+
+
+def make_runtime(dtype, device="cuda:0", kernels=None) -> Runtime:
+    """The product's runtime: a CUDA device and this package's kernels.  A test
+    may pass a stand-in for the kernels (then any device is allowed)."""
+    device = torch.device(device)
+    if kernels is None:
+        from ..kernels.ops import CudaKernels
+        kernels = CudaKernels(device)
+    return Runtime(device=device, dtype=parse_dtype(dtype), kernels=kernels)
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, runtime: Runtime, page_size: int, pool_tokens: int,
+                 max_requests: int):
+        self.model = model
+        self.spec = model.spec
+        self.runtime = runtime
+        self.page_size = page_size
+        plan = plan_cache(model.cache_needs(), model.cache_sources(), page_size, pool_tokens)
+        self.plan = plan
+        self.cache = CacheManager(plan.groups, max_requests)
+        self.storage = CacheStorage(plan, runtime, max_requests)
+        self.workspace = Workspace(runtime.device)
+        self._meta_host: Optional[torch.Tensor] = None
+        self._meta_dev: Optional[torch.Tensor] = None
+        self.steps_run = 0
+
+    # ------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                    pool_tokens: int = 4096, max_requests: int = 4, kernels=None) -> "ModelRunner":
+        _, _, spec = load_config(model_dir)
+        runtime = make_runtime(dtype, device, kernels)
+        model = DecoderModel(spec, runtime)
+        load_weights(model, model_dir, runtime)
+        return cls(model, runtime, page_size, pool_tokens, max_requests)
+
+    @property
+    def max_context_tokens(self) -> int:
+        """min(model's positions, what the smallest pool holds)
+        (src/qwen/qwen_model_runner.cc:128-134)."""
+        pool = min((g.num_pages * g.page_size for g in self.plan.groups), default=self.spec.max_positions)
+        return min(self.spec.max_positions, pool)
+
+    # ------------------------------------------------------------ requests
+    def admit(self, request_id: Hashable) -> None:
+        rc = self.cache.admit(request_id)
+        self.storage.zero_state_slot(rc.state_slot)
+
+    def end(self, request_id: Hashable) -> None:
+        self.cache.release(request_id)
+
+    def has(self, request_id: Hashable) -> bool:
+        return self.cache.has(request_id)
+
+    def length(self, request_id: Hashable) -> int:
+        return self.cache.length(request_id)
+
+    # ------------------------------------------------------------ metadata
+    def _meta_buffers(self, count: int):
+        if self._meta_host is None or self._meta_host.numel() < count:
+            cap = max(4096, 2 * count)
+            pin = self.runtime.device.type == "cuda"
+            self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.runtime.device)
+        return self._meta_host, self._meta_dev
+
+    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        lengths = {e.request_id: self.cache.length(e.request_id) for e in entries}
+        (tokens, positions, seq_of_token, q_start, q_lens, ctx_lens, logit_rows) = flatten_entries(
+            entries, lengths, self.spec.vocab_size, self.spec.max_positions)
+        T, S, R = len(tokens), len(entries), len(logit_rows)
+        slots = [self.cache.get(e.request_id).state_slot for e in entries]
+        group_tables: Dict[str, List[List[int]]] = {}
+        widths: Dict[str, int] = {}
+        for g in self.plan.groups:
+            rows = [self.cache.get(e.request_id).tables[g.name] for e in entries]
+            widths[g.name] = max(1, max(len(r) for r in rows))
+            group_tables[g.name] = rows
+        # layout of the packed array, every segment on a 16-byte boundary
+        segments = [("tokens", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1),
+                    ("ctx_len", S), ("state_slots", S), ("logit_rows", R)]
+        segments += [("table:" + name, S * w) for name, w in widths.items()]
+        offsets, cursor = {}, 0
+        for name, n in segments:
+            offsets[name] = cursor
+            cursor += _align4(max(n, 1))
+        host, dev = self._meta_buffers(cursor)
+        flat = [0] * cursor
+
+        def put(name, values):
+            o = offsets[name]
+            flat[o:o + len(values)] = values
+
+        put("tokens", tokens)
+        put("positions", positions)
+        put("seq_of_token", seq_of_token)
+        put("q_start", q_start)
+        put("ctx_len", ctx_lens)
+        put("state_slots", slots)
+        put("logit_rows", logit_rows)
+        for name, rows in group_tables.items():
+            w = widths[name]
+            o = offsets["table:" + name]
+            for s, row in enumerate(rows):
+                flat[o + s * w:o + s * w + len(row)] = row
+                for j in range(len(row), w):
+                    flat[o + s * w + j] = -1
+        host[:cursor] = torch.tensor(flat, dtype=torch.int32)
+        dev[:cursor].copy_(host[:cursor], non_blocking=True)
+
+        def view(name, n):
+            o = offsets[name]
+            return dev[o:o + n]
+
+        tables = {name: view("table:" + name, S * w).view(S, w) for name, w in widths.items()}
+        return StepContext(
+            num_tokens=T, num_seqs=S, tokens=view("tokens", T), positions=view("positions", T),
+            seq_of_token=view("seq_of_token", T), q_start=view("q_start", S + 1),
+            ctx_len=view("ctx_len", S), state_slots=view("state_slots", S),
+            logit_rows=view("logit_rows", R), tables=tables, workspace=self.workspace,
+            request_ids=[e.request_id for e in entries], q_lens=q_lens, ctx_lens=ctx_lens,
+            slot_list=slots, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+
+    # ------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits [wanted, vocab] on the device in
+        the order of the entries and of their ``want`` (None if nothing is
+        wanted).  The array is reused by the next step."""
+        if not entries:
+            raise BatchError("a step needs at least one entry")
+        if len(entries) > self.cache.max_requests:
+            raise BatchError(f"{len(entries)} entries in one step; at most {self.cache.max_requests} "
+                             f"requests are live at a time")
+        for e in entries:
+            if not self.cache.has(e.request_id):
+                self.admit(e.request_id)
+        for e in entries:
+            self.cache.reserve(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
+        ctx = self._build_context(entries)
+        logits = self.model.forward(ctx, self.storage.views)
+        for e, new_len in zip(entries, ctx.ctx_lens):
+            self.cache.commit(e.request_id, new_len)
+        self.steps_run += 1
+        if check and hasattr(self.runtime.kernels, "check_error_word"):
+            self.runtime.kernels.check_error_word()
+        return logits

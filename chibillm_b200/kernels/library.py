@@ -1,0 +1,60 @@
+"""Loads the compiled CUDA libraries and declares their C entry points."""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Dict, Sequence
+
+from ..csrc import build
+
+_lock = threading.Lock()
+_loaded: Dict[str, ctypes.CDLL] = {}
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+# entry point -> argument types (all return int: 0 ok, >0 a CUDA error, <0 ours)
+_SIGNATURES = {
+    "chibi_kernels": {
+        "chibi_embed": [P, P, I, P, I, L, I, I, P, P],
+        "chibi_rmsnorm": [P, I, P, I, P, I, L, I, L, L, F, F, P],
+        "chibi_qk_norm_rope_append": [P, I, L, P, P, P, I, P, P, I, P, P, P, P, I, L, I, I, I, I, I,
+                                      I, F, F, I, P, P],
+        "chibi_swiglu": [P, I, P, I, L, I, P],
+        "chibi_gather_rows": [P, I, P, P, I, L, I, L, P],
+        "chibi_cast": [P, I, P, I, L, P],
+        "chibi_add_into": [P, P, I, L, P],
+        "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
+        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
+        "chibi_sample": [P, L, L, I, P, P, P, P],
+    },
+}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def load(name: str, defines: Sequence[str] = ()) -> ctypes.CDLL:
+    """Return the library, compiling it first if its current version is absent."""
+    key = name + "".join(defines)
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is not None:
+            return lib
+        try:
+            path = build.ensure_library(name, defines)
+        except build.BuildError as e:
+            raise KernelLibraryError(
+                f"the CUDA library '{name}' of chibillm_b200 could not be built; there is no other "
+                f"path to run the model on.\n{e}") from None
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelLibraryError(f"cannot load {path}: {e}") from None
+        for fn, argtypes in _SIGNATURES.get(name, {}).items():
+            f = getattr(lib, fn)
+            f.argtypes = argtypes
+            f.restype = c_int
+        _loaded[key] = lib
+        return lib

@@ -1,0 +1,244 @@
+"""The operations the parts are made of, each a launch of a CUDA kernel of this
+package.  There is no other implementation behind these calls: a tensor that
+is not on a CUDA device, or a library that cannot be built or loaded, raises.
+
+All functions write into tensors the caller provides (so a step allocates
+nothing once its workspace exists) and launch on torch's current stream.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("chibillm_b200 runs on a CUDA device only; got a tensor on "
+                              f"'{t.device}' (there is no CPU path)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{what}: invalid argument")
+    if status == -2:
+        raise KernelError(f"{what}: sizes outside what the kernel supports")
+    raise KernelError(f"{what}: CUDA error {status}")
+
+
+def _rows_contiguous(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what} must be 2-d with contiguous rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+
+
+class CudaKernels:
+    """The one set of operations of the product path."""
+
+    name = "cuda"
+
+    def __init__(self, device: torch.device):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is available; chibillm_b200 has no CPU path")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError(f"device '{device}' is not a CUDA device; chibillm_b200 has no CPU path")
+        self.lib = library.load("chibi_kernels")
+        self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ helpers
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_error_word(self) -> None:
+        """Synchronises and raises if a kernel met an index outside its tables."""
+        code = int(self.error.item())
+        if code:
+            self.error.zero_()
+            what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",
+                    3: "a page id outside the pool (attention)"}.get(code, f"code {code}")
+            raise KernelError(f"a kernel refused {what}")
+
+    # ------------------------------------------------------------------ ops
+    def embed(self, tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+        _need_cuda(tokens, table, out)
+        if tokens.dtype != torch.int32 or not tokens.is_contiguous():
+            raise KernelError("embed: tokens must be contiguous int32")
+        _rows_contiguous(table, "embed: table")
+        if not out.is_contiguous() or out.shape != (tokens.numel(), table.shape[1]):
+            raise KernelError("embed: out must be contiguous [tokens, hidden]")
+        if not table.is_contiguous():
+            raise KernelError("embed: table must be contiguous")
+        _check(self.lib.chibi_embed(_ptr(tokens), _ptr(table), _code(table), _ptr(out), _code(out),
+                                    tokens.numel(), table.shape[1], table.shape[0],
+                                    _ptr(self.error), self._stream()), "embed")
+
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float,
+                out: torch.Tensor) -> None:
+        """x, out: [groups, n] (rows may be strided); weight [n]."""
+        _need_cuda(x, weight, out)
+        _rows_contiguous(x, "rmsnorm: x")
+        _rows_contiguous(out, "rmsnorm: out")
+        n = x.shape[1]
+        if weight.shape != (n,) or not weight.is_contiguous() or out.shape != x.shape:
+            raise KernelError(f"rmsnorm: weight {tuple(weight.shape)} / out {tuple(out.shape)} do not "
+                              f"match x {tuple(x.shape)}")
+        _check(self.lib.chibi_rmsnorm(_ptr(x), _code(x), _ptr(weight), _code(weight), _ptr(out),
+                                      _code(out), x.shape[0], n, x.stride(0), out.stride(0),
+                                      float(eps), float(offset), self._stream()), "rmsnorm")
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+               residual: Optional[torch.Tensor] = None) -> None:
+        """out[M, N] = x[M, K] @ w[N, K]^T (+ residual, 32-bit, may alias out)."""
+        _need_cuda(x, w, out, residual)
+        _rows_contiguous(x, "linear: x")
+        _rows_contiguous(w, "linear: w")
+        _rows_contiguous(out, "linear: out")
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape != (M, N):
+            raise KernelError(f"linear: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+        if residual is not None:
+            _rows_contiguous(residual, "linear: residual")
+            if residual.dtype != torch.float32 or residual.shape != (M, N):
+                raise KernelError("linear: residual must be float32 [M, N]")
+        _check(self.lib.chibi_gemm_simt(
+            _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _ptr(residual), M, N, K,
+            x.stride(0), w.stride(0), out.stride(0),
+            residual.stride(0) if residual is not None else 0, self._stream()), "linear")
+
+    def qk_norm_rope_append(self, qkv: torch.Tensor, q_out: torch.Tensor,
+                            k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                            q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                            inv_freq: Optional[torch.Tensor], rotary_dim: int, eps: float,
+                            norm_offset: float, positions: torch.Tensor,
+                            seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
+                            nq: int, nkv: int, d: int, page_size: int) -> None:
+        """Per head: RMSNorm (when a weight is given), split-half rotation of the
+        first ``rotary_dim`` features, then q -> q_out, k and v -> cache pages.
+        qkv: [T, (nq + 2 nkv) d], or [T, nq d] when no cache is given (the layer
+        then reads another layer's cache).  Cache: [pages, nkv, page_size, d]."""
+        _need_cuda(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, inv_freq, positions,
+                   seq_of_token, block_table)
+        _rows_contiguous(qkv, "qk_norm_rope_append: qkv")
+        T = qkv.shape[0]
+        append = k_cache is not None
+        width = (nq + 2 * nkv) * d if append else nq * d
+        if qkv.shape[1] < width or not q_out.is_contiguous() or q_out.shape != (T, nq * d):
+            raise KernelError("qk_norm_rope_append: qkv / q_out shapes")
+        if q_out.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope_append: q_out must have qkv's element type")
+        if (q_norm_w is None) != (k_norm_w is None):
+            raise KernelError("qk_norm_rope_append: give both norm weights or none")
+        if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32
+                           or inv_freq.numel() < rotary_dim // 2):
+            raise KernelError("qk_norm_rope_append: inv_freq must hold rotary_dim/2 float32 values")
+        num_pages = 0
+        table_stride = 0
+        if append:
+            if (k_cache.shape != v_cache.shape or k_cache.dim() != 4 or not k_cache.is_contiguous()
+                    or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
+                raise KernelError(f"qk_norm_rope_append: cache shape {tuple(k_cache.shape)}")
+            num_pages = k_cache.shape[0]
+            _rows_contiguous(block_table, "qk_norm_rope_append: block_table")
+            table_stride = block_table.stride(0)
+        w_type = _code(q_norm_w) if q_norm_w is not None else F32
+        _check(self.lib.chibi_qk_norm_rope_append(
+            _ptr(qkv), _code(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+            _code(k_cache) if append else F32, _ptr(q_norm_w), _ptr(k_norm_w), w_type,
+            _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token), _ptr(block_table), table_stride, T,
+            nq, nkv, d, int(rotary_dim), page_size, num_pages, float(eps), float(norm_offset),
+            1 if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append")
+
+    def attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  out: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
+                  ctx_len: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
+                  nq: int, nkv: int, d: int, page_size: int, scale: float,
+                  window: Optional[int], max_q_len: int, max_ctx_len: int) -> None:
+        """Causal attention of every token over its sequence's pages."""
+        _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions)
+        T = q.shape[0]
+        if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != q.shape:
+            raise KernelError("attention: q / out must be contiguous [T, nq*d]")
+        if out.dtype != q.dtype:
+            raise KernelError("attention: out must have q's element type")
+        if (k_cache.shape != v_cache.shape or k_cache.dim() != 4 or not k_cache.is_contiguous()
+                or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
+            raise KernelError(f"attention: cache shape {tuple(k_cache.shape)}")
+        _rows_contiguous(block_table, "attention: block_table")
+        _check(self.lib.chibi_attention_generic(
+            _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
+            _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
+            _ptr(seq_of_token), _ptr(positions), T, nq, nkv, d, page_size, k_cache.shape[0],
+            float(scale), int(window or 0), _ptr(self.error), self._stream()), "attention")
+
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        _need_cuda(gate_up, out)
+        if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.shape[1] != 2 * out.shape[1] \
+                or gate_up.shape[0] != out.shape[0]:
+            raise KernelError("swiglu: gate_up must be contiguous [T, 2I] and out [T, I]")
+        _check(self.lib.chibi_swiglu(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out),
+                                     out.shape[0], out.shape[1], self._stream()), "swiglu")
+
+    def gather_rows(self, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+        _need_cuda(x, rows, out)
+        if not x.is_contiguous() or not out.is_contiguous() or rows.dtype != torch.int32 \
+                or out.shape != (rows.numel(), x.shape[1]):
+            raise KernelError("gather_rows: shapes")
+        _check(self.lib.chibi_gather_rows(_ptr(x), _code(x), _ptr(rows), _ptr(out), _code(out),
+                                          rows.numel(), x.shape[1], x.shape[0], self._stream()),
+               "gather_rows")
+
+    def cast(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        _need_cuda(x, out)
+        if not x.is_contiguous() or not out.is_contiguous() or x.numel() != out.numel():
+            raise KernelError("cast: shapes")
+        _check(self.lib.chibi_cast(_ptr(x), _code(x), _ptr(out), _code(out), x.numel(),
+                                   self._stream()), "cast")
+
+    def add_into(self, acc: torch.Tensor, x: torch.Tensor) -> None:
+        _need_cuda(acc, x)
+        if acc.dtype != torch.float32 or not acc.is_contiguous() or not x.is_contiguous() \
+                or acc.numel() != x.numel():
+            raise KernelError("add_into: acc must be contiguous float32 of x's size")
+        _check(self.lib.chibi_add_into(_ptr(acc), _ptr(x), _code(x), x.numel(), self._stream()),
+               "add_into")
+
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor],
+               uniform: Optional[torch.Tensor], out: torch.Tensor) -> None:
+        """Greedy rows (temperature <= 0 or None) take the arg max, ties to the
+        lowest id; other rows sample by inverse CDF with the given uniform."""
+        _need_cuda(logits, temperature, uniform, out)
+        _rows_contiguous(logits, "sample: logits")
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() != logits.shape[0]:
+            raise KernelError("sample: logits float32 [R, V], out int32 [R]")
+        for t in (temperature, uniform):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != logits.shape[0]):
+                raise KernelError("sample: temperature / uniform must be float32 [R]")
+        _check(self.lib.chibi_sample(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
+                                     _ptr(temperature), _ptr(uniform), _ptr(out), self._stream()),
+               "sample")

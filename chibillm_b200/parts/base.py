@@ -1,0 +1,189 @@
+"""Interfaces of the parts a decoder is put together from, and their registries.
+
+A part is built from its spec (sizes and constants as fields) and the names of
+its tensors.  It declares which tensors it expects, takes them when they are
+loaded, says what cache it needs, and runs on a batch.  No part knows which
+model it is in.
+
+Kinds are looked up in registries, so a new mixer, feed-forward, norm, position
+encoding or block arrangement is a class plus one ``register_*`` call; nothing
+in the framework's files has to change for it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+
+# ------------------------------------------------------------------ runtime
+@dataclass
+class Runtime:
+    """What every part needs to run: device, activation type, kernels."""
+
+    device: torch.device
+    dtype: torch.dtype           # activations and caches: torch.bfloat16 or torch.float32
+    kernels: object              # the operations (chibillm_b200.kernels.ops.CudaKernels)
+
+    @property
+    def is_float32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+# ------------------------------------------------------------------ tensors
+@dataclass(frozen=True)
+class TensorSpec:
+    """A tensor a part expects in the checkpoint."""
+
+    name: str
+    shape: Tuple[int, ...]
+    kind: str = "float"          # "float" (kept bfloat16 / 32-bit) or "int" (kept int32)
+
+
+# ------------------------------------------------------------------ cache needs
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values of every position, in pages; ``window`` None = all keys
+    stay, an integer = only that many most recent ones are ever read."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class FixedStateNeed:
+    """Per-request state of fixed size: named arrays, zeroed when a request is
+    admitted.  ``arrays``: ((name, shape, dtype), ...)."""
+
+    arrays: Tuple[Tuple[str, Tuple[int, ...], torch.dtype], ...]
+
+
+# ------------------------------------------------------------------ parts
+class Part:
+    def expected_tensors(self) -> List[TensorSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take the loaded tensors (already on the device) this part declared."""
+
+
+class Norm(Part):
+    """y = norm(x) over the last ``spec.size`` features."""
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Position information applied to queries and keys inside a mixer.
+
+    ``fused_rotation()`` returns (inv_freq table, rotary_dim) when the encoding
+    is a split-half rotation that the attention kernels apply themselves, else
+    None; then ``apply`` is called on q and k before they are cached.
+    """
+
+    def fused_rotation(self):
+        return None
+
+    def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], ctx) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a sequence.
+
+    ``forward`` reads the normalised input ``x`` [T, hidden] and adds its result
+    into the 32-bit ``residual`` [T, hidden].  ``cache`` is what the cache
+    manager made for this run step from ``cache_need()`` (a PagedKVView, a
+    FixedStateView or None).
+    """
+
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Per-token transformation; adds its result into ``residual``."""
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """An arrangement of mixer, feed-forward and norms around the residual."""
+
+    mixer: Mixer
+
+    def forward(self, residual: torch.Tensor, ctx, cache) -> None:
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------ registries
+_NORMS: Dict[str, Callable] = {}
+_POSITIONS: Dict[str, Callable] = {}
+_MIXERS: Dict[str, Callable] = {}
+_FEED_FORWARDS: Dict[str, Callable] = {}
+_BLOCKS: Dict[str, Callable] = {}
+
+
+def _register(table: Dict[str, Callable], what: str, kind: str, factory: Callable, replace: bool):
+    if kind in table and not replace:
+        raise ValueError(f"{what} kind '{kind}' is already registered")
+    table[kind] = factory
+
+
+def _lookup(table: Dict[str, Callable], what: str, kind: str) -> Callable:
+    try:
+        return table[kind]
+    except KeyError:
+        raise KeyError(f"{what} kind '{kind}' is not registered; known: {sorted(table)}") from None
+
+
+def register_norm(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(spec: NormSpec, weight_name: str, runtime) -> Norm"""
+    _register(_NORMS, "norm", kind, factory, replace)
+
+
+def register_position(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(spec: PositionSpec, runtime) -> PositionEncoding"""
+    _register(_POSITIONS, "position encoding", kind, factory, replace)
+
+
+def register_mixer(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(spec: MixerSpec, names: dict role -> tensor name, runtime) -> Mixer"""
+    _register(_MIXERS, "mixer", kind, factory, replace)
+
+
+def register_feed_forward(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(spec: FeedForwardSpec, names: dict role -> tensor name, runtime) -> FeedForward"""
+    _register(_FEED_FORWARDS, "feed-forward", kind, factory, replace)
+
+
+def register_block(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(layer: LayerSpec, runtime) -> Block"""
+    _register(_BLOCKS, "block arrangement", kind, factory, replace)
+
+
+def make_norm(spec, weight_name: str, runtime: Runtime) -> Norm:
+    return _lookup(_NORMS, "norm", spec.kind)(spec, weight_name, runtime)
+
+
+def make_position(spec, runtime: Runtime) -> PositionEncoding:
+    return _lookup(_POSITIONS, "position encoding", spec.kind)(spec, runtime)
+
+
+def make_mixer(spec, names: Dict[str, str], runtime: Runtime) -> Mixer:
+    return _lookup(_MIXERS, "mixer", spec.kind)(spec, names, runtime)
+
+
+def make_feed_forward(spec, names: Dict[str, str], runtime: Runtime) -> FeedForward:
+    return _lookup(_FEED_FORWARDS, "feed-forward", spec.kind)(spec, names, runtime)
+
+
+def make_block(layer, runtime: Runtime) -> Block:
+    return _lookup(_BLOCKS, "block arrangement", layer.arrangement)(layer, runtime)

@@ -1,0 +1,37 @@
+"""RMSNorm as a part: y = (x * rsqrt(mean(x^2) + eps)) * (w + offset), statistics
+in 32-bit (src/metal/kernels/tensor_ops.metal:76-105)."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .base import Norm, Runtime, TensorSpec, register_norm
+
+
+class RMSNorm(Norm):
+    def __init__(self, spec, weight_name: str, runtime: Runtime):
+        self.spec = spec
+        self.weight_name = weight_name
+        self.runtime = runtime
+        self.weight: torch.Tensor = None
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        return [TensorSpec(self.weight_name, (self.spec.size,))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """x, out: [rows, k * size]; every run of ``size`` features is one group."""
+        n = self.spec.size
+        if x.shape[-1] == n:
+            self.runtime.kernels.rmsnorm(x, self.weight, self.spec.eps, self.spec.weight_offset, out)
+        else:
+            if not x.is_contiguous() or not out.is_contiguous():
+                raise ValueError("grouped norm needs contiguous rows")
+            self.runtime.kernels.rmsnorm(x.view(-1, n), self.weight, self.spec.eps,
+                                         self.spec.weight_offset, out.view(-1, n))
+
+
+register_norm("rmsnorm", RMSNorm, replace=True)
