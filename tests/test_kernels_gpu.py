@@ -1,0 +1,272 @@
+"""Each CUDA kernel alone against its plain PyTorch restatement
+(tests/reference_ops.py), at sizes other than the engine tests use: head sizes
+16/48/128, group sizes 1/2/5, widths and vocabularies that are no power of two,
+token counts that are no multiple of a tile, positions that straddle pages."""
+import math
+
+import pytest
+import torch
+
+from reference_ops import ReferenceKernels
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def k():
+    from chibillm_b200.kernels.ops import CudaKernels
+    return CudaKernels(torch.device("cuda:0"))
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return ReferenceKernels()
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def close(a, b, dtype, what, rel=None):
+    a, b = a.float(), b.float()
+    scale = float(b.abs().max()) + 1e-30
+    tol = rel if rel is not None else (3e-6 if dtype == torch.float32 else 1.2e-2)
+    worst = float((a - b).abs().max())
+    assert torch.isfinite(a).all(), f"{what}: not finite"
+    assert worst <= tol * scale, f"{what}: max |diff| {worst:.3e} > {tol:.1e} * {scale:.3e}"
+
+
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_embed(k, ref, wdtype):
+    table = rnd(1000, 200, dtype=wdtype)
+    tokens = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32, device="cuda")
+    out = torch.full((5, 200), float("nan"), device="cuda")
+    exp = torch.empty_like(out)
+    k.embed(tokens, table, out)
+    ref.embed(tokens, table, exp)
+    assert torch.equal(out, exp)
+
+
+@pytest.mark.parametrize("n", [16, 200, 4096])
+@pytest.mark.parametrize("xdtype,odtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                           (torch.bfloat16, torch.bfloat16)])
+def test_rmsnorm(k, ref, n, xdtype, odtype):
+    x = rnd(37, n, dtype=xdtype, seed=1, scale=3.0)
+    w = (1 + 0.1 * rnd(n, seed=2)).to(odtype)
+    out = torch.full((37, n), float("nan"), dtype=odtype, device="cuda")
+    exp = torch.empty_like(out)
+    k.rmsnorm(x, w, 1e-5, 0.0, out)
+    ref.rmsnorm(x, w, 1e-5, 0.0, exp)
+    close(out, exp, odtype, "rmsnorm", rel=3e-6 if odtype == torch.float32 else 8e-3)
+    # strided rows and a weight offset
+    wide = rnd(9, 3 * n, dtype=xdtype, seed=3)
+    view = wide[:, n:2 * n]
+    out2 = torch.empty(9, n, dtype=odtype, device="cuda")
+    exp2 = torch.empty_like(out2)
+    k.rmsnorm(view, w, 1e-6, 1.0, out2)
+    ref.rmsnorm(view, w, 1e-6, 1.0, exp2)
+    close(out2, exp2, odtype, "rmsnorm strided", rel=3e-6 if odtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("M", [1, 5, 64, 130])
+@pytest.mark.parametrize("xdtype,wdtype,odtype", [
+    (torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+    (torch.bfloat16, torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16, torch.float32),
+    (torch.bfloat16, torch.float32, torch.bfloat16)])
+def test_linear(k, ref, M, xdtype, wdtype, odtype):
+    N, K = 203, 100
+    x = rnd(M, K, dtype=xdtype, seed=4)
+    w = rnd(N, K, dtype=wdtype, seed=5, scale=0.1)
+    out = torch.full((M, N), float("nan"), dtype=odtype, device="cuda")
+    exp = torch.empty_like(out)
+    k.linear(x, w, out)
+    ref.linear(x, w, exp)
+    close(out, exp, odtype, "linear")
+    if odtype == torch.float32:
+        res = rnd(M, N, seed=6)
+        exp_res = torch.empty_like(res)
+        ref.linear(x, w, exp_res, residual=res)
+        k.linear(x, w, res, residual=res)          # in place
+        close(res, exp_res, odtype, "linear + residual")
+
+
+def _paged_setup(seq_ctx, q_lens, page_size, num_pages, seed):
+    """Block tables through shuffled pages for sequences that hold ``seq_ctx``
+    tokens after feeding their last ``q_lens`` ones."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    S = len(seq_ctx)
+    width = max((c + page_size - 1) // page_size for c in seq_ctx)
+    table = torch.full((S, width), -1, dtype=torch.int32)
+    cursor = 0
+    for s, c in enumerate(seq_ctx):
+        n = (c + page_size - 1) // page_size
+        table[s, :n] = torch.tensor(perm[cursor:cursor + n], dtype=torch.int32)
+        cursor += n
+    assert cursor <= num_pages
+    positions, seq_of_token, q_start = [], [], [0]
+    for s, (c, n) in enumerate(zip(seq_ctx, q_lens)):
+        positions += list(range(c - n, c))
+        seq_of_token += [s] * n
+        q_start.append(q_start[-1] + n)
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    return table.cuda(), dev(positions), dev(seq_of_token), dev(q_start), dev(seq_ctx)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,norms", [(6, 2, 48, 48, True), (4, 4, 16, 8, True),
+                                                (5, 1, 128, 128, False), (2, 1, 32, 0, True)])
+def test_qk_norm_rope_append(k, ref, dtype, nq, nkv, d, rot, norms):
+    page, pages = 8, 40
+    seq_ctx, q_lens = [19, 8, 70], [19, 1, 7]
+    table, positions, seq_of_token, _, _ = _paged_setup(seq_ctx, q_lens, page, pages, seed=7)
+    T = sum(q_lens)
+    qkv = rnd(T, (nq + 2 * nkv) * d, dtype=dtype, seed=8)
+    qn = (1 + 0.1 * rnd(d, seed=9)).to(dtype) if norms else None
+    kn = (1 + 0.1 * rnd(d, seed=10)).to(dtype) if norms else None
+    inv_freq = torch.pow(torch.tensor(1e4), -2 * torch.arange(max(rot, 2) // 2, dtype=torch.float32) / max(rot, 2)).cuda()
+    outs = []
+    for impl in (k, ref):
+        q_out = torch.full((T, nq * d), float("nan"), dtype=dtype, device="cuda")
+        kc = torch.full((pages, nkv, page, d), 7.0, dtype=dtype, device="cuda")
+        vc = torch.full((pages, nkv, page, d), 7.0, dtype=dtype, device="cuda")
+        impl.qk_norm_rope_append(qkv, q_out, kc, vc, qn, kn, inv_freq if rot else None, rot, 1e-6, 0.0,
+                                 positions, seq_of_token, table, nq, nkv, d, page)
+        outs.append((q_out, kc, vc))
+    if hasattr(k, "check_error_word"):
+        k.check_error_word()
+    tol = 3e-6 if dtype == torch.float32 else 8e-3
+    close(outs[0][0], outs[1][0], dtype, "q", rel=tol)
+    close(outs[0][1], outs[1][1], dtype, "key cache", rel=tol)
+    assert torch.equal(outs[0][2], outs[1][2]), "value cache"
+    # q only: a layer that reads another layer's cache
+    q_only = torch.empty(T, nq * d, dtype=dtype, device="cuda")
+    k.qk_norm_rope_append(qkv[:, :nq * d].contiguous(), q_only, None, None, qn, kn,
+                          inv_freq if rot else None, rot, 1e-6, 0.0, positions, seq_of_token, None,
+                          nq, nkv, d, page)
+    close(q_only, outs[1][0], dtype, "q only", rel=tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,window", [(4, 2, 16, None), (6, 3, 48, 24), (5, 1, 128, None),
+                                             (8, 8, 64, 7), (10, 2, 32, 33)])
+def test_attention_against_plain(k, ref, dtype, nq, nkv, d, window):
+    page, pages = 8, 64
+    # whole prompts, single decoded tokens at page edges, a portion in the middle
+    seq_ctx, q_lens = [33, 64, 65, 16, 150], [33, 1, 1, 16, 21]
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, q_lens, page, pages, seed=11)
+    T = sum(q_lens)
+    q = rnd(T, nq * d, dtype=dtype, seed=12)
+    # pages that no sequence owns hold NaN: reading one would show
+    kc = torch.full((pages, nkv, page, d), float("nan"), dtype=dtype, device="cuda")
+    vc = torch.full((pages, nkv, page, d), float("nan"), dtype=dtype, device="cuda")
+    for s, c in enumerate(seq_ctx):
+        for p in range(c):
+            pg = int(table[s, p // page])
+            kc[pg, :, p % page, :] = rnd(nkv, d, dtype=dtype, seed=1000 + 17 * s + p)
+            vc[pg, :, p % page, :] = rnd(nkv, d, dtype=dtype, seed=5000 + 17 * s + p)
+    out = torch.full((T, nq * d), float("nan"), dtype=dtype, device="cuda")
+    exp = torch.empty_like(out)
+    scale = 1.0 / math.sqrt(d)
+    args = (table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, scale, window,
+            max(q_lens), max(seq_ctx))
+    k.attention(q, kc, vc, out, *args)
+    ref.attention(q, kc, vc, exp, *args)
+    k.check_error_word()
+    close(out, exp, dtype, "attention", rel=1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("needle,window", [(0, None), (3, None), (255, None), (256, None), (700, None),
+                                           (1000 - 40, 40), (1000 - 41, 40)])
+def test_attention_finds_one_far_key(k, dtype, needle, window):
+    """One key among a thousand matches the query; the output must be that key's
+    value -- or, if the key lies just outside the window, must not be."""
+    nq, nkv, d, page = 2, 1, 64, 16
+    ctx = 1000
+    pages = 80
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup([ctx], [1], page, pages, seed=13)
+    q = torch.zeros(1, nq * d, dtype=dtype, device="cuda")
+    q[0, 5] = 40.0
+    q[0, d + 5] = 40.0
+    kc = (0.01 * rnd(pages, nkv, page, d, seed=14)).to(dtype)
+    vc = rnd(pages, nkv, page, d, dtype=dtype, seed=15)
+    pg = int(table[0, needle // page])
+    kc[pg, 0, needle % page, 5] = 40.0
+    out = torch.empty(1, nq * d, dtype=dtype, device="cuda")
+    k.attention(q, kc, vc, out, table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page,
+                1.0 / math.sqrt(d), window, 1, ctx)
+    target = vc[pg, 0, needle % page, :].float()
+    visible = window is None or needle > (ctx - 1) - window
+    got = out.float().view(nq, d)
+    for h in range(nq):
+        err = float((got[h] - target).abs().max())
+        if visible:
+            assert err < 2e-2, f"head {h}: the key at {needle} was not found (err {err})"
+        else:
+            assert err > 0.3, f"head {h}: the key at {needle} lies outside the window but was used"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_gather(k, ref, dtype):
+    gu = rnd(13, 2 * 176, dtype=dtype, seed=16, scale=3.0)
+    out = torch.empty(13, 176, dtype=dtype, device="cuda")
+    exp = torch.empty_like(out)
+    k.swiglu(gu, out)
+    ref.swiglu(gu, exp)
+    close(out, exp, dtype, "swiglu", rel=3e-6 if dtype == torch.float32 else 8e-3)
+    x = rnd(29, 80, seed=17)
+    rows = torch.tensor([28, 0, 7, 7], dtype=torch.int32, device="cuda")
+    g = torch.empty(4, 80, device="cuda")
+    k.gather_rows(x, rows, g)
+    assert torch.equal(g, x[rows.long()])
+
+
+def test_cast_and_add(k):
+    x = rnd(1001, dtype=torch.float32, seed=18)
+    y = torch.empty(1001, dtype=torch.bfloat16, device="cuda")
+    k.cast(x, y)
+    assert torch.equal(y, x.to(torch.bfloat16))
+    acc = rnd(1001, seed=19)
+    exp = acc + y.float()
+    k.add_into(acc, y)
+    assert torch.equal(acc, exp)
+
+
+@pytest.mark.parametrize("vocab", [301, 4096, 151936])
+def test_sample_greedy_and_ties(k, vocab):
+    logits = rnd(5, vocab, seed=20)
+    logits[1, 17] = 50.0
+    logits[1, 200] = 50.0          # tie: the lower id wins
+    logits[2, vocab - 1] = 60.0
+    logits[3] = 0.0                # all equal: id 0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    k.sample(logits, None, None, out)
+    exp = [int(torch.nonzero(logits[r] == logits[r].max())[0, 0]) for r in range(5)]
+    assert out.tolist() == exp
+    assert exp[1] == 17 and exp[2] == vocab - 1 and exp[3] == 0
+
+
+@pytest.mark.parametrize("vocab", [301, 151936])
+def test_sample_temperature(k, vocab):
+    R = 64
+    logits = rnd(R, vocab, seed=21, scale=2.0)
+    temps = torch.full((R,), 0.7, device="cuda")
+    temps[0] = 0.0                                     # a greedy row beside sampled ones
+    uni = torch.rand(R, generator=torch.Generator(device="cuda").manual_seed(22), device="cuda")
+    uni[1], uni[2] = 0.0, 0.99999994
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    k.sample(logits, temps, uni, out)
+    got = out.tolist()
+    assert got[0] == int(logits[0].argmax())
+    for r in range(1, R):
+        p = torch.exp((logits[r].double() - logits[r].double().max()) / 0.7)
+        cdf = torch.cumsum(p, 0) / p.sum()
+        u = float(uni[r])
+        lo = float(cdf[got[r] - 1]) if got[r] > 0 else 0.0
+        hi = float(cdf[got[r]])
+        # the chosen id's interval of the CDF holds u, up to 32-bit rounding of the sums
+        assert lo - 1e-4 <= u <= hi + 1e-4, f"row {r}: id {got[r]} covers [{lo}, {hi}], u = {u}"
