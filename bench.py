@@ -1,0 +1,355 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of chibillm_b200 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step.  The default run has the layer sizes of the
+Qwen3-8B shape with random bfloat16 weights, a batch of 8 and a context capacity
+of 4,096 tokens per request (2,048 held when decoding starts).  One JSON line is
+printed: ``value`` is decoded tokens a second over K device-timed steps; ``e2e``
+the same through the Python entry point (host token ids in, sampled ids out,
+every step); ``prefill`` a 2,048-token prompt in one step; ``roofline`` the
+decode step's bytes (every weight once, the cache of the live requests) over
+its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
+64.  Token ids are uniform random; the caches that decoding starts from are
+filled by real prefill steps for the end-to-end run and with random values for
+the device-timed runs (the work of a decode step does not depend on the values).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "attention_bias": False,
+    "hidden_act": "silu", "rope_scaling": None, "torch_dtype": "bfloat16",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
+    "tie_word_embeddings": False, "use_sliding_window": False, "sliding_window": None,
+}
+FULL_LAYERS = 36
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                obj = json.load(f)
+            peaks = {k: float(obj[k]) for k in ("hbm_gbs", "bf16_tflops") if k in obj}
+            peaks["bf16_tflops_sustained"] = float(obj.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+            if len(peaks) == 3:
+                return peaks, "measured"
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed
+    region runs (reading only; nothing is set)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ accounting
+def layer_weight_elements(c) -> int:
+    H, I = c["hidden_size"], c["intermediate_size"]
+    qw = c["num_attention_heads"] * c["head_dim"]
+    kw = c["num_key_value_heads"] * c["head_dim"]
+    return H * (qw + 2 * kw) + qw * H + 3 * H * I
+
+
+def decode_step_bytes(c, layers, ctx_lens) -> float:
+    """Bytes a decode step has to read: every weight it uses once (layers, norms,
+    output matrix, the embedding rows of its tokens) and the cache of the live
+    requests."""
+    H = c["hidden_size"]
+    weights = layers * (layer_weight_elements(c) + 2 * H + 2 * c["head_dim"]) + H + c["vocab_size"] * H
+    weights += len(ctx_lens) * H
+    kv_per_token = layers * 2 * c["num_key_value_heads"] * c["head_dim"]
+    return 2.0 * (weights + kv_per_token * sum(ctx_lens))
+
+
+def prefill_flops(c, layers, tokens, wanted_rows=1) -> float:
+    linear = 2.0 * tokens * layers * layer_weight_elements(c)
+    attention = layers * 2.0 * c["num_attention_heads"] * c["head_dim"] * float(tokens) * tokens
+    head = 2.0 * wanted_rows * c["hidden_size"] * c["vocab_size"]
+    return linear + attention + head
+
+
+# ------------------------------------------------------------------ measurements
+def fill_request(runner, request_id, tokens_held: int) -> None:
+    """Give a request ``tokens_held`` tokens of context without running them:
+    pages are reserved and hold whatever the pool was filled with."""
+    runner.admit(request_id)
+    runner.cache.reserve(request_id, tokens_held)
+    runner.cache.commit(request_id, tokens_held)
+
+
+def measure_decode(runner, sampler, batch, ctx_start, steps, warmup, vocab, tag):
+    """K decode steps of ``batch`` requests, timed on the device."""
+    import torch
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.sampling import SamplingParams
+
+    ids = [f"{tag}{i}" for i in range(batch)]
+    for rid in ids:
+        fill_request(runner, rid, ctx_start)
+    g = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, vocab, (batch,), generator=g).tolist()
+    params = [SamplingParams()] * batch
+    keys = list(range(batch))
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = 0
+    ctx_lens = []
+    for i in range(warmup + steps):
+        if i == warmup:
+            torch.cuda.synchronize()
+            launches0 = runner.runtime.kernels.launches
+            start.record()
+        if i >= warmup:
+            ctx_lens.append(ctx_start + i + 1)
+        logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)], check=False)
+        tokens = sampler.sample(logits, params, keys, [i] * batch)
+    end.record()
+    torch.cuda.synchronize()
+    runner.runtime.kernels.check_error_word()
+    ms = start.elapsed_time(end)
+    launches = runner.runtime.kernels.launches - launches0
+    for rid in ids:
+        runner.end(rid)
+    mean_ctx = sum(ctx_lens) / len(ctx_lens)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+            "mean_ctx": mean_ctx}
+
+
+def measure_prefill(runner, tokens_n, vocab, repeats=3):
+    import torch
+    from chibillm_b200.engine.batch import StepEntry
+
+    g = torch.Generator().manual_seed(2)
+    best = None
+    for r in range(repeats + 1):
+        ids = torch.randint(0, vocab, (tokens_n,), generator=g).tolist()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry("prefill", ids, [tokens_n - 1])], check=False)
+        end.record()
+        torch.cuda.synchronize()
+        runner.end("prefill")
+        ms = start.elapsed_time(end)
+        if r > 0:                          # the first run warms up
+            best = ms if best is None else min(best, ms)
+    runner.runtime.kernels.check_error_word()
+    return best
+
+
+def measure_e2e(llm, batch, prompt_len, steps, warmup, vocab):
+    """The same decode steps through the public entry point: every step takes
+    host token ids (the packed batch goes to the device from pinned memory) and
+    returns the sampled ids to the host."""
+    import torch
+    from chibillm_b200.sampling import SamplingParams
+
+    g = torch.Generator().manual_seed(3)
+    engine = llm.engine
+    for i in range(batch):
+        prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+        engine.add(("e2e", i), prompt, SamplingParams(max_new_tokens=warmup + steps + 8, ignore_eos=True))
+    while any(s.status == "waiting" for s in engine.scheduler.sequences.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = llm.runner.last_meta_bytes
+    for i in range(batch):
+        engine.cancel(("e2e", i))
+        engine.remove(("e2e", i))
+    return {"tok_s": produced / dt, "h2d": h2d, "d2h": batch * 4 + 4}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="run only the first layers (each at full size); the JSON names both numbers")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=2048, help="tokens held when decoding starts")
+    ap.add_argument("--context", type=int, default=4096, help="context capacity per request")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--point-steps", type=int, default=32)
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "nireo/chibillm is an Apple-Metal C++ program without setup.py or pyproject.toml; "
+                          "pip cannot install it and no machine here can run Metal"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this engine runs on a single GPU (--gpus {args.gpus} refused)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import chibillm_b200
+    from chibillm_b200.sampling import Sampler
+
+    cfg = dict(QWEN3_8B)
+    layers = min(args.layers, FULL_LAYERS)
+    cfg["num_hidden_layers"] = layers
+    vocab = cfg["vocab_size"]
+    peaks, peaks_src = load_peaks()
+    big = 64 if not args.skip_points else args.batch
+    per_request = args.prompt + args.warmup + max(args.steps, args.point_steps) + 64
+    pool = ((max(big, args.batch) * per_request + 63) // 64) * 64
+    t_load = time.time()
+    llm = chibillm_b200.LLM(None, dtype="bfloat16", device="cuda:0", context_length=args.context,
+                            kv_cache_tokens=pool, max_sequences=max(big, args.batch),
+                            max_batch_tokens=max(8192, args.prefill_tokens), prefill_chunk_tokens=2048,
+                            random_config=cfg, random_seed=0)
+    runner = llm.runner
+    # the pool holds random values, so decoding from "filled" requests reads real numbers
+    for name in runner.storage.keys:
+        runner.storage.keys[name].normal_(0.0, 1.0)
+        runner.storage.values[name].normal_(0.0, 1.0)
+    sampler = Sampler(runner.runtime)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+
+    prefill_ms = measure_prefill(runner, args.prefill_tokens, vocab)
+    flops = prefill_flops(cfg, layers, args.prefill_tokens)
+
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = measure_decode(runner, sampler, args.batch, args.prompt, args.steps, args.warmup, vocab, "d")
+    clock_info = clocks.stop()
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = measure_decode(runner, sampler, b, args.prompt, args.point_steps, args.warmup, vocab, f"p{b}_")
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_ms_per_step"] = round(r["ms_per_step"], 4)
+            bytes_b = decode_step_bytes(cfg, layers, [r["mean_ctx"]] * b)
+            points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+
+    e2e = None
+    if not args.skip_e2e:
+        e2e = measure_e2e(llm, args.batch, args.prompt, args.steps, args.warmup, vocab)
+
+    step_bytes = decode_step_bytes(cfg, layers, [main_run["mean_ctx"]] * args.batch)
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random bf16 weights, KV bf16 paged, block 16)",
+        "value": round(main_run["tok_s"], 2),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape, random weights", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "single GPU", "layers": layers, "layers_full": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": vocab, "kv_block": 16,
+            "decode_ctx_start": args.prompt, "prefill_tokens": args.prefill_tokens,
+            "l2": "inputs larger than L2: every step streams all weights",
+            "peaks": peaks_src,
+        },
+        "prefill": {"value": round(args.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": args.prefill_tokens,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "gpu_launches": int(main_run["launches"]),
+        "clocks": clock_info,
+        "load_seconds": round(load_s, 1),
+    }
+    if e2e is not None:
+        out["e2e"] = {"value": round(e2e["tok_s"], 2), "unit": "tokens/s",
+                      "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -19,18 +19,26 @@ class LLM:
     ``max_sequences`` requests of ``context_length``).  The option names are the
     reference's command-line flags (src/cli_options.cc:13-25)."""
 
-    def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
+    def __init__(self, model_dir: Optional[str], dtype: str = "bfloat16", device: str = "cuda:0",
                  context_length: int = 4096, kv_cache_tokens: Optional[int] = None,
                  max_sequences: int = 4, max_batch_tokens: int = 512, prefill_chunk_tokens: int = 64,
-                 page_size: int = KV_PAGE_SIZE, kernels=None):
+                 page_size: int = KV_PAGE_SIZE, kernels=None, random_config: Optional[dict] = None,
+                 random_seed: int = 0):
         if context_length <= 0 or context_length % page_size != 0:
             raise ValueError(f"context_length must be a positive multiple of {page_size}")
         pool = kv_cache_tokens if kv_cache_tokens is not None else context_length * max_sequences
         if pool <= 0 or pool % page_size != 0:
             raise ValueError(f"kv_cache_tokens must be a positive multiple of {page_size}")
-        self.runner = ModelRunner.from_folder(model_dir, dtype=dtype, device=device, page_size=page_size,
-                                              pool_tokens=pool, max_requests=max_sequences,
-                                              kernels=kernels)
+        if (model_dir is None) == (random_config is None):
+            raise ValueError("give a model folder or a configuration for random weights")
+        if model_dir is not None:
+            self.runner = ModelRunner.from_folder(model_dir, dtype=dtype, device=device,
+                                                  page_size=page_size, pool_tokens=pool,
+                                                  max_requests=max_sequences, kernels=kernels)
+        else:
+            self.runner = ModelRunner.from_random(random_config, seed=random_seed, dtype=dtype,
+                                                  device=device, page_size=page_size, pool_tokens=pool,
+                                                  max_requests=max_sequences, kernels=kernels)
         self.context_length = min(context_length, self.runner.max_context_tokens)
         self.engine = InferenceEngine(self.runner, SchedulerConfig(
             max_sequences=max_sequences, max_batch_tokens=max_batch_tokens,

@@ -67,6 +67,8 @@ class ModelRunner:
         self.workspace = Workspace(runtime.device)
         self._meta_host: Optional[torch.Tensor] = None
         self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_copied = None      # event: the last copy out of the pinned array is done
+        self.last_meta_bytes = 0      # bytes the last step sent to the device
         self.steps_run = 0
 
     # ------------------------------------------------------------ construction
@@ -77,6 +79,25 @@ class ModelRunner:
         runtime = make_runtime(dtype, device, kernels)
         model = DecoderModel(spec, runtime)
         load_weights(model, model_dir, runtime)
+        return cls(model, runtime, page_size, pool_tokens, max_requests)
+
+    @classmethod
+    def from_random(cls, config_object: dict, seed: int = 0, dtype="bfloat16", device="cuda:0",
+                    page_size: int = 16, pool_tokens: int = 4096, max_requests: int = 4,
+                    kernels=None, num_layers: Optional[int] = None) -> "ModelRunner":
+        """A model of the architecture and sizes that ``config_object`` (the
+        content of a config.json) names, with random weights made on the device.
+        ``num_layers`` runs only the first layers (for measurements that must fit
+        a time or memory limit; every layer keeps its full size)."""
+        from ..config.registry import find_architecture
+        from ..weights.random_init import bind_random_weights
+        if num_layers is not None:
+            config_object = dict(config_object, num_hidden_layers=num_layers)
+        arch = find_architecture(config_object)
+        spec = arch.model_spec(arch.read_config(config_object))
+        runtime = make_runtime(dtype, device, kernels)
+        model = DecoderModel(spec, runtime)
+        bind_random_weights(model, seed, runtime)
         return cls(model, runtime, page_size, pool_tokens, max_requests)
 
     @property
@@ -150,8 +171,15 @@ class ModelRunner:
                 flat[o + s * w:o + s * w + len(row)] = row
                 for j in range(len(row), w):
                     flat[o + s * w + j] = -1
+        if self._meta_copied is not None:
+            self._meta_copied.synchronize()     # the pinned array may still be read by the last copy
         host[:cursor] = torch.tensor(flat, dtype=torch.int32)
         dev[:cursor].copy_(host[:cursor], non_blocking=True)
+        if dev.is_cuda:
+            if self._meta_copied is None:
+                self._meta_copied = torch.cuda.Event()
+            self._meta_copied.record()
+        self.last_meta_bytes = cursor * 4
 
         def view(name, n):
             o = offsets[name]

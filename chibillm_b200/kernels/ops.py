@@ -68,6 +68,7 @@ class CudaKernels:
             raise KernelError(f"device '{device}' is not a CUDA device; chibillm_b200 has no CPU path")
         self.lib = library.load("chibi_kernels")
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0           # kernels of this package launched so far
 
     # ------------------------------------------------------------------ helpers
     @staticmethod
@@ -93,6 +94,7 @@ class CudaKernels:
             raise KernelError("embed: out must be contiguous [tokens, hidden]")
         if not table.is_contiguous():
             raise KernelError("embed: table must be contiguous")
+        self.launches += 1
         _check(self.lib.chibi_embed(_ptr(tokens), _ptr(table), _code(table), _ptr(out), _code(out),
                                     tokens.numel(), table.shape[1], table.shape[0],
                                     _ptr(self.error), self._stream()), "embed")
@@ -107,6 +109,7 @@ class CudaKernels:
         if weight.shape != (n,) or not weight.is_contiguous() or out.shape != x.shape:
             raise KernelError(f"rmsnorm: weight {tuple(weight.shape)} / out {tuple(out.shape)} do not "
                               f"match x {tuple(x.shape)}")
+        self.launches += 1
         _check(self.lib.chibi_rmsnorm(_ptr(x), _code(x), _ptr(weight), _code(weight), _ptr(out),
                                       _code(out), x.shape[0], n, x.stride(0), out.stride(0),
                                       float(eps), float(offset), self._stream()), "rmsnorm")
@@ -126,6 +129,7 @@ class CudaKernels:
             _rows_contiguous(residual, "linear: residual")
             if residual.dtype != torch.float32 or residual.shape != (M, N):
                 raise KernelError("linear: residual must be float32 [M, N]")
+        self.launches += 1
         _check(self.lib.chibi_gemm_simt(
             _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _ptr(residual), M, N, K,
             x.stride(0), w.stride(0), out.stride(0),
@@ -167,6 +171,7 @@ class CudaKernels:
             _rows_contiguous(block_table, "qk_norm_rope_append: block_table")
             table_stride = block_table.stride(0)
         w_type = _code(q_norm_w) if q_norm_w is not None else F32
+        self.launches += 1
         _check(self.lib.chibi_qk_norm_rope_append(
             _ptr(qkv), _code(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
             _code(k_cache) if append else F32, _ptr(q_norm_w), _ptr(k_norm_w), w_type,
@@ -190,6 +195,7 @@ class CudaKernels:
                 or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
             raise KernelError(f"attention: cache shape {tuple(k_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
+        self.launches += 1
         _check(self.lib.chibi_attention_generic(
             _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
@@ -201,6 +207,7 @@ class CudaKernels:
         if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.shape[1] != 2 * out.shape[1] \
                 or gate_up.shape[0] != out.shape[0]:
             raise KernelError("swiglu: gate_up must be contiguous [T, 2I] and out [T, I]")
+        self.launches += 1
         _check(self.lib.chibi_swiglu(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out),
                                      out.shape[0], out.shape[1], self._stream()), "swiglu")
 
@@ -209,6 +216,7 @@ class CudaKernels:
         if not x.is_contiguous() or not out.is_contiguous() or rows.dtype != torch.int32 \
                 or out.shape != (rows.numel(), x.shape[1]):
             raise KernelError("gather_rows: shapes")
+        self.launches += 1
         _check(self.lib.chibi_gather_rows(_ptr(x), _code(x), _ptr(rows), _ptr(out), _code(out),
                                           rows.numel(), x.shape[1], x.shape[0], self._stream()),
                "gather_rows")
@@ -217,6 +225,7 @@ class CudaKernels:
         _need_cuda(x, out)
         if not x.is_contiguous() or not out.is_contiguous() or x.numel() != out.numel():
             raise KernelError("cast: shapes")
+        self.launches += 1
         _check(self.lib.chibi_cast(_ptr(x), _code(x), _ptr(out), _code(out), x.numel(),
                                    self._stream()), "cast")
 
@@ -225,6 +234,7 @@ class CudaKernels:
         if acc.dtype != torch.float32 or not acc.is_contiguous() or not x.is_contiguous() \
                 or acc.numel() != x.numel():
             raise KernelError("add_into: acc must be contiguous float32 of x's size")
+        self.launches += 1
         _check(self.lib.chibi_add_into(_ptr(acc), _ptr(x), _code(x), x.numel(), self._stream()),
                "add_into")
 
@@ -239,6 +249,7 @@ class CudaKernels:
         for t in (temperature, uniform):
             if t is not None and (t.dtype != torch.float32 or t.numel() != logits.shape[0]):
                 raise KernelError("sample: temperature / uniform must be float32 [R]")
+        self.launches += 1
         _check(self.lib.chibi_sample(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
                                      _ptr(temperature), _ptr(uniform), _ptr(out), self._stream()),
                "sample")
