@@ -28,7 +28,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
 
 # name of library -> sources (relative to this folder)
 LIBRARIES: Dict[str, List[str]] = {
-    "chibi_kernels": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling.cu"],
+    "chibi_kernels": ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_generic.cu",
+                      "sampling.cu"],
 }
 
 

@@ -25,6 +25,8 @@ _SIGNATURES = {
         "chibi_cast": [P, I, P, I, L, P],
         "chibi_add_into": [P, P, I, L, P],
         "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
+        "chibi_gemm_bf16_splits": [I, I, I],
+        "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
         "chibi_sample": [P, L, L, I, P, P, P, P],
     },

@@ -69,6 +69,15 @@ class CudaKernels:
         self.lib = library.load("chibi_kernels")
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0           # kernels of this package launched so far
+        self.use_tensor_cores = True
+        self.tensor_core_calls = 0  # matrix products that ran on the tcgen05 kernel
+        self._scratch_buf: Optional[torch.Tensor] = None
+
+    def _scratch(self, floats: int) -> torch.Tensor:
+        """32-bit scratch for kernels that split a reduction over several CTAs."""
+        if self._scratch_buf is None or self._scratch_buf.numel() < floats:
+            self._scratch_buf = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=self.device)
+        return self._scratch_buf
 
     # ------------------------------------------------------------------ helpers
     @staticmethod
@@ -81,7 +90,10 @@ class CudaKernels:
         if code:
             self.error.zero_()
             what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",
-                    3: "a page id outside the pool (attention)"}.get(code, f"code {code}")
+                    3: "a page id outside the pool (attention)",
+                    11: "a wait that ran out (matrix product: loader)",
+                    12: "a wait that ran out (matrix product: tensor-core issuer)",
+                    13: "a wait that ran out (matrix product: epilogue)"}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
     # ------------------------------------------------------------------ ops
@@ -129,6 +141,21 @@ class CudaKernels:
             _rows_contiguous(residual, "linear: residual")
             if residual.dtype != torch.float32 or residual.shape != (M, N):
                 raise KernelError("linear: residual must be float32 [M, N]")
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.use_tensor_cores:
+            splits = self.lib.chibi_gemm_bf16_splits(M, N, K)
+            if splits > 0:
+                scratch = self._scratch(splits * M * N) if splits > 1 else None
+                status = self.lib.chibi_gemm_bf16(
+                    _ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(residual), M, N, K, x.stride(0),
+                    w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                    _ptr(scratch), scratch.numel() if scratch is not None else 0, _ptr(self.error),
+                    self._stream())
+                if status == 0:
+                    self.launches += 2 if splits > 1 else 1
+                    self.tensor_core_calls += 1
+                    return
+                if status != -2:
+                    _check(status, "linear (tensor cores)")
         self.launches += 1
         _check(self.lib.chibi_gemm_simt(
             _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _ptr(residual), M, N, K,

@@ -270,3 +270,46 @@ def test_sample_temperature(k, vocab):
         hi = float(cdf[got[r]])
         # the chosen id's interval of the CDF holds u, up to 32-bit rounding of the sums
         assert lo - 1e-4 <= u <= hi + 1e-4, f"row {r}: id {got[r]} covers [{lo}, {hi}], u = {u}"
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64, 65, 128, 300])
+@pytest.mark.parametrize("N,K", [(203, 96), (256, 512), (1000, 1000), (384, 4096)])
+def test_linear_tensor_cores(k, ref, M, N, K):
+    """The tcgen05 kernel at sizes that are no multiple of its tiles: rows and
+    features past the edge, a K tail, K ranges split over CTAs for few rows, and
+    enough K blocks that the ring of stages wraps several times."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=30)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=31, scale=0.05)
+    before = k.tensor_core_calls
+    for odtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=odtype, device="cuda")
+        exp = torch.empty_like(out)
+        k.linear(x, w, out)
+        ref.linear(x, w, exp)
+        close(out, exp, odtype, f"tensor-core linear -> {odtype}", rel=2e-5 if odtype == torch.float32 else 8e-3)
+    res = rnd(M, N, seed=32)
+    exp_res = torch.empty_like(res)
+    ref.linear(x, w, exp_res, residual=res)
+    k.linear(x, w, res, residual=res)
+    close(res, exp_res, torch.float32, "tensor-core linear + residual in place", rel=2e-5)
+    assert k.tensor_core_calls == before + 3, "the tensor-core kernel refused an aligned shape"
+    k.check_error_word()
+    # a view with a row stride (the q part of a packed projection, a slice of the weights)
+    wide = rnd(M, K + 64, dtype=torch.bfloat16, seed=33)
+    out = torch.empty(M, 128, dtype=torch.float32, device="cuda")
+    exp = torch.empty_like(out)
+    k.linear(wide[:, 64:], w[:128], out)
+    ref.linear(wide[:, 64:], w[:128], exp)
+    close(out, exp, torch.float32, "tensor-core linear on views", rel=2e-5)
+
+
+def test_linear_falls_back_when_unaligned(k, ref):
+    x = rnd(5, 100, dtype=torch.bfloat16, seed=34)      # K = 100 is no multiple of 8
+    w = rnd(40, 100, dtype=torch.bfloat16, seed=35)
+    out = torch.empty(5, 40, dtype=torch.float32, device="cuda")
+    exp = torch.empty_like(out)
+    before = k.tensor_core_calls
+    k.linear(x, w, out)
+    ref.linear(x, w, exp)
+    assert k.tensor_core_calls == before
+    close(out, exp, torch.float32, "fallback linear", rel=2e-5)
