@@ -1,0 +1,596 @@
+// Causal grouped-query attention over the paged bfloat16 cache on the tensor
+// cores, for one head size per compiled library (-DCHIBI_HEAD_DIM=d, d a
+// multiple of 16 up to 256).  Two kernels:
+//
+// * decode: sequences that bring one token.  One CTA per (key range, kv head,
+//   sequence); the query heads that share the kv head are the rows of one
+//   16-row MMA tile, so every key and value is read once for the whole group.
+//   The four warps of a CTA take the 16-key tiles of the CTA's range in turn,
+//   each with its own cp.async ring, and merge their (max, sum, output) at the
+//   end.  With more than one key range per sequence the partial results go to
+//   scratch memory and a second kernel merges them.
+// * prefill: sequences that bring several tokens.  The rows of a 64-row tile are
+//   (token, head in group) pairs; K and V tiles of 64 keys are loaded once per
+//   CTA (double-buffered cp.async) and used by all four warps.
+//
+// Scores are (q . k) * scale in 32-bit; softmax state (running max and sum) and
+// the output accumulator are 32-bit; probabilities are rounded to bfloat16 for
+// the second product.  A row sees keys max(0, pos - window + 1) .. pos.
+#include "common.cuh"
+
+#ifndef CHIBI_HEAD_DIM
+#define CHIBI_HEAD_DIM 128
+#endif
+
+namespace chibi {
+
+constexpr int D = CHIBI_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int DPAD = D + 8;           // row stride in shared memory (16 bytes of padding)
+constexpr int KSTEPS = D / 16;        // k-steps of q . k
+constexpr int NTILES_D = D / 8;       // 8-wide output tiles of p . v
+constexpr int CHUNKS = D / 8;         // 16-byte chunks per row
+constexpr bool Q_IN_REGS = D <= 128;
+
+struct AttnParams {
+    const __nv_bfloat16* q;        // [T, nq * D]
+    const __nv_bfloat16* k_cache;  // [pages, nkv, page_size, D]
+    const __nv_bfloat16* v_cache;
+    __nv_bfloat16* out;            // [T, nq * D]
+    const int* block_table;
+    int table_stride;
+    const int* q_start;            // [S + 1]
+    const int* ctx_len;            // [S]
+    int nq, nkv, group;
+    int page_size, num_pages;
+    float scale_log2;              // scale * log2(e)
+    int window;
+    int splits;                    // decode: key ranges per sequence
+    float* scratch_o;              // decode: [S, nq, splits, D]
+    float* scratch_ml;             // decode: [S, nq, splits, 2]
+    int skip_single;               // prefill: leave one-token sequences to the decode kernel
+    int* error;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid)
+{
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p)
+{
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p)
+{
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Loads `rows` keys (or values) starting at position key0 of one (sequence, kv
+// head) into shared memory [rows][DPAD]; rows at or past key_end are zeroed.
+// `tid` / `nthreads` describe the group of threads that shares the work.
+__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* dst, const __nv_bfloat16* cache,
+                                             const int* table, int kv_head, int nkv, int page_size,
+                                             int num_pages, int key0, int key_end, int rows, int tid,
+                                             int nthreads, int* error)
+{
+    for (int c = tid; c < rows * CHUNKS; c += nthreads) {
+        const int row = c / CHUNKS, col = c - row * CHUNKS;
+        const int key = key0 + row;
+        bool valid = key < key_end;
+        const __nv_bfloat16* src = cache;
+        if (valid) {
+            const int page = table[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                valid = false;
+                if (error)
+                    atomicExch(error, 3);
+            } else {
+                src = cache + (((size_t)page * nkv + kv_head) * page_size + key % page_size) * D + col * 8;
+            }
+        }
+        cp_async16(dst + row * DPAD + col * 8, src, valid);
+    }
+}
+
+// Loads the A fragments of a 16-row query tile from shared memory.
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KSTEPS][4], const __nv_bfloat16* q_tile, int lane)
+{
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+        ldmatrix_x4(qf[ks], q_tile + (lane & 15) * DPAD + ks * 16 + (lane >> 4) * 8);
+}
+
+// s[nt] += q . k^T for `NT` 8-key tiles (NT even) of the K tile at k_tile.
+template <int NT>
+__device__ __forceinline__ void qk_product(float (&s)[NT][4], const uint32_t (&qf)[KSTEPS][4],
+                                           const __nv_bfloat16* q_tile, const __nv_bfloat16* k_tile, int lane)
+{
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t a[4];
+        if constexpr (Q_IN_REGS) {
+            a[0] = qf[ks][0]; a[1] = qf[ks][1]; a[2] = qf[ks][2]; a[3] = qf[ks][3];
+        } else {
+            ldmatrix_x4(a, q_tile + (lane & 15) * DPAD + ks * 16 + (lane >> 4) * 8);
+        }
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_tile + (np * 16 + (mi >> 1) * 8 + r8) * DPAD + ks * 16 + (mi & 1) * 8);
+            mma_bf16(s[2 * np], a, b[0], b[1]);
+            mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// o += p . v for `NT` 8-key tiles of probabilities (already in s, unnormalised).
+template <int NT>
+__device__ __forceinline__ void pv_product(float (&o)[NTILES_D][4], const float (&s)[NT][4],
+                                           const __nv_bfloat16* v_tile, int lane)
+{
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int kp = 0; kp < NT / 2; ++kp) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+        a[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+        a[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+        a[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+#pragma unroll
+        for (int nt = 0; nt < NTILES_D; nt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_tile + (kp * 16 + (mi & 1) * 8 + r8) * DPAD + (nt + (mi >> 1)) * 8);
+            mma_bf16(o[nt], a, b[0], b[1]);
+            mma_bf16(o[nt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Online softmax over NT 8-key tiles.  Scores come in as raw dot products; on
+// return s holds exp2(score * scale_log2 - m_new) (0 where masked), m/l are
+// updated and o is rescaled.  `pos_lo/hi`: positions of this thread's two rows;
+// a key is visible when first_lo/hi <= key <= pos_lo/hi and key < key_end.
+template <int NT>
+__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILES_D][4], float (&m)[2],
+                                             float (&l)[2], float scale_log2, int key0, int key_end,
+                                             int pos_lo, int pos_hi, int first_lo, int first_hi, int lane)
+{
+    const int tig = lane & 3;
+    float mx[2] = { -INFINITY, -INFINITY };
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = key0 + nt * 8 + tig * 2 + (e & 1);
+            const bool hi = e >= 2;
+            const bool vis = key < key_end && key <= (hi ? pos_hi : pos_lo) && key >= (hi ? first_hi : first_lo);
+            s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+            mx[hi] = fmaxf(mx[hi], s[nt][e]);
+        }
+    }
+    float corr[2], base[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        base[h] = m_new == -INFINITY ? 0.f : m_new;       // a row that has seen no key yet
+        corr[h] = exp2f(m[h] - base[h]);                  // 0 when m was -inf
+        m[h] = m_new;
+    }
+    float sum[2] = { 0.f, 0.f };
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[nt][e] - base[e >> 1]);
+            s[nt][e] = p;
+            sum[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+        l[h] = l[h] * corr[h] + sum[h];
+    }
+#pragma unroll
+    for (int nt = 0; nt < NTILES_D; ++nt) {
+        o[nt][0] *= corr[0];
+        o[nt][1] *= corr[0];
+        o[nt][2] *= corr[1];
+        o[nt][3] *= corr[1];
+    }
+}
+
+// ------------------------------------------------------------------ decode
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE = 16;                 // keys per warp tile
+constexpr int DEC_STAGES = D <= 128 ? 3 : 2;
+constexpr int DEC_STAGE_ELEMS = 2 * DEC_TILE * DPAD;   // K tile then V tile
+constexpr int DEC_Q_ELEMS = 16 * DPAD;
+constexpr size_t DEC_SMEM_PIPE = (size_t)(DEC_Q_ELEMS + DEC_WARPS * DEC_STAGES * DEC_STAGE_ELEMS) * 2;
+constexpr size_t DEC_SMEM_MERGE = (size_t)DEC_WARPS * (16 * (D + 1) + 32) * 4;
+constexpr size_t DEC_SMEM = DEC_SMEM_PIPE > DEC_SMEM_MERGE ? DEC_SMEM_PIPE : DEC_SMEM_MERGE;
+
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* pipe = q_tile + DEC_Q_ELEMS;
+
+    const int seq = blockIdx.z, split = blockIdx.x;
+    const int row_blocks = (p.group + 15) / 16;
+    const int kv_head = blockIdx.y / row_blocks, row_block = blockIdx.y - kv_head * row_blocks;
+    const int t = p.q_start[seq];
+    if (p.q_start[seq + 1] - t != 1)
+        return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = p.ctx_len[seq] - 1;
+    const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int key_end = pos + 1;
+    const int tiles_total = (key_end - first + DEC_TILE - 1) / DEC_TILE;
+    const int tiles_per_split = (tiles_total + p.splits - 1) / p.splits;
+    const int tile_begin = split * tiles_per_split;
+    int tile_end = tile_begin + tiles_per_split;
+    if (tile_end > tiles_total)
+        tile_end = tiles_total;
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    const int rows = min(16, p.group - row_block * 16);          // query heads in this tile
+    const int head0 = kv_head * p.group + row_block * 16;
+
+    // query rows -> shared memory (rows past the group are zero)
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += blockDim.x) {
+        const int row = c / CHUNKS, col = c - row * CHUNKS;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows)
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nq + head0 + row) * D + col * 8);
+        *reinterpret_cast<uint4*>(q_tile + row * DPAD + col * 8) = v;
+    }
+    __syncthreads();
+    uint32_t qf[KSTEPS][4];
+    if constexpr (Q_IN_REGS)
+        load_q_frags(qf, q_tile, lane);
+
+    float o[NTILES_D][4];
+#pragma unroll
+    for (int nt = 0; nt < NTILES_D; ++nt)
+        o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m[2] = { -INFINITY, -INFINITY }, l[2] = { 0.f, 0.f };
+
+    __nv_bfloat16* my_pipe = pipe + (size_t)warp * DEC_STAGES * DEC_STAGE_ELEMS;
+    const int my_first_tile = tile_begin + warp;
+    const int my_tiles = my_first_tile < tile_end ? (tile_end - my_first_tile + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    auto issue = [&](int i) {
+        if (i < my_tiles) {
+            const int key0 = first + (my_first_tile + i * DEC_WARPS) * DEC_TILE;
+            __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
+            load_kv_rows(st, p.k_cache, table, kv_head, p.nkv, p.page_size, p.num_pages, key0, key_end,
+                         DEC_TILE, lane, 32, p.error);
+            load_kv_rows(st + DEC_TILE * DPAD, p.v_cache, table, kv_head, p.nkv, p.page_size, p.num_pages,
+                         key0, key_end, DEC_TILE, lane, 32, p.error);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i)
+        issue(i);
+    for (int i = 0; i < my_tiles; ++i) {
+        issue(i + DEC_STAGES - 1);
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
+        const __nv_bfloat16* k_tile = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
+        const __nv_bfloat16* v_tile = k_tile + DEC_TILE * DPAD;
+        const int key0 = first + (my_first_tile + i * DEC_WARPS) * DEC_TILE;
+        float s[2][4] = { { 0.f, 0.f, 0.f, 0.f }, { 0.f, 0.f, 0.f, 0.f } };
+        qk_product<2>(s, qf, q_tile, k_tile, lane);
+        softmax_tile<2>(s, o, m, l, p.scale_log2, key0, key_end, pos, pos, first, first, lane);
+        pv_product<2>(o, s, v_tile, lane);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the warps: [warp][row][D + 1] outputs, then [warp][16] max and sum
+    float* mo = reinterpret_cast<float*>(smem_raw);
+    float* mm = mo + DEC_WARPS * 16 * (D + 1);
+    float* ml = mm + DEC_WARPS * 16;
+    {
+        const int g = lane >> 2, tig = lane & 3;
+        float* base = mo + (size_t)warp * 16 * (D + 1);
+#pragma unroll
+        for (int nt = 0; nt < NTILES_D; ++nt) {
+            base[g * (D + 1) + nt * 8 + tig * 2] = o[nt][0];
+            base[g * (D + 1) + nt * 8 + tig * 2 + 1] = o[nt][1];
+            base[(g + 8) * (D + 1) + nt * 8 + tig * 2] = o[nt][2];
+            base[(g + 8) * (D + 1) + nt * 8 + tig * 2 + 1] = o[nt][3];
+        }
+        if (tig == 0) {
+            mm[warp * 16 + g] = m[0];
+            mm[warp * 16 + g + 8] = m[1];
+            ml[warp * 16 + g] = l[0];
+            ml[warp * 16 + g + 8] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+        const int row = idx / D, c = idx - row * D;
+        float mmax = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w)
+            mmax = fmaxf(mmax, mm[w * 16 + row]);
+        const float base = mmax == -INFINITY ? 0.f : mmax;
+        float acc = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = exp2f(mm[w * 16 + row] - base);
+            acc += mo[((size_t)w * 16 + row) * (D + 1) + c] * f;
+            lsum += ml[w * 16 + row] * f;
+        }
+        const int head = head0 + row;
+        if (p.splits == 1) {
+            p.out[((size_t)t * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        } else {
+            const size_t slot = ((size_t)seq * p.nq + head) * p.splits + split;
+            p.scratch_o[slot * D + c] = acc;
+            if (c == 0) {
+                p.scratch_ml[slot * 2] = mmax;
+                p.scratch_ml[slot * 2 + 1] = lsum;
+            }
+        }
+    }
+}
+
+// Merges the key ranges of one (sequence, head): one block of D threads.
+__global__ void attn_decode_merge_kernel(const AttnParams p)
+{
+    const int seq = blockIdx.y, head = blockIdx.x, c = threadIdx.x;
+    const int t = p.q_start[seq];
+    if (p.q_start[seq + 1] - t != 1)
+        return;
+    const size_t slot0 = ((size_t)seq * p.nq + head) * p.splits;
+    float mmax = -INFINITY;
+    for (int s = 0; s < p.splits; ++s)
+        mmax = fmaxf(mmax, p.scratch_ml[(slot0 + s) * 2]);
+    const float base = mmax == -INFINITY ? 0.f : mmax;
+    float acc = 0.f, lsum = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+        const float f = exp2f(p.scratch_ml[(slot0 + s) * 2] - base);
+        acc += p.scratch_o[(slot0 + s) * D + c] * f;
+        lsum += p.scratch_ml[(slot0 + s) * 2 + 1] * f;
+    }
+    p.out[((size_t)t * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+}
+
+// ------------------------------------------------------------------ prefill
+constexpr int PRE_WARPS = 4;
+constexpr int PRE_ROWS = PRE_WARPS * 16;      // query rows per CTA
+constexpr int PRE_KEYS = D <= 128 ? 64 : 32;  // keys per tile
+constexpr int PRE_NT = PRE_KEYS / 8;
+constexpr size_t PRE_SMEM = (size_t)(PRE_ROWS * DPAD + 2 * 2 * PRE_KEYS * DPAD) * 2;
+
+__global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const AttnParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* kv = q_tile + PRE_ROWS * DPAD;        // [stage][K | V][PRE_KEYS][DPAD]
+
+    const int seq = blockIdx.z, kv_head = blockIdx.y;
+    const int t0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - t0;
+    if (q_len <= 0 || (q_len == 1 && p.skip_single))
+        return;
+    const int rows_total = q_len * p.group;
+    const int row0 = blockIdx.x * PRE_ROWS;
+    if (row0 >= rows_total)
+        return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int pos0 = p.ctx_len[seq] - q_len;
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+
+    // query rows -> shared memory; row r is (token r / group, head r % group)
+    for (int c = threadIdx.x; c < PRE_ROWS * CHUNKS; c += blockDim.x) {
+        const int row = c / CHUNKS, col = c - row * CHUNKS;
+        const int r = row0 + row;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_total) {
+            const int tok = r / p.group, h = r - tok * p.group;
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(t0 + tok) * p.nq + kv_head * p.group + h) * D + col * 8);
+        }
+        *reinterpret_cast<uint4*>(q_tile + row * DPAD + col * 8) = v;
+    }
+
+    const int last_row = min(rows_total, row0 + PRE_ROWS) - 1;
+    const int min_pos = pos0 + row0 / p.group, max_pos = pos0 + last_row / p.group;
+    const int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    const int key_end = max_pos + 1;
+    const int n_tiles = (key_end - key_begin + PRE_KEYS - 1) / PRE_KEYS;
+
+    // this thread's two rows
+    const int r_lo = row0 + warp * 16 + g, r_hi = r_lo + 8;
+    const int pos_lo = r_lo < rows_total ? pos0 + r_lo / p.group : -1;
+    const int pos_hi = r_hi < rows_total ? pos0 + r_hi / p.group : -1;
+    const int first_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+    const int first_hi = (p.window > 0 && pos_hi - p.window + 1 > 0) ? pos_hi - p.window + 1 : 0;
+    // rows of this warp: positions between warp_min_pos and warp_max_pos
+    const int w_first_row = row0 + warp * 16;
+    const int w_last_row = min(rows_total, w_first_row + 16) - 1;
+    const bool warp_active = w_first_row < rows_total;
+    const int warp_max_pos = warp_active ? pos0 + w_last_row / p.group : -1;
+    const int warp_min_first = !warp_active ? 0
+        : ((p.window > 0 && pos0 + w_first_row / p.group - p.window + 1 > 0)
+               ? pos0 + w_first_row / p.group - p.window + 1 : 0);
+
+    auto issue = [&](int i) {
+        if (i < n_tiles) {
+            __nv_bfloat16* st = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
+            const int key0 = key_begin + i * PRE_KEYS;
+            load_kv_rows(st, p.k_cache, table, kv_head, p.nkv, p.page_size, p.num_pages, key0, key_end,
+                         PRE_KEYS, threadIdx.x, blockDim.x, p.error);
+            load_kv_rows(st + PRE_KEYS * DPAD, p.v_cache, table, kv_head, p.nkv, p.page_size, p.num_pages,
+                         key0, key_end, PRE_KEYS, threadIdx.x, blockDim.x, p.error);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    __syncthreads();                       // q_tile is complete
+    uint32_t qf[KSTEPS][4];
+    const __nv_bfloat16* my_q = q_tile + warp * 16 * DPAD;
+    if constexpr (Q_IN_REGS)
+        load_q_frags(qf, my_q, lane);
+
+    float o[NTILES_D][4];
+#pragma unroll
+    for (int nt = 0; nt < NTILES_D; ++nt)
+        o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m[2] = { -INFINITY, -INFINITY }, l[2] = { 0.f, 0.f };
+
+    for (int i = 0; i < n_tiles; ++i) {
+        issue(i + 1);
+        cp_async_wait<1>();
+        __syncthreads();
+        const __nv_bfloat16* k_tile = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
+        const __nv_bfloat16* v_tile = k_tile + PRE_KEYS * DPAD;
+        const int key0 = key_begin + i * PRE_KEYS;
+        // skip tiles that no row of this warp can see
+        if (warp_active && key0 <= warp_max_pos && key0 + PRE_KEYS > warp_min_first) {
+            float s[PRE_NT][4];
+#pragma unroll
+            for (int nt = 0; nt < PRE_NT; ++nt)
+                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+            qk_product<PRE_NT>(s, qf, my_q, k_tile, lane);
+            softmax_tile<PRE_NT>(s, o, m, l, p.scale_log2, key0, key_end, pos_lo, pos_hi, first_lo, first_hi, lane);
+            pv_product<PRE_NT>(o, s, v_tile, lane);
+        }
+        __syncthreads();                   // the stage may be overwritten by the next issue
+    }
+    cp_async_wait<0>();
+
+    const int tig = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = h ? r_hi : r_lo;
+        if (r >= rows_total)
+            continue;
+        const int tok = r / p.group, head = kv_head * p.group + (r - tok * p.group);
+        const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+        __nv_bfloat16* dst = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
+#pragma unroll
+        for (int nt = 0; nt < NTILES_D; ++nt) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + tig * 2) = v;
+        }
+    }
+}
+
+} // namespace chibi
+
+using namespace chibi;
+
+CHIBI_API int chibi_attention_mma_head_dim() { return D; }
+
+// Scratch floats that a decode launch with these sizes needs.
+CHIBI_API long long chibi_attention_mma_scratch_floats(int seqs, int nq, int splits)
+{
+    return splits > 1 ? (long long)seqs * nq * splits * (D + 2) : 0;
+}
+
+// mode bit 0: run the decode kernel (one-token sequences); bit 1: run the
+// prefill kernel (the others; all sequences when bit 0 is clear).
+CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                  const int* block_table, int table_stride, const int* q_start,
+                                  const int* ctx_len, int seqs, int nq, int nkv, int page_size,
+                                  int num_pages, float scale, int window, int mode, int max_q_len,
+                                  int splits, float* scratch, long long scratch_floats, int* error,
+                                  cudaStream_t stream)
+{
+    if (seqs <= 0)
+        return CHIBI_OK;
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1)
+        return CHIBI_ERR_ARGUMENT;
+    AttnParams p {};
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.q_start = q_start;
+    p.ctx_len = ctx_len;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.group = nq / nkv;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.splits = splits;
+    p.error = error;
+    p.skip_single = (mode & 1) ? 1 : 0;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    if (mode & 1) {
+        if (splits > 1) {
+            const long long need = chibi_attention_mma_scratch_floats(seqs, nq, splits);
+            if (!scratch || scratch_floats < need)
+                return CHIBI_ERR_ARGUMENT;
+            p.scratch_o = scratch;
+            p.scratch_ml = scratch + (size_t)seqs * nq * splits * D;
+        }
+        const int row_blocks = (p.group + 15) / 16;
+        const dim3 grid(splits, nkv * row_blocks, seqs);
+        attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(p);
+        int st = launch_status();
+        if (st != CHIBI_OK)
+            return st;
+        if (splits > 1) {
+            attn_decode_merge_kernel<<<dim3(nq, seqs), D, 0, stream>>>(p);
+            st = launch_status();
+            if (st != CHIBI_OK)
+                return st;
+        }
+    }
+    if (mode & 2) {
+        const long long rows = (long long)max_q_len * p.group;
+        const dim3 grid((unsigned)((rows + PRE_ROWS - 1) / PRE_ROWS), nkv, seqs);
+        attn_prefill_kernel<<<grid, PRE_WARPS * 32, PRE_SMEM, stream>>>(p);
+        return launch_status();
+    }
+    return CHIBI_OK;
+}

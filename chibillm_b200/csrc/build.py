@@ -30,7 +30,11 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
 LIBRARIES: Dict[str, List[str]] = {
     "chibi_kernels": ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_generic.cu",
                       "sampling.cu"],
+    # one library per head size: built with -DCHIBI_HEAD_DIM=<d> when a model needs it
+    "chibi_attention_mma": ["attention_mma.cu"],
 }
+# head sizes whose attention library build_all() makes ahead of time
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
 
 class BuildError(RuntimeError):
@@ -150,8 +154,15 @@ def ensure_library(name: str, defines: Sequence[str] = (), verbose: bool = True)
     return target
 
 
+def attention_library(head_dim: int, verbose: bool = True) -> str:
+    return ensure_library("chibi_attention_mma", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
+
+
 def build_all(verbose: bool = True) -> List[str]:
-    return [ensure_library(name, verbose=verbose) for name in LIBRARIES]
+    out = [ensure_library("chibi_kernels", verbose=verbose)]
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        out += list(pool.map(lambda d: attention_library(d, verbose), PREBUILT_HEAD_DIMS))
+    return out
 
 
 if __name__ == "__main__":

@@ -77,6 +77,7 @@ class StepContext:
     ctx_lens: List[int] = field(default_factory=list)
     slot_list: List[int] = field(default_factory=list)
     max_q_len: int = 0
+    min_q_len: int = 0
     max_ctx_len: int = 0
 
     @property

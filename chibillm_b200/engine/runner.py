@@ -192,7 +192,8 @@ class ModelRunner:
             ctx_len=view("ctx_len", S), state_slots=view("state_slots", S),
             logit_rows=view("logit_rows", R), tables=tables, workspace=self.workspace,
             request_ids=[e.request_id for e in entries], q_lens=q_lens, ctx_lens=ctx_lens,
-            slot_list=slots, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+            slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens),
+            max_ctx_len=max(ctx_lens))
 
     # ------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:

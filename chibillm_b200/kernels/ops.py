@@ -72,6 +72,8 @@ class CudaKernels:
         self.use_tensor_cores = True
         self.tensor_core_calls = 0  # matrix products that ran on the tcgen05 kernel
         self._scratch_buf: Optional[torch.Tensor] = None
+        self._attention_libs = {}
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     def _scratch(self, floats: int) -> torch.Tensor:
         """32-bit scratch for kernels that split a reduction over several CTAs."""
@@ -210,8 +212,11 @@ class CudaKernels:
                   out: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
                   ctx_len: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                   nq: int, nkv: int, d: int, page_size: int, scale: float,
-                  window: Optional[int], max_q_len: int, max_ctx_len: int) -> None:
-        """Causal attention of every token over its sequence's pages."""
+                  window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0) -> None:
+        """Causal attention of every token over its sequence's pages.  bfloat16
+        with a head size that is a multiple of 16 runs on the tensor cores (one
+        library per head size, compiled when first needed); everything else, the
+        32-bit path included, runs the plain kernel."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions)
         T = q.shape[0]
         if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != q.shape:
@@ -222,12 +227,42 @@ class CudaKernels:
                 or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
             raise KernelError(f"attention: cache shape {tuple(k_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
+        if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+                and d % 16 == 0 and d <= 256):
+            self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
+                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len)
+            return
         self.launches += 1
         _check(self.lib.chibi_attention_generic(
             _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
             _ptr(seq_of_token), _ptr(positions), T, nq, nkv, d, page_size, k_cache.shape[0],
             float(scale), int(window or 0), _ptr(self.error), self._stream()), "attention")
+
+    def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
+                       page_size, scale, window, max_q_len, max_ctx_len, min_q_len) -> None:
+        lib = self._attention_libs.get(d)
+        if lib is None:
+            lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
+            if lib.chibi_attention_mma_head_dim() != d:
+                raise KernelError(f"the attention library for head size {d} was built for another size")
+            self._attention_libs[d] = lib
+        seqs = ctx_len.numel()
+        mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
+        splits, scratch = 1, None
+        if mode & 1:
+            # enough CTAs to fill the GPU twice, at least 64 keys per key range
+            ctas = seqs * nkv * ((nq // nkv + 15) // 16)
+            splits = max(1, min(-(-2 * self.sm_count // ctas), -(-max_ctx_len // 64), 64))
+            if splits > 1:
+                scratch = self._scratch(seqs * nq * splits * (d + 2))
+        status = lib.chibi_attention_mma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+            _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
+            int(window or 0), mode, int(max_q_len), splits, _ptr(scratch),
+            scratch.numel() if scratch is not None else 0, _ptr(self.error), self._stream())
+        self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
+        _check(status, "attention (tensor cores)")
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         _need_cuda(gate_up, out)

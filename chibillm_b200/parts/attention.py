@@ -100,7 +100,7 @@ class PagedAttention(Mixer):
         att = ctx.workspace.get("attn.out", (T, qw), rt.dtype)
         k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
-                    s.window, ctx.max_q_len, ctx.max_ctx_len)
+                    s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len)
         k.linear(att, self.o_proj, residual, residual=residual)
 
 

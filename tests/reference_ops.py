@@ -82,7 +82,7 @@ class ReferenceKernels:
         v_cache[pages, :, slots, :] = v.to(v_cache.dtype)
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
-                  positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len):
+                  positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv

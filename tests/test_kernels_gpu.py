@@ -152,11 +152,17 @@ def test_qk_norm_rope_append(k, ref, dtype, nq, nkv, d, rot, norms):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,window", [(4, 2, 16, None), (6, 3, 48, 24), (5, 1, 128, None),
-                                             (8, 8, 64, 7), (10, 2, 32, 33)])
-def test_attention_against_plain(k, ref, dtype, nq, nkv, d, window):
-    page, pages = 8, 64
+                                             (8, 8, 64, 7), (10, 2, 32, 33), (20, 1, 64, None),
+                                             (4, 1, 256, 100)])
+@pytest.mark.parametrize("seq_ctx,q_lens", [
     # whole prompts, single decoded tokens at page edges, a portion in the middle
-    seq_ctx, q_lens = [33, 64, 65, 16, 150], [33, 1, 1, 16, 21]
+    ([33, 64, 65, 16, 150], [33, 1, 1, 16, 21]),
+    # decoding only, contexts of very different lengths
+    ([1, 17, 128, 129, 400], [1, 1, 1, 1, 1]),
+    # portions only, one of them longer than a tile of query rows
+    ([200, 90], [130, 2])])
+def test_attention_against_plain(k, ref, dtype, nq, nkv, d, window, seq_ctx, q_lens):
+    page, pages = 8, 128
     table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, q_lens, page, pages, seed=11)
     T = sum(q_lens)
     q = rnd(T, nq * d, dtype=dtype, seed=12)
@@ -164,15 +170,15 @@ def test_attention_against_plain(k, ref, dtype, nq, nkv, d, window):
     kc = torch.full((pages, nkv, page, d), float("nan"), dtype=dtype, device="cuda")
     vc = torch.full((pages, nkv, page, d), float("nan"), dtype=dtype, device="cuda")
     for s, c in enumerate(seq_ctx):
-        for p in range(c):
-            pg = int(table[s, p // page])
-            kc[pg, :, p % page, :] = rnd(nkv, d, dtype=dtype, seed=1000 + 17 * s + p)
-            vc[pg, :, p % page, :] = rnd(nkv, d, dtype=dtype, seed=5000 + 17 * s + p)
+        idx = torch.arange(c, device="cuda")
+        pg = table[s, idx // page].long()
+        kc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=dtype, seed=1000 + s)
+        vc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=dtype, seed=5000 + s)
     out = torch.full((T, nq * d), float("nan"), dtype=dtype, device="cuda")
     exp = torch.empty_like(out)
     scale = 1.0 / math.sqrt(d)
     args = (table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, scale, window,
-            max(q_lens), max(seq_ctx))
+            max(q_lens), max(seq_ctx), min(q_lens))
     k.attention(q, kc, vc, out, *args)
     ref.attention(q, kc, vc, exp, *args)
     k.check_error_word()
