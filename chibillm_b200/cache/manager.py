@@ -110,6 +110,7 @@ class GroupLayout:
     page_size: int
     num_pages: int
     num_entries: int            # run steps that own a cache in this group
+    max_blocks: int = 0         # logical blocks a request can reach (width of the device table)
 
 
 @dataclass
@@ -146,6 +147,18 @@ class CacheManager:
         self.slots = SlotPool(max_requests)
         self.max_requests = max_requests
         self.requests: Dict[Hashable, RequestCache] = {}
+        # per group: (table row, logical block, page or -1) changes since the last drain, in
+        # order; the row of a request is its state slot
+        self._updates: Dict[str, List[Tuple[int, int, int]]] = {g.name: [] for g in groups}
+
+    def drain_updates(self, group: str) -> List[Tuple[int, int, int]]:
+        """Block-table changes since the last call, for the mirror on the device:
+        at most one per (row, block), the latest (they are applied in parallel)."""
+        last: Dict[Tuple[int, int], int] = {}
+        for row, index, page in self._updates[group]:
+            last[(row, index)] = page
+        self._updates[group] = []
+        return [(row, index, page) for (row, index), page in last.items()]
 
     # ---- queries
     def has(self, request_id: Hashable) -> bool:
@@ -196,7 +209,14 @@ class CacheManager:
             wanted[name] = need
         for name, need in wanted.items():
             if need > 0:
-                rc.tables[name].extend(self.pools[name].take(need))
+                table = rc.tables[name]
+                limit = self.groups[name].max_blocks
+                if limit and len(table) + need > limit:
+                    raise CacheError("invalid_reservation",
+                                     f"group '{name}': {len(table) + need} blocks exceed the table's {limit}")
+                for page in self.pools[name].take(need):
+                    self._updates[name].append((rc.state_slot, len(table), page))
+                    table.append(page)
         rc.reserved = max(rc.reserved, tokens)
 
     def commit(self, request_id: Hashable, new_length: int) -> None:
@@ -216,6 +236,8 @@ class CacheManager:
             if gone:
                 self.pools[name].give(gone)
                 for i in range(dead):
+                    if table[i] >= 0:
+                        self._updates[name].append((rc.state_slot, i, -1))
                     table[i] = -1
 
     def release(self, request_id: Hashable) -> None:

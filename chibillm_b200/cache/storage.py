@@ -47,9 +47,11 @@ def group_name(need: PagedKVNeed) -> str:
 
 
 def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_size: int,
-               pool_tokens: int) -> CachePlan:
+               pool_tokens: int, max_positions: int = 0) -> CachePlan:
     """Sort the run steps' needs into groups.  ``pool_tokens`` is how many
-    tokens every group's pool can hold; it is rounded up to whole pages."""
+    tokens every group's pool can hold; it is rounded up to whole pages.
+    ``max_positions`` (the model's limit; default: the pool's size) bounds the
+    logical blocks of one request, which is the width of the device tables."""
     if page_size <= 0 or pool_tokens <= 0:
         raise CacheError("invalid_configuration", "page_size and pool_tokens must be positive")
     num_pages = (pool_tokens + page_size - 1) // page_size
@@ -81,8 +83,9 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
             steps.append(None)
         else:
             raise CacheError("invalid_configuration", f"run step {i}: unknown cache need {need!r}")
+    max_blocks = (max(max_positions, 1) + page_size - 1) // page_size if max_positions else num_pages
     groups = tuple(GroupLayout(name, n.num_kv_heads, n.head_dim, n.window, page_size, num_pages,
-                               entries[name]) for name, n in needs_of.items())
+                               entries[name], max_blocks) for name, n in needs_of.items())
     return CachePlan(groups, tuple(steps))
 
 
@@ -97,6 +100,10 @@ class CacheStorage:
             shape = (g.num_entries, g.num_pages, g.num_kv_heads, g.page_size, g.head_dim)
             self.keys[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
             self.values[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+        # the block tables' mirror on the device: row = a request's state slot
+        self.tables: Dict[str, torch.Tensor] = {
+            g.name: torch.full((num_slots, max(g.max_blocks, 1)), -1, dtype=torch.int32, device=runtime.device)
+            for g in plan.groups}
         self.views: List[object] = []
         self._state_arrays: List[torch.Tensor] = []
         page_sizes = {g.name: g.page_size for g in plan.groups}

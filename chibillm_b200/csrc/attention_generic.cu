@@ -24,7 +24,8 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                          const TC* __restrict__ v_cache, TQ* __restrict__ out,
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ q_start, const int* __restrict__ ctx_len,
-                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                         const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
+                         const int* __restrict__ positions,
                          long long tokens, int nq, int nkv, int d, int page_size, int num_pages,
                          float scale, int window, int* __restrict__ error)
 {
@@ -45,7 +46,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
     __syncwarp();
 
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int* table = block_table + (size_t)seq * table_stride;
+    const int* table = block_table + (size_t)(seq_rows ? seq_rows[seq] : seq) * table_stride;
     constexpr int SLOTS = MAX_D / 32;
     float acc[SLOTS];
 #pragma unroll
@@ -113,7 +114,8 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
                                       const void* v_cache, int cache_type, void* out,
                                       const int* block_table, int table_stride,
                                       const int* q_start, const int* ctx_len,
-                                      const int* seq_of_token, const int* positions,
+                                      const int* seq_of_token, const int* seq_rows,
+                                      const int* positions,
                                       long long tokens, int nq, int nkv, int d, int page_size,
                                       int num_pages, float scale, int window, int* error,
                                       cudaStream_t stream)
@@ -131,7 +133,7 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
     CHIBI_DISPATCH_TYPE(q_type, TQ, CHIBI_DISPATCH_TYPE(cache_type, TC, {
         attention_generic_kernel<TQ, TC><<<(unsigned)blocks, warps * 32, smem, stream>>>(
             (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
-            table_stride, q_start, ctx_len, seq_of_token, positions, tokens, nq, nkv, d, page_size,
+            table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, page_size,
             num_pages, scale, window, error);
     }));
     return launch_status();

@@ -39,6 +39,7 @@ struct AttnParams {
     __nv_bfloat16* out;            // [T, nq * D]
     const int* block_table;
     int table_stride;
+    const int* seq_rows;           // [S] row of the block table per sequence, or null (row = s)
     const int* q_start;            // [S + 1]
     const int* ctx_len;            // [S]
     int nq, nkv, group;
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     int tile_end = tile_begin + tiles_per_split;
     if (tile_end > tiles_total)
         tile_end = tiles_total;
-    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    const int* table = p.block_table + (size_t)(p.seq_rows ? p.seq_rows[seq] : seq) * p.table_stride;
     const int rows = min(16, p.group - row_block * 16);          // query heads in this tile
     const int head0 = kv_head * p.group + row_block * 16;
 
@@ -415,7 +416,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const Attn
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2;
     const int pos0 = p.ctx_len[seq] - q_len;
-    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    const int* table = p.block_table + (size_t)(p.seq_rows ? p.seq_rows[seq] : seq) * p.table_stride;
 
     // query rows -> shared memory; row r is (token r / group, head r % group)
     for (int c = threadIdx.x; c < PRE_ROWS * CHUNKS; c += blockDim.x) {
@@ -527,8 +528,8 @@ CHIBI_API long long chibi_attention_mma_scratch_floats(int seqs, int nq, int spl
 // mode bit 0: run the decode kernel (one-token sequences); bit 1: run the
 // prefill kernel (the others; all sequences when bit 0 is clear).
 CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                  const int* block_table, int table_stride, const int* q_start,
-                                  const int* ctx_len, int seqs, int nq, int nkv, int page_size,
+                                  const int* block_table, int table_stride, const int* seq_rows,
+                                  const int* q_start, const int* ctx_len, int seqs, int nq, int nkv, int page_size,
                                   int num_pages, float scale, int window, int mode, int max_q_len,
                                   int splits, float* scratch, long long scratch_floats, int* error,
                                   cudaStream_t stream)
@@ -544,6 +545,7 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     p.out = static_cast<__nv_bfloat16*>(out);
     p.block_table = block_table;
     p.table_stride = table_stride;
+    p.seq_rows = seq_rows;
     p.q_start = q_start;
     p.ctx_len = ctx_len;
     p.nq = nq;

@@ -56,7 +56,7 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ 
 // normalised over their d features (when a norm weight is given), rotated
 // (split-half pairs (j, j + rot/2), angle = float(pos) * inv_freq[j]) and
 // written to q_out or to the key cache; value heads are copied to the value
-// cache.  Cache layout: [page][kv_head][slot][d]; page = block_table[seq][pos /
+// cache.  Cache layout: [page][kv_head][slot][d]; page = block_table[row][pos /
 // page_size], slot = pos % page_size.
 template <typename TX, typename TW, typename TC>
 __global__ void qk_norm_rope_append_kernel(
@@ -64,7 +64,8 @@ __global__ void qk_norm_rope_append_kernel(
     TC* __restrict__ k_cache, TC* __restrict__ v_cache, const TW* __restrict__ q_norm_w,
     const TW* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ block_table, int table_stride, int nq, int nkv, int d, int rot,
+    const int* __restrict__ seq_rows, const int* __restrict__ block_table, int table_stride, int nq,
+    int nkv, int d, int rot,
     int page_size, int num_pages, float eps, float norm_offset, int append,
     int* __restrict__ error)
 {
@@ -80,7 +81,8 @@ __global__ void qk_norm_rope_append_kernel(
     long long cache_base = -1;
     if (append) {
         const int seq = seq_of_token[t];
-        const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        const int table_row = seq_rows ? seq_rows[seq] : seq;
+        const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
         if (page < 0 || page >= num_pages) {
             if (threadIdx.x == 0 && error)
                 atomicExch(error, 2);
@@ -194,6 +196,28 @@ __global__ void add_into_kernel(float* __restrict__ acc, const TX* __restrict__ 
         acc[i] += to_f32(x[i]);
 }
 
+// updates = [count, (row, index, page) * count]: table[row][index] = page.
+__global__ void apply_table_updates_kernel(int* __restrict__ table, int table_stride, int table_rows,
+                                           const int* __restrict__ updates, int capacity,
+                                           int* __restrict__ error)
+{
+    int n = updates[0];
+    if (n > capacity) {
+        n = capacity;
+        if (threadIdx.x == 0 && blockIdx.x == 0 && error)
+            atomicExch(error, 4);
+    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int row = updates[1 + 3 * i], index = updates[2 + 3 * i], page = updates[3 + 3 * i];
+        if (row < 0 || row >= table_rows || index < 0 || index >= table_stride) {
+            if (error)
+                atomicExch(error, 4);
+            continue;
+        }
+        table[(size_t)row * table_stride + index] = page;
+    }
+}
+
 static int grid_for(long long total, int block)
 {
     long long g = (total + block - 1) / block;
@@ -241,7 +265,8 @@ CHIBI_API int chibi_rmsnorm(const void* x, int x_type, const void* w, int w_type
 CHIBI_API int chibi_qk_norm_rope_append(
     const void* qkv, int x_type, long long qkv_stride, void* q_out, void* k_cache, void* v_cache,
     int cache_type, const void* q_norm_w, const void* k_norm_w, int w_type, const float* inv_freq,
-    const int* positions, const int* seq_of_token, const int* block_table, int table_stride,
+    const int* positions, const int* seq_of_token, const int* seq_rows, const int* block_table,
+    int table_stride,
     long long tokens, int nq, int nkv, int d, int rot, int page_size, int num_pages, float eps,
     float norm_offset, int append, int* error, cudaStream_t stream)
 {
@@ -255,7 +280,7 @@ CHIBI_API int chibi_qk_norm_rope_append(
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
         qk_norm_rope_append_kernel<TX, TW, TC><<<(unsigned)tokens, warps * 32, smem, stream>>>(
             (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
-            (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token,
+            (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
             block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
             append, error);
     })));
@@ -306,5 +331,17 @@ CHIBI_API int chibi_add_into(float* acc, const void* x, int x_type, long long to
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         add_into_kernel<TX><<<grid_for(total, 256), 256, 0, stream>>>(acc, (const TX*)x, total);
     });
+    return launch_status();
+}
+
+CHIBI_API int chibi_apply_table_updates(int* table, int table_stride, int table_rows,
+                                        const int* updates, int capacity, int* error,
+                                        cudaStream_t stream)
+{
+    if (capacity <= 0)
+        return CHIBI_OK;
+    const int blocks = capacity > 4096 ? 16 : 1;
+    apply_table_updates_kernel<<<blocks, 256, 0, stream>>>(table, table_stride, table_rows, updates,
+                                                           capacity, error);
     return launch_status();
 }

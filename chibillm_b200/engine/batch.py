@@ -37,6 +37,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.generation = 0        # counts allocations: a captured graph is valid for one value
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -50,6 +51,7 @@ class Workspace:
                 grow = max(grow, 2 * buf.numel()) if count < (1 << 28) else count
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._buffers[key] = buf
+            self.generation += 1
         return buf[:count].view(*shape)
 
     def bytes(self) -> int:
@@ -67,9 +69,9 @@ class StepContext:
     seq_of_token: torch.Tensor           # int32 [T]
     q_start: torch.Tensor                # int32 [S + 1]
     ctx_len: torch.Tensor                # int32 [S]  (tokens held after this step)
-    state_slots: torch.Tensor            # int32 [S]
+    state_slots: torch.Tensor            # int32 [S]: each sequence's state slot
     logit_rows: torch.Tensor             # int32 [R]
-    tables: Dict[str, torch.Tensor]      # group -> int32 [S, blocks]
+    tables: Dict[str, torch.Tensor]      # group -> int32 [slots, blocks]; a sequence's row is its slot
     workspace: Workspace
     # host copies, for sizing launches and for mixers that walk sequences
     request_ids: List[Hashable] = field(default_factory=list)
@@ -79,6 +81,11 @@ class StepContext:
     max_q_len: int = 0
     min_q_len: int = 0
     max_ctx_len: int = 0
+
+    @property
+    def seq_rows(self) -> torch.Tensor:
+        """Row of the block tables per sequence (its state slot)."""
+        return self.state_slots
 
     @property
     def decode_only(self) -> bool:

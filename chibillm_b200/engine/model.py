@@ -59,6 +59,19 @@ class DecoderModel:
     def cache_sources(self) -> List[Optional[int]]:
         return [step.cache_of for step in self.spec.run_order]
 
+    def launch_key(self, ctx: StepContext):
+        """What the parts decide on the host from this batch's values (beyond its
+        numbers of tokens, sequences and wanted rows), as a hashable; None if any
+        part cannot promise that a captured step stays valid."""
+        keys = []
+        for step in self.spec.run_order:
+            block = self.blocks[step.layer]
+            key = block.launch_key(ctx)
+            if key is None:
+                return None
+            keys.append(key)
+        return tuple(keys)
+
     # ---- run
     def forward(self, ctx: StepContext, cache_views: Sequence[object]) -> Optional[torch.Tensor]:
         """Run the tokens of ``ctx``; returns 32-bit logits [R, vocab] of the

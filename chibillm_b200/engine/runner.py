@@ -60,7 +60,8 @@ class ModelRunner:
         self.spec = model.spec
         self.runtime = runtime
         self.page_size = page_size
-        plan = plan_cache(model.cache_needs(), model.cache_sources(), page_size, pool_tokens)
+        plan = plan_cache(model.cache_needs(), model.cache_sources(), page_size, pool_tokens,
+                          model.spec.max_positions)
         self.plan = plan
         self.cache = CacheManager(plan.groups, max_requests)
         self.storage = CacheStorage(plan, runtime, max_requests)
@@ -70,6 +71,12 @@ class ModelRunner:
         self._meta_copied = None      # event: the last copy out of the pinned array is done
         self.last_meta_bytes = 0      # bytes the last step sent to the device
         self.steps_run = 0
+        self._meta_epoch = 0
+        self.use_graphs = runtime.device.type == "cuda"
+        self._graphs: Dict[tuple, tuple] = {}
+        self._graphs_warm = set()
+        self._graphs_epoch = None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -122,30 +129,36 @@ class ModelRunner:
         return self.cache.length(request_id)
 
     # ------------------------------------------------------------ metadata
+    META_CAPACITY = 1 << 20      # int32 values; allocated once so that its address never changes
+
     def _meta_buffers(self, count: int):
         if self._meta_host is None or self._meta_host.numel() < count:
-            cap = max(4096, 2 * count)
+            cap = max(self.META_CAPACITY, 2 * count)
             pin = self.runtime.device.type == "cuda"
             self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.runtime.device)
+            self._meta_epoch += 1
         return self._meta_host, self._meta_dev
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], fixed_update_capacity: bool):
+        """Flatten the entries, send the packed metadata to the device and bring
+        the device's block tables up to date.  With ``fixed_update_capacity`` the
+        layout of the packed array depends only on the numbers of tokens,
+        sequences and wanted rows (what a captured graph needs); returns None if
+        the table updates of this step do not fit that layout."""
         lengths = {e.request_id: self.cache.length(e.request_id) for e in entries}
         (tokens, positions, seq_of_token, q_start, q_lens, ctx_lens, logit_rows) = flatten_entries(
             entries, lengths, self.spec.vocab_size, self.spec.max_positions)
         T, S, R = len(tokens), len(entries), len(logit_rows)
         slots = [self.cache.get(e.request_id).state_slot for e in entries]
-        group_tables: Dict[str, List[List[int]]] = {}
-        widths: Dict[str, int] = {}
-        for g in self.plan.groups:
-            rows = [self.cache.get(e.request_id).tables[g.name] for e in entries]
-            widths[g.name] = max(1, max(len(r) for r in rows))
-            group_tables[g.name] = rows
+        updates = {g.name: self.cache.drain_updates(g.name) for g in self.plan.groups}
+        if fixed_update_capacity and any(len(u) > 2 * S for u in updates.values()):
+            fixed_update_capacity = False
+        caps = {name: (2 * S if fixed_update_capacity else len(u)) for name, u in updates.items()}
         # layout of the packed array, every segment on a 16-byte boundary
         segments = [("tokens", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1),
                     ("ctx_len", S), ("state_slots", S), ("logit_rows", R)]
-        segments += [("table:" + name, S * w) for name, w in widths.items()]
+        segments += [("updates:" + name, 1 + 3 * cap) for name, cap in caps.items()]
         offsets, cursor = {}, 0
         for name, n in segments:
             offsets[name] = cursor
@@ -164,13 +177,8 @@ class ModelRunner:
         put("ctx_len", ctx_lens)
         put("state_slots", slots)
         put("logit_rows", logit_rows)
-        for name, rows in group_tables.items():
-            w = widths[name]
-            o = offsets["table:" + name]
-            for s, row in enumerate(rows):
-                flat[o + s * w:o + s * w + len(row)] = row
-                for j in range(len(row), w):
-                    flat[o + s * w + j] = -1
+        for name, ups in updates.items():
+            put("updates:" + name, [len(ups)] + [v for triple in ups for v in triple])
         if self._meta_copied is not None:
             self._meta_copied.synchronize()     # the pinned array may still be read by the last copy
         host[:cursor] = torch.tensor(flat, dtype=torch.int32)
@@ -185,21 +193,79 @@ class ModelRunner:
             o = offsets[name]
             return dev[o:o + n]
 
-        tables = {name: view("table:" + name, S * w).view(S, w) for name, w in widths.items()}
-        return StepContext(
+        ctx = StepContext(
             num_tokens=T, num_seqs=S, tokens=view("tokens", T), positions=view("positions", T),
             seq_of_token=view("seq_of_token", T), q_start=view("q_start", S + 1),
             ctx_len=view("ctx_len", S), state_slots=view("state_slots", S),
-            logit_rows=view("logit_rows", R), tables=tables, workspace=self.workspace,
+            logit_rows=view("logit_rows", R), tables=self.storage.tables, workspace=self.workspace,
             request_ids=[e.request_id for e in entries], q_lens=q_lens, ctx_lens=ctx_lens,
             slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens),
             max_ctx_len=max(ctx_lens))
+        update_views = {name: (view("updates:" + name, 1 + 3 * cap), cap) for name, cap in caps.items()}
+        return ctx, update_views, fixed_update_capacity
+
+    def _run_model(self, ctx: StepContext, update_views) -> Optional[torch.Tensor]:
+        k = self.runtime.kernels
+        for name, (view, cap) in update_views.items():
+            if cap > 0:
+                k.apply_table_updates(self.storage.tables[name], view, cap)
+        return self.model.forward(ctx, self.storage.views)
+
+    # ------------------------------------------------------------ graphs
+    def _graph_epoch(self):
+        k = self.runtime.kernels
+        return (self.workspace.generation, getattr(k, "scratch_generation", 0), self._meta_epoch)
+
+    def _graph_key(self, ctx: StepContext):
+        """What a captured decode step depends on besides the data in the packed
+        array, or None if this step cannot be replayed from a graph."""
+        if not self.use_graphs or ctx.max_q_len != 1 or not getattr(self.runtime.kernels, "supports_graphs", False):
+            return None
+        launch = self.model.launch_key(ctx)
+        if launch is None:
+            return None
+        return (ctx.num_seqs, ctx.logit_rows.numel(), launch)
+
+    def _step_with_graph(self, key, ctx, update_views) -> Optional[torch.Tensor]:
+        epoch = self._graph_epoch()
+        if epoch != self._graphs_epoch:
+            self._graphs.clear()
+            self._graphs_warm.clear()
+            self._graphs_epoch = epoch
+        entry = self._graphs.get(key)
+        k = self.runtime.kernels
+        if entry is None:
+            if key not in self._graphs_warm:
+                # first time: run as usual, so that every array and library exists
+                self._graphs_warm.add(key)
+                logits = self._run_model(ctx, update_views)
+                if self._graph_epoch() != epoch:        # something was allocated: start over later
+                    self._graphs_warm.discard(key)
+                return logits
+            graph = torch.cuda.CUDAGraph()
+            before = k.launches
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                logits = self._run_model(ctx, update_views)
+            entry = (graph, logits, k.launches - before)
+            k.launches = before
+            self._graphs[key] = entry
+        graph, logits, launches = entry
+        graph.replay()
+        k.launches += launches
+        self.graph_replays += 1
+        return logits
 
     # ------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device in
         the order of the entries and of their ``want`` (None if nothing is
-        wanted).  The array is reused by the next step."""
+        wanted).  The array is reused by the next step.
+
+        A step in which every request brings one token is captured into a CUDA
+        graph the second time its shape is seen and replayed from then on; what
+        changes between replays (tokens, positions, lengths, table updates,
+        wanted rows) travels in the packed metadata array."""
         if not entries:
             raise BatchError("a step needs at least one entry")
         if len(entries) > self.cache.max_requests:
@@ -210,8 +276,13 @@ class ModelRunner:
                 self.admit(e.request_id)
         for e in entries:
             self.cache.reserve(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
-        ctx = self._build_context(entries)
-        logits = self.model.forward(ctx, self.storage.views)
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        ctx, update_views, fixed = self._build_context(entries, decode_only and self.use_graphs)
+        key = self._graph_key(ctx) if fixed else None
+        if key is not None:
+            logits = self._step_with_graph(key, ctx, update_views)
+        else:
+            logits = self._run_model(ctx, update_views)
         for e, new_len in zip(entries, ctx.ctx_lens):
             self.cache.commit(e.request_id, new_len)
         self.steps_run += 1

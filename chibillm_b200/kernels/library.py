@@ -18,8 +18,9 @@ _SIGNATURES = {
     "chibi_kernels": {
         "chibi_embed": [P, P, I, P, I, L, I, I, P, P],
         "chibi_rmsnorm": [P, I, P, I, P, I, L, I, L, L, F, F, P],
-        "chibi_qk_norm_rope_append": [P, I, L, P, P, P, I, P, P, I, P, P, P, P, I, L, I, I, I, I, I,
+        "chibi_qk_norm_rope_append": [P, I, L, P, P, P, I, P, P, I, P, P, P, P, P, I, L, I, I, I, I, I,
                                       I, F, F, I, P, P],
+        "chibi_apply_table_updates": [P, I, I, P, I, P, P],
         "chibi_swiglu": [P, I, P, I, L, I, P],
         "chibi_gather_rows": [P, I, P, P, I, L, I, L, P],
         "chibi_cast": [P, I, P, I, L, P],
@@ -27,12 +28,12 @@ _SIGNATURES = {
         "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
         "chibi_gemm_bf16_splits": [I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
-        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
+        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
         "chibi_sample": [P, L, L, I, P, P, P, P],
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
-        "chibi_attention_mma": [P, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, I, P, L, P, P],
+        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, L, P, P],
     },
 }
 

@@ -72,6 +72,8 @@ class CudaKernels:
         self.use_tensor_cores = True
         self.tensor_core_calls = 0  # matrix products that ran on the tcgen05 kernel
         self._scratch_buf: Optional[torch.Tensor] = None
+        self.scratch_generation = 0
+        self.supports_graphs = True     # every op is a plain launch on the current stream
         self._attention_libs = {}
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
@@ -79,6 +81,7 @@ class CudaKernels:
         """32-bit scratch for kernels that split a reduction over several CTAs."""
         if self._scratch_buf is None or self._scratch_buf.numel() < floats:
             self._scratch_buf = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=self.device)
+            self.scratch_generation += 1
         return self._scratch_buf
 
     # ------------------------------------------------------------------ helpers
@@ -93,6 +96,7 @@ class CudaKernels:
             self.error.zero_()
             what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",
                     3: "a page id outside the pool (attention)",
+                    4: "a block-table update outside the table",
                     11: "a wait that ran out (matrix product: loader)",
                     12: "a wait that ran out (matrix product: tensor-core issuer)",
                     13: "a wait that ran out (matrix product: epilogue)"}.get(code, f"code {code}")
@@ -170,13 +174,15 @@ class CudaKernels:
                             inv_freq: Optional[torch.Tensor], rotary_dim: int, eps: float,
                             norm_offset: float, positions: torch.Tensor,
                             seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
-                            nq: int, nkv: int, d: int, page_size: int) -> None:
+                            nq: int, nkv: int, d: int, page_size: int,
+                            seq_rows: Optional[torch.Tensor] = None) -> None:
         """Per head: RMSNorm (when a weight is given), split-half rotation of the
         first ``rotary_dim`` features, then q -> q_out, k and v -> cache pages.
         qkv: [T, (nq + 2 nkv) d], or [T, nq d] when no cache is given (the layer
-        then reads another layer's cache).  Cache: [pages, nkv, page_size, d]."""
+        then reads another layer's cache).  Cache: [pages, nkv, page_size, d].
+        Sequence s uses row ``seq_rows[s]`` of the block table (row s when None)."""
         _need_cuda(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, inv_freq, positions,
-                   seq_of_token, block_table)
+                   seq_of_token, block_table, seq_rows)
         _rows_contiguous(qkv, "qk_norm_rope_append: qkv")
         T = qkv.shape[0]
         append = k_cache is not None
@@ -204,7 +210,8 @@ class CudaKernels:
         _check(self.lib.chibi_qk_norm_rope_append(
             _ptr(qkv), _code(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
             _code(k_cache) if append else F32, _ptr(q_norm_w), _ptr(k_norm_w), w_type,
-            _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token), _ptr(block_table), table_stride, T,
+            _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token), _ptr(seq_rows), _ptr(block_table),
+            table_stride, T,
             nq, nkv, d, int(rotary_dim), page_size, num_pages, float(eps), float(norm_offset),
             1 if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append")
 
@@ -212,12 +219,14 @@ class CudaKernels:
                   out: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
                   ctx_len: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                   nq: int, nkv: int, d: int, page_size: int, scale: float,
-                  window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0) -> None:
+                  window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0,
+                  seq_rows: Optional[torch.Tensor] = None) -> None:
         """Causal attention of every token over its sequence's pages.  bfloat16
         with a head size that is a multiple of 16 runs on the tensor cores (one
         library per head size, compiled when first needed); everything else, the
         32-bit path included, runs the plain kernel."""
-        _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions)
+        _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
+                   seq_rows)
         T = q.shape[0]
         if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != q.shape:
             raise KernelError("attention: q / out must be contiguous [T, nq*d]")
@@ -230,17 +239,24 @@ class CudaKernels:
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and d % 16 == 0 and d <= 256):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
-                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len)
+                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows)
             return
         self.launches += 1
         _check(self.lib.chibi_attention_generic(
             _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
-            _ptr(seq_of_token), _ptr(positions), T, nq, nkv, d, page_size, k_cache.shape[0],
+            _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, page_size,
+            k_cache.shape[0],
             float(scale), int(window or 0), _ptr(self.error), self._stream()), "attention")
 
+    def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
+        """Key ranges per sequence of the decode attention kernel: enough CTAs to
+        fill the GPU twice, at least 64 keys per range."""
+        ctas = seqs * nkv * ((nq // nkv + 15) // 16)
+        return max(1, min(-(-2 * self.sm_count // ctas), -(-max_ctx_len // 64), 64))
+
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
-                       page_size, scale, window, max_q_len, max_ctx_len, min_q_len) -> None:
+                       page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:
         lib = self._attention_libs.get(d)
         if lib is None:
             lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
@@ -251,18 +267,28 @@ class CudaKernels:
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
         splits, scratch = 1, None
         if mode & 1:
-            # enough CTAs to fill the GPU twice, at least 64 keys per key range
-            ctas = seqs * nkv * ((nq // nkv + 15) // 16)
-            splits = max(1, min(-(-2 * self.sm_count // ctas), -(-max_ctx_len // 64), 64))
+            splits = self.decode_attention_splits(seqs, nq, nkv, max_ctx_len)
             if splits > 1:
                 scratch = self._scratch(seqs * nq * splits * (d + 2))
         status = lib.chibi_attention_mma(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
-            _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
+            _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
             int(window or 0), mode, int(max_q_len), splits, _ptr(scratch),
             scratch.numel() if scratch is not None else 0, _ptr(self.error), self._stream())
         self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
         _check(status, "attention (tensor cores)")
+
+    def apply_table_updates(self, table: torch.Tensor, updates: torch.Tensor, capacity: int) -> None:
+        """table[row][index] = page for the (row, index, page) triples that follow
+        the count in ``updates`` (int32: [count, row, index, page, ...])."""
+        _need_cuda(table, updates)
+        if table.dtype != torch.int32 or updates.dtype != torch.int32 or table.dim() != 2 \
+                or not table.is_contiguous() or updates.numel() < 1 + 3 * capacity:
+            raise KernelError("apply_table_updates: int32 table [rows, blocks] and 1 + 3 * capacity updates")
+        self.launches += 1
+        _check(self.lib.chibi_apply_table_updates(_ptr(table), table.shape[1], table.shape[0],
+                                                  _ptr(updates), int(capacity), _ptr(self.error),
+                                                  self._stream()), "apply_table_updates")
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         _need_cuda(gate_up, out)

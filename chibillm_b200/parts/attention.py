@@ -61,6 +61,16 @@ class PagedAttention(Mixer):
         s = self.spec
         return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window)
 
+    def launch_key(self, ctx):
+        if self.position.fused_rotation() is None:
+            return None                      # an encoding of its own: nothing is promised
+        k = self.runtime.kernels
+        splits = getattr(k, "decode_attention_splits", None)
+        if splits is None:
+            return None
+        s = self.spec
+        return (splits(ctx.num_seqs, s.num_heads, s.num_kv_heads, ctx.max_ctx_len),)
+
     # ---- run
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache) -> None:
         s, rt = self.spec, self.runtime
@@ -96,11 +106,12 @@ class PagedAttention(Mixer):
             qkv, q, cache.keys if writes else None, cache.values if writes else None,
             q_norm_w, k_norm_w, inv_freq, rotary_dim, norm.eps if norm is not None else 0.0,
             norm.weight_offset if norm is not None else 0.0,
-            ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size)
+            ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size,
+            ctx.seq_rows)
         att = ctx.workspace.get("attn.out", (T, qw), rt.dtype)
         k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
-                    s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len)
+                    s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows)
         k.linear(att, self.o_proj, residual, residual=residual)
 
 

@@ -68,6 +68,14 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Take the loaded tensors (already on the device) this part declared."""
 
+    def launch_key(self, ctx):
+        """Host-side decisions of ``forward`` that depend on the batch's values
+        (not only on its numbers of tokens and sequences), as a hashable; a
+        decode step is replayed from a CUDA graph only while this stays the same.
+        None (the default) means: never capture a step that runs this part --
+        right for a part that reads values on the host or allocates while it runs."""
+        return None
+
 
 class Norm(Part):
     """y = norm(x) over the last ``spec.size`` features."""

@@ -32,6 +32,10 @@ class PreNormBlock(Block):
         for p in self._parts:
             p.bind(tensors)
 
+    def launch_key(self, ctx):
+        a, b = self.mixer.launch_key(ctx), self.feed_forward.launch_key(ctx)
+        return None if a is None or b is None else (a, b)
+
     def forward(self, residual: torch.Tensor, ctx, cache) -> None:
         x = ctx.workspace.get("block.normed", tuple(residual.shape), self.runtime.dtype)
         self.mixer_norm.forward(residual, x)

@@ -47,7 +47,7 @@ class ReferenceKernels:
 
     def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, inv_freq,
                             rotary_dim, eps, norm_offset, positions, seq_of_token, block_table,
-                            nq, nkv, d, page_size):
+                            nq, nkv, d, page_size, seq_rows=None):
         self._count("qk_norm_rope_append")
         T = qkv.shape[0]
         qw, kw = nq * d, nkv * d
@@ -75,14 +75,16 @@ class ReferenceKernels:
         k = rotate(norm(qkv[:, qw:qw + kw].float().reshape(T, nkv, d), k_norm_w))
         v = qkv[:, qw + kw:qw + 2 * kw].float().reshape(T, nkv, d)
         pos = positions.long()
-        pages = block_table[seq_of_token.long(), pos // page_size].long()
+        rows = seq_of_token.long() if seq_rows is None else seq_rows.long()[seq_of_token.long()]
+        pages = block_table[rows, pos // page_size].long()
         assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
         slots = pos % page_size
         k_cache[pages, :, slots, :] = k.to(k_cache.dtype)
         v_cache[pages, :, slots, :] = v.to(v_cache.dtype)
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
-                  positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0):
+                  positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0,
+                  seq_rows=None):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv
@@ -90,6 +92,8 @@ class ReferenceKernels:
         res = torch.zeros(T, nq, d, dtype=torch.float32, device=q.device)
         for t in range(T):
             s = int(seq_of_token[t])
+            if seq_rows is not None:
+                s = int(seq_rows[s])
             p = int(positions[t])
             first = max(0, p - window + 1) if window else 0
             idx = torch.arange(first, p + 1, device=q.device)
@@ -103,6 +107,13 @@ class ReferenceKernels:
                 pr = torch.softmax(sc, dim=0)
                 res[t, h] = pr @ vals[:, g, :]
         out.copy_(res.reshape(T, nq * d).to(out.dtype))
+
+    def apply_table_updates(self, table, updates, capacity):
+        n = int(updates[0])
+        assert n <= capacity
+        for i in range(n):
+            row, index, page = (int(v) for v in updates[1 + 3 * i:4 + 3 * i])
+            table[row, index] = page
 
     def swiglu(self, gate_up, out):
         self._count("swiglu")

@@ -181,3 +181,41 @@ def test_plan_groups_by_need_and_shares_caches():
     storage.views[3].arrays["h"][1] = 5.0
     storage.zero_state_slot(1)
     assert float(storage.views[3].arrays["h"].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_device_mirror_follows_the_tables(seed):
+    """The drained updates, applied in any order (the device applies them in
+    parallel), keep a mirror [slot][block] equal to the host tables of the live
+    requests -- also when a slot passes from one request to the next."""
+    rng = random.Random(100 + seed)
+    m = manager(pages=24, page_size=4, window=10, max_requests=3)
+    mirror = {g: {} for g in m.groups}
+    live = {}
+    next_id = 0
+    for step in range(400):
+        r = rng.random()
+        if r < 0.3 and len(live) < 3:
+            m.admit(next_id); live[next_id] = 0; next_id += 1
+        elif r < 0.8 and live:
+            rid = rng.choice(list(live))
+            grow = rng.choice([1, 1, 3, 9, 20])
+            try:
+                m.reserve(rid, live[rid] + grow)
+                live[rid] += grow
+                m.commit(rid, live[rid])
+            except CacheError:
+                pass
+        elif live:
+            rid = rng.choice(list(live)); m.release(rid); del live[rid]
+        if rng.random() < 0.5:          # a step happens: updates travel to the device
+            for g in m.groups:
+                ups = m.drain_updates(g)
+                assert len({(row, idx) for row, idx, _ in ups}) == len(ups)
+                rng.shuffle(ups)
+                for row, idx, page in ups:
+                    mirror[g][(row, idx)] = page
+                for rid in live:
+                    rc = m.get(rid)
+                    for idx, page in enumerate(rc.tables[g]):
+                        assert mirror[g].get((rc.state_slot, idx), -1) == page
