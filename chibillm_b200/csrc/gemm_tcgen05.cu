@@ -449,3 +449,60 @@ CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_t
     }
     return CHIBI_OK;
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+#include "no_alloc_api.h"
+
+// Scratch for the split-K partial sums of chibi_gemm_bf16_noalloc.  In host code
+// this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_noalloc_scratch[CHIBI_NOALLOC_SCRATCH_FLOATS];
+
+CHIBI_API const char* chibi_error_string(int code)
+{
+    switch (code) {
+    case CHIBI_OK: return "ok";
+    case CHIBI_ERR_ARGUMENT: return "invalid argument";
+    case CHIBI_ERR_UNSUPPORTED: return "shape or alignment that this kernel does not take";
+    case CHIBI_ERR_DEVICE_CHECK: return "a device-side check failed";
+    case CHIBI_ERR_SCRATCH_LIMIT:
+        return "the product needs more scratch than the library's built-in array holds "
+               "(splits * M * N > CHIBI_NOALLOC_SCRATCH_FLOATS)";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error code";
+    }
+}
+
+CHIBI_API int chibi_gemm_bf16_noalloc(const void* x, const void* w, void* out, int out_type,
+                                      const float* residual, int M, int N, int K,
+                                      long long x_stride, long long w_stride, long long out_stride,
+                                      long long res_stride, int* error, cudaStream_t stream)
+{
+    constexpr int MAX_DEVICES = 64;
+    static float* device_ptr[MAX_DEVICES] = {};
+    static std::mutex mutex;
+    const int splits = chibi_gemm_bf16_splits(M, N, K);
+    if (M > 0 && N > 0 && splits <= 0)
+        return CHIBI_ERR_UNSUPPORTED;
+    if (splits > 1 && (long long)splits * M * N > (long long)CHIBI_NOALLOC_SCRATCH_FLOATS)
+        return CHIBI_ERR_SCRATCH_LIMIT;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess)
+        return (int)e;
+    if (device < 0 || device >= MAX_DEVICES)
+        return CHIBI_ERR_ARGUMENT;
+    float* scratch;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (!device_ptr[device]) {
+            // once per device, with that device current: the array's address on this device
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess)
+                return (int)e;
+            device_ptr[device] = static_cast<float*>(p);
+        }
+        scratch = device_ptr[device];
+    }
+    return chibi_gemm_bf16(x, w, out, out_type, residual, M, N, K, x_stride, w_stride, out_stride,
+                           res_stride, scratch, CHIBI_NOALLOC_SCRATCH_FLOATS, error, stream);
+}
