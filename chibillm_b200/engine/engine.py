@@ -72,9 +72,12 @@ class InferenceEngine:
         self._next_key = 0
 
     # ---- requests
-    def add(self, seq_id: Hashable, prompt: Seq[int], params: Optional[SamplingParams] = None) -> str:
+    def add(self, seq_id: Hashable, prompt: Seq[int], params: Optional[SamplingParams] = None,
+            sample_key: Optional[int] = None) -> str:
         """Queue a request.  Returns "admitted" or "deferred" (it waits in line);
-        raises if it can never fit."""
+        raises if it can never fit.  ``sample_key`` names the request to the
+        sampler: with the same seed, key and temperature a request samples the
+        same tokens whatever else runs (default: a running number)."""
         params = params or SamplingParams()
         limit = self.runner.max_context_tokens
         if len(prompt) + 1 > limit:
@@ -86,7 +89,7 @@ class InferenceEngine:
         if not self.scheduler.fits_cache(seq):
             raise SchedulerError("sequence_too_large", f"request {seq_id!r} can never fit the cache")
         self.metrics[seq_id] = RequestMetrics(prompt_tokens=len(prompt), submitted_at=time.perf_counter())
-        self._keys[seq_id] = self._next_key
+        self._keys[seq_id] = self._next_key if sample_key is None else int(sample_key)
         self._next_key += 1
         self.pending.append(seq)
         self._admit_pending()
@@ -161,7 +164,7 @@ class InferenceEngine:
         for i, (prompt, p) in enumerate(zip(prompts, params)):
             sid = ("generate", self._next_key, i)
             ids.append(sid)
-            self.add(sid, prompt, p)
+            self.add(sid, prompt, p, sample_key=i)
         while not self.is_finished():
             self.step()
         out = []

@@ -1,0 +1,337 @@
+"""Each part alone against the plain implementation's function for it, at sizes
+other than the engine tests'; generation through the Python entry point; and a
+toy architecture, defined here, whose mixer keeps state of its own: it is
+registered, built, loaded and stepped without a change to the framework."""
+import json
+import math
+import os
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen3
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def runtime(dtype):
+    from chibillm_b200.engine.runner import make_runtime
+    return make_runtime(dtype, DEV)
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+class FakeCtx:
+    """The least a feed-forward needs of a step's context."""
+
+    def __init__(self):
+        from chibillm_b200.engine.batch import Workspace
+        self.workspace = Workspace(torch.device(DEV))
+
+
+TOL = {"float32": 5e-6, "bfloat16": 2e-2}
+
+
+def close(got, ref, dtype, what):
+    scale = float(ref.abs().max())
+    worst = float((got.float().cpu() - ref).abs().max())
+    assert worst <= TOL[dtype] * scale, f"{what} ({dtype}): {worst:.3e} > {TOL[dtype]:.0e} * {scale:.3f}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    from chibillm_b200.config import NormSpec
+    from chibillm_b200.parts import make_norm
+    rt = runtime(dtype)
+    norm = make_norm(NormSpec("rmsnorm", 200, 2e-5, 0.0), "w", rt)
+    assert [(t.name, t.shape) for t in norm.expected_tensors()] == [("w", (200,))]
+    w = (1 + 0.1 * rnd(200, seed=1)).to(torch.bfloat16)
+    norm.bind({"w": w.to(DEV).to(rt.dtype)})
+    x = rnd(13, 200, seed=2, scale=4.0)
+    out = torch.empty(13, 200, dtype=rt.dtype, device=DEV)
+    norm.forward(x.to(DEV), out)
+    close(out, plain_qwen3.rms_norm(x, w.float(), 2e-5), dtype, "norm")
+    # per-head use: every run of 200 features of a wider row is one group
+    wide = rnd(5, 600, seed=3)
+    out = torch.empty(5, 600, dtype=rt.dtype, device=DEV)
+    norm.forward(wide.to(DEV).to(rt.dtype), out)
+    ref = plain_qwen3.rms_norm(wide.to(rt.dtype).float().view(5, 3, 200), w.float(), 2e-5).view(5, 600)
+    close(out, ref, dtype, "grouped norm")
+
+
+def test_position_part():
+    from chibillm_b200.config import PositionSpec
+    from chibillm_b200.parts import make_position
+    rt = runtime("float32")
+    rope = make_position(PositionSpec("rope", head_dim=48, rotary_dim=48, theta=5e5), rt)
+    table, rot = rope.fused_rotation()
+    assert rot == 48 and torch.equal(table.cpu(), plain_qwen3.rope_inverse_frequencies(5e5, 48))
+    none = make_position(PositionSpec("none"), rt)
+    assert none.fused_rotation() == (None, 0)
+    with pytest.raises(ValueError):
+        make_position(PositionSpec("rope", head_dim=48, rotary_dim=50, theta=1e4), rt)
+    with pytest.raises(KeyError):
+        make_position(PositionSpec("alibi"), rt)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    from chibillm_b200.config import GatedMLPSpec
+    from chibillm_b200.parts import make_feed_forward
+    rt = runtime(dtype)
+    H, I, T = 72, 200, 11
+    names = {"gate_proj": "g", "up_proj": "u", "down_proj": "d"}
+    ff = make_feed_forward(GatedMLPSpec("gated_mlp", hidden_size=H, intermediate_size=I, activation="silu"),
+                           names, rt)
+    assert sorted((t.name, t.shape) for t in ff.expected_tensors()) == [("d", (H, I)), ("g", (I, H)), ("u", (I, H))]
+    w = {n: rnd(*s, seed=i, scale=0.1, dtype=torch.bfloat16) for i, (n, s) in
+         enumerate([("g", (I, H)), ("u", (I, H)), ("d", (H, I))])}
+    ff.bind({n: t.to(DEV).to(rt.dtype) for n, t in w.items()})
+    x = rnd(T, H, seed=7).to(rt.dtype)
+    residual = rnd(T, H, seed=8)
+    res_dev = residual.to(DEV).clone()
+    ff.forward(x.to(DEV), res_dev, FakeCtx())
+    xf = x.float()
+    gate, up = xf @ w["g"].float().t(), xf @ w["u"].float().t()
+    ref = residual + ((gate / (1 + torch.exp(-gate))) * up) @ w["d"].float().t()
+    close(res_dev, ref, dtype, "feed-forward")
+
+
+def _one_layer_runner(dtype, tmp_path, window=None):
+    """A runner over a one-layer model with sizes the engine tests do not use."""
+    cfg = tiny_configs.get("A")
+    cfg.update(num_hidden_layers=1, hidden_size=72, num_attention_heads=6, num_key_value_heads=2, head_dim=32,
+               intermediate_size=136, vocab_size=211, rope_theta=2e4, rms_norm_eps=1e-5,
+               max_position_embeddings=256, tie_word_embeddings=False)
+    if window:
+        cfg.update(use_sliding_window=True, sliding_window=window, max_window_layers=0)
+    from chibillm_b200.weights import write_random_model
+    from chibillm_b200.engine.runner import ModelRunner
+    folder = os.path.join(str(tmp_path), f"one_layer_{dtype}_{window}")
+    write_random_model(cfg, folder, seed=11)
+    runner = ModelRunner.from_folder(folder, dtype=dtype, device=DEV, page_size=8, pool_tokens=256)
+    return cfg, folder, runner
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [None, 20])
+def test_mixer_and_block_parts(dtype, window, tmp_path):
+    """The attention mixer alone (its output added to a zero residual) and the
+    whole block, fed with hidden states of our own in two steps (40 tokens, then
+    9 more) so that the second step reads the first one's pages."""
+    from chibillm_b200.engine.batch import StepEntry
+    cfg, folder, runner = _one_layer_runner(dtype, tmp_path, window)
+    config, weights = plain_qwen3.read_model_folder(folder)
+    config["head_dim"] = cfg["head_dim"]
+    rt = runner.runtime
+    block = runner.model.blocks[0]
+    T0, T1, H = 40, 9, cfg["hidden_size"]
+    hidden = rnd(T0 + T1, H, seed=21)
+    prefix = "model.layers.0."
+    # plain: mixer output = attention_block(h) - h, with the block's own input norm inside
+    ref_attn = plain_qwen3.attention_block(hidden, weights, prefix, config, window) - hidden
+    ref_block = plain_qwen3.mlp_block(plain_qwen3.attention_block(hidden, weights, prefix, config, window),
+                                      weights, prefix, config)
+    for what in ("mixer", "block"):
+        rid = f"{what}-{dtype}"
+        outs = []
+        for lo, hi in ((0, T0), (T0, T0 + T1)):
+            entries = [StepEntry(rid, [0] * (hi - lo), [])]
+            if not runner.has(rid):
+                runner.admit(rid)
+            runner.cache.reserve(rid, hi)
+            ctx, updates, _ = runner._build_context(entries, False)
+            for name, (view, cap) in updates.items():
+                if cap:
+                    rt.kernels.apply_table_updates(runner.storage.tables[name], view, cap)
+            h = hidden[lo:hi].to(DEV)
+            if what == "mixer":
+                x = torch.empty(hi - lo, H, dtype=rt.dtype, device=DEV)
+                block.mixer_norm.forward(h, x)
+                residual = torch.zeros(hi - lo, H, device=DEV)
+                block.mixer.forward(x, residual, ctx, runner.storage.views[0])
+            else:
+                residual = h.clone()
+                block.forward(residual, ctx, runner.storage.views[0])
+            outs.append(residual.cpu())
+            runner.cache.commit(rid, hi)
+        rt.kernels.check_error_word()
+        runner.end(rid)
+        close(torch.cat(outs), ref_attn if what == "mixer" else ref_block, dtype, f"{what} window={window}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
+    import chibillm_b200
+    folder = helpers.make_model_dir(tmp_path, "B", seed=1)
+    config, weights = plain_qwen3.read_model_folder(folder)
+    prompts = list(helpers.random_requests(384, [1, 7, 23, 40], seed=1).values())
+    expected = [plain_qwen3.generate_greedy(config, weights, p, 12) for p in prompts]
+    llm = chibillm_b200.LLM(folder, dtype=dtype, context_length=128, kv_cache_tokens=256, max_sequences=3,
+                            max_batch_tokens=16, prefill_chunk_tokens=8)
+    got = llm.generate(prompts, max_tokens=12, ignore_eos=True)
+    if dtype == "float32":
+        assert got == expected
+    else:
+        # bfloat16 may flip a near-tie; what follows a flip differs, so compare up to the first one
+        same = sum(1 for g, e in zip(got, expected) if g == e)
+        first = [next((i for i, (a, b) in enumerate(zip(g, e)) if a != b), 12) for g, e in zip(got, expected)]
+        assert same >= 3 and min(first) >= 4, (got, expected)
+    llm.runner.cache.check_invariants()
+    assert not llm.runner.cache.requests
+    # sampling with a temperature: the same seed gives the same tokens, whatever the batch budget
+    a = llm.generate(prompts, max_tokens=8, temperature=0.7, seed=1, ignore_eos=True)
+    llm2 = chibillm_b200.LLM(folder, dtype=dtype, context_length=128, kv_cache_tokens=512, max_sequences=4,
+                             max_batch_tokens=512, prefill_chunk_tokens=64)
+    b = llm2.generate(prompts, max_tokens=8, temperature=0.7, seed=1, ignore_eos=True)
+    if dtype == "float32":
+        assert a == b
+    c = llm2.generate(prompts, max_tokens=8, temperature=0.7, seed=2, ignore_eos=True)
+    assert c != b
+
+
+# ------------------------------------------------------------------ a toy architecture
+@dataclass(frozen=True)
+class ToyStateSpec:
+    kind: str
+    hidden_size: int = 0
+    decay: float = 0.5
+
+
+def _register_toy():
+    """A mixer with a running state h per request: h <- decay * h + x_t;
+    out_t = W h.  Its state lives in the cache manager's slots."""
+    from chibillm_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec, PositionSpec,
+                                      RunStep, register_architecture)
+    from chibillm_b200.parts import FixedStateNeed, Mixer, TensorSpec, register_mixer
+
+    class ToyStateMixer(Mixer):
+        def __init__(self, spec, names, rt):
+            self.spec, self.names, self.rt = spec, names, rt
+
+        def expected_tensors(self):
+            return [TensorSpec(self.names["mix"], (self.spec.hidden_size, self.spec.hidden_size))]
+
+        def bind(self, tensors):
+            self.w = tensors[self.names["mix"]].float()
+
+        def cache_need(self):
+            return FixedStateNeed((("h", (self.spec.hidden_size,), torch.float32),))
+
+        def forward(self, x, residual, ctx, cache):
+            h_all = cache.arrays["h"]
+            start = 0
+            for slot, n in zip(ctx.slot_list, ctx.q_lens):
+                h = h_all[slot].clone()
+                for t in range(start, start + n):
+                    h = self.spec.decay * h + x[t].float()
+                    residual[t] += self.w @ h
+                h_all[slot] = h
+                start += n
+
+    register_mixer("toy_state", ToyStateMixer, replace=True)
+
+    def read_config(obj):
+        return obj
+
+    def model_spec(obj):
+        H = obj["hidden_size"]
+        norm = NormSpec("rmsnorm", H, obj["eps"], 0.0)
+        mlp = GatedMLPSpec("gated_mlp", hidden_size=H, intermediate_size=obj["intermediate_size"], activation="silu")
+        attn = AttentionSpec(kind="attention", hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16,
+                             scale=0.25, window=None, qk_norm=None,
+                             position=PositionSpec("rope", head_dim=16, rotary_dim=16, theta=1e4))
+        names_attn = (("mixer_norm", "n1.weight"), ("feed_forward_norm", "n2.weight"), ("q_proj", "q.weight"),
+                      ("k_proj", "k.weight"), ("v_proj", "v.weight"), ("o_proj", "o.weight"),
+                      ("gate_proj", "gate.weight"), ("up_proj", "up.weight"), ("down_proj", "down.weight"))
+        names_toy = (("mixer_norm", "n1.weight"), ("feed_forward_norm", "n2.weight"), ("mix", "mix.weight"),
+                     ("gate_proj", "gate.weight"), ("up_proj", "up.weight"), ("down_proj", "down.weight"))
+        layers = (LayerSpec("prenorm", attn, mlp, norm, norm, "layers.0.", names_attn),
+                  LayerSpec("prenorm", ToyStateSpec("toy_state", H, obj["decay"]), mlp, norm, norm, "layers.1.",
+                            names_toy))
+        # attention, toy, the toy layer again (shared weights, a state of its own), attention
+        # once more reading the first step's cache
+        order = (RunStep(0), RunStep(1), RunStep(1), RunStep(0, cache_of=0))
+        return ModelSpec(architecture="ToyHybridForCausalLM", vocab_size=obj["vocab_size"], hidden_size=H,
+                         max_positions=obj["max_positions"], layers=layers, run_order=order, final_norm=norm,
+                         embedding_name="embed.weight", final_norm_name="norm.weight", output_name="head.weight",
+                         tie_output_to_embedding=True)
+
+    register_architecture("ToyHybridForCausalLM", read_config, model_spec, replace=True)
+
+
+def _toy_plain(obj, w, ids):
+    """Whole sequence, no cache."""
+    T = len(ids)
+    h = plain_qwen3.embedding(w["embed.weight"], ids)
+    eps = obj["eps"]
+
+    def mlp(h, p):
+        x = plain_qwen3.rms_norm(h, w[p + "n2.weight"], eps)
+        gate, up = x @ w[p + "gate.weight"].t(), x @ w[p + "up.weight"].t()
+        return h + ((gate / (1 + torch.exp(-gate))) * up) @ w[p + "down.weight"].t()
+
+    def attn(h, p, kv_from=None):
+        x = plain_qwen3.rms_norm(h, w[p + "n1.weight"], eps)
+        pos = torch.arange(T)
+        q = plain_qwen3.rope((x @ w[p + "q.weight"].t()).view(T, 4, 16), pos, 1e4)
+        if kv_from is None:
+            k = plain_qwen3.rope((x @ w[p + "k.weight"].t()).view(T, 2, 16), pos, 1e4)
+            v = (x @ w[p + "v.weight"].t()).view(T, 2, 16)
+        else:
+            k, v = kv_from
+        out = plain_qwen3.causal_attention(q, k, v, None).reshape(T, 64)
+        return h + out @ w[p + "o.weight"].t(), (k, v)
+
+    def toy(h, p):
+        x = plain_qwen3.rms_norm(h, w[p + "n1.weight"], eps)
+        state = torch.zeros(h.shape[1])
+        out = torch.empty_like(h)
+        for t in range(T):
+            state = obj["decay"] * state + x[t]
+            out[t] = w[p + "mix.weight"] @ state
+        return h + out
+
+    h, kv = attn(h, "layers.0.")
+    h = mlp(h, "layers.0.")
+    for _ in range(2):
+        h = mlp(toy(h, "layers.1."), "layers.1.")
+    h, _ = attn(h, "layers.0.", kv_from=kv)
+    h = mlp(h, "layers.0.")
+    return plain_qwen3.rms_norm(h, w["norm.weight"], eps) @ w["embed.weight"].t()
+
+
+def test_toy_architecture_with_a_state_of_its_own(tmp_path):
+    from chibillm_b200.config import unregister_architecture
+    from chibillm_b200.engine.runner import ModelRunner
+    from chibillm_b200.weights import write_random_model
+    _register_toy()
+    try:
+        obj = {"architectures": ["ToyHybridForCausalLM"], "hidden_size": 64, "intermediate_size": 96,
+               "vocab_size": 131, "eps": 1e-5, "decay": 0.6, "max_positions": 128}
+        folder = write_random_model(obj, str(tmp_path / "toy"), seed=3, dtype=torch.float32)
+        runner = ModelRunner.from_folder(folder, dtype="float32", device=DEV, page_size=4, pool_tokens=256,
+                                         max_requests=3)
+        # two run steps keep state, the two attention steps share one paged cache
+        assert [type(v).__name__ for v in runner.storage.views] == \
+               ["PagedKVView", "FixedStateView", "FixedStateView", "PagedKVView"]
+        assert not runner.storage.views[3].writes and runner.plan.groups[0].num_entries == 1
+        _, w = plain_qwen3.read_model_folder(folder)
+        reqs = helpers.random_requests(131, [30, 17, 45, 8, 26], seed=9)
+        ref = {rid: _toy_plain(obj, w, ids) for rid, ids in reqs.items()}
+        for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, 1), "portions"),
+                            (helpers.trace_mixed(reqs, 192, seed=2, max_live=3, decode_tail=6), "mixed")):
+            got = helpers.run_trace(runner, trace)
+            helpers.assert_logits_close(got, ref, 2e-5, f"toy {what}")
+            runner.cache.check_invariants()
+        assert runner.graph_replays == 0        # a part that gives no launch key is never captured
+    finally:
+        unregister_architecture("ToyHybridForCausalLM")
