@@ -92,30 +92,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Loads `rows` keys (or values) starting at position key0 of one (sequence, kv
-// head) into shared memory [rows][DPAD]; rows at or past key_end are zeroed.
-// `tid` / `nthreads` describe the group of threads that shares the work.
-__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* dst, const __nv_bfloat16* cache,
-                                             const int* table, int kv_head, int nkv, int page_size,
-                                             int num_pages, int key0, int key_end, int rows, int tid,
-                                             int nthreads, int* error)
+// Loads 16 keys and their values, positions key0 .. key0 + 15 of one (sequence,
+// kv head), into shared memory [16][DPAD] each; rows at or past key_end are
+// zeroed.  One warp: lanes 0..15 look up the page of one row each (one division
+// per row, shared by K and V), the row offsets travel by shuffle, and every lane
+// issues its 16-byte chunks.
+__device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
+                                               const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
+                                               const int* table, int kv_head, int nkv, int page_size,
+                                               int num_pages, int key0, int key_end, int lane, int* error)
 {
-    for (int c = tid; c < rows * CHUNKS; c += nthreads) {
-        const int row = c / CHUNKS, col = c - row * CHUNKS;
-        const int key = key0 + row;
-        bool valid = key < key_end;
-        const __nv_bfloat16* src = cache;
-        if (valid) {
-            const int page = table[key / page_size];
+    long long off = -1;
+    {
+        const int key = key0 + (lane & 15);
+        if (key < key_end) {
+            const int block = key / page_size;
+            const int page = table[block];
             if (page < 0 || page >= num_pages) {
-                valid = false;
                 if (error)
                     atomicExch(error, 3);
             } else {
-                src = cache + (((size_t)page * nkv + kv_head) * page_size + key % page_size) * D + col * 8;
+                off = (((long long)page * nkv + kv_head) * page_size + (key - block * page_size)) * D;
             }
         }
-        cp_async16(dst + row * DPAD + col * 8, src, valid);
+    }
+#pragma unroll
+    for (int i = 0; i < 16 * CHUNKS / 32; ++i) {
+        const int c = lane + 32 * i;
+        const int row = c / CHUNKS, col = c - row * CHUNKS;
+        const long long o = __shfl_sync(0xffffffffu, off, row);
+        const bool valid = o >= 0;
+        const long long src = valid ? o + col * 8 : 0;
+        cp_async16(k_dst + row * DPAD + col * 8, k_cache + src, valid);
+        cp_async16(v_dst + row * DPAD + col * 8, v_cache + src, valid);
     }
 }
 
@@ -294,10 +303,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         if (i < my_tiles) {
             const int key0 = first + (my_first_tile + i * DEC_WARPS) * DEC_TILE;
             __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
-            load_kv_rows(st, p.k_cache, table, kv_head, p.nkv, p.page_size, p.num_pages, key0, key_end,
-                         DEC_TILE, lane, 32, p.error);
-            load_kv_rows(st + DEC_TILE * DPAD, p.v_cache, table, kv_head, p.nkv, p.page_size, p.num_pages,
-                         key0, key_end, DEC_TILE, lane, 32, p.error);
+            load_kv_tile16(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, table, kv_head, p.nkv,
+                           p.page_size, p.num_pages, key0, key_end, lane, p.error);
         }
         cp_async_commit();
     };
@@ -455,10 +462,10 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const Attn
         if (i < n_tiles) {
             __nv_bfloat16* st = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
             const int key0 = key_begin + i * PRE_KEYS;
-            load_kv_rows(st, p.k_cache, table, kv_head, p.nkv, p.page_size, p.num_pages, key0, key_end,
-                         PRE_KEYS, threadIdx.x, blockDim.x, p.error);
-            load_kv_rows(st + PRE_KEYS * DPAD, p.v_cache, table, kv_head, p.nkv, p.page_size, p.num_pages,
-                         key0, key_end, PRE_KEYS, threadIdx.x, blockDim.x, p.error);
+            for (int sub = warp; sub < PRE_KEYS / 16; sub += PRE_WARPS)
+                load_kv_tile16(st + sub * 16 * DPAD, st + (PRE_KEYS + sub * 16) * DPAD, p.k_cache, p.v_cache,
+                               table, kv_head, p.nkv, p.page_size, p.num_pages, key0 + sub * 16, key_end,
+                               lane, p.error);
         }
         cp_async_commit();
     };

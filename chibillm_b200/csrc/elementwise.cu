@@ -30,8 +30,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 // One block per group of n features: inv = rsqrt(sum(x^2)/n + eps);
 // y = (x * inv) * (w + offset).
 template <typename TX, typename TW, typename TO>
-__global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
-                               TO* __restrict__ out, int n, long long x_stride,
+__global__ void rmsnorm_kernel(const TX* x, const TW* __restrict__ w, TO* out,   // out may be x
+                               int n, long long x_stride,
                                long long out_stride, float eps, float offset)
 {
     __shared__ float scratch[33];
@@ -50,14 +50,57 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ 
     }
 }
 
+// The same for 32-bit rows and bfloat16 weights and output, n a multiple of 4
+// and at most 16 * blockDim.x: the row stays in registers between the two passes.
+__global__ void __launch_bounds__(512)
+rmsnorm_f32_bf16_kernel(const float* x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* out, int n,
+                        long long x_stride, long long out_stride, float eps, float offset)
+{
+    __shared__ float scratch[33];
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * x_stride);
+    __nv_bfloat16* dst = out + (size_t)blockIdx.x * out_stride;
+    const int n4 = n >> 2;
+    float4 v[4];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        v[i] = j < n4 ? row[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s = fmaf(v[i].x, v[i].x, s);
+        s = fmaf(v[i].y, v[i].y, s);
+        s = fmaf(v[i].z, v[i].z, s);
+        s = fmaf(v[i].w, v[i].w, s);
+    }
+    s = block_sum(s, scratch);
+    const float inv = rsqrtf(s / (float)n + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        if (j < n4) {
+            const uint2 wv = *reinterpret_cast<const uint2*>(w + 4 * j);
+            const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv.x);
+            const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
+            const __nv_bfloat162 o01 = __floats2bfloat162_rn((v[i].x * inv) * (__low2float(w01) + offset),
+                                                             (v[i].y * inv) * (__high2float(w01) + offset));
+            const __nv_bfloat162 o23 = __floats2bfloat162_rn((v[i].z * inv) * (__low2float(w23) + offset),
+                                                             (v[i].w * inv) * (__high2float(w23) + offset));
+            uint2 ov;
+            ov.x = *reinterpret_cast<const uint32_t*>(&o01);
+            ov.y = *reinterpret_cast<const uint32_t*>(&o23);
+            *reinterpret_cast<uint2*>(dst + 4 * j) = ov;
+        }
+    }
+}
+
 // ------------------------------------------- per-head norm + rotation + append
-// One block per token, one warp per head job.  Jobs 0..nq-1 are query heads,
-// nq..nq+nkv-1 key heads, the rest value heads.  Query and key heads are
-// normalised over their d features (when a norm weight is given), rotated
-// (split-half pairs (j, j + rot/2), angle = float(pos) * inv_freq[j]) and
-// written to q_out or to the key cache; value heads are copied to the value
-// cache.  Cache layout: [page][kv_head][slot][d]; page = block_table[row][pos /
-// page_size], slot = pos % page_size.
+// grid (tokens, ceil(jobs / warps)), one warp per head job.  Jobs 0..nq-1 are
+// query heads, nq..nq+nkv-1 key heads, the rest value heads.  Query and key
+// heads are normalised over their d features (when a norm weight is given),
+// rotated (split-half pairs (j, j + rot/2), angle = float(pos) * inv_freq[j];
+// the block computes the token's cosines and sines once) and written to q_out
+// or to the key cache; value heads are copied to the value cache.  Cache
+// layout: [page][kv_head][slot][d]; page = block_table[row][pos / page_size],
+// slot = pos % page_size.
 template <typename TX, typename TW, typename TC>
 __global__ void qk_norm_rope_append_kernel(
     const TX* __restrict__ qkv, long long qkv_stride, TX* __restrict__ q_out,
@@ -65,88 +108,89 @@ __global__ void qk_norm_rope_append_kernel(
     const TW* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ seq_rows, const int* __restrict__ block_table, int table_stride, int nq,
-    int nkv, int d, int rot,
-    int page_size, int num_pages, float eps, float norm_offset, int append,
+    int nkv, int d, int rot, int page_size, int num_pages, float eps, float norm_offset, int append,
     int* __restrict__ error)
 {
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
-    float* buf = smem + (size_t)warp * d;
+    const int half = rot >> 1;
+    float* cs = smem;                       // [half] cosines, [half] sines
+    float* buf = smem + 2 * half + (size_t)warp * d;
     const int pos = positions[t];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float a = (float)pos * inv_freq[j];
+        cs[j] = cosf(a);
+        cs[half + j] = sinf(a);
+    }
+    __syncthreads();
     const int jobs = append ? nq + 2 * nkv : nq;
-    const TX* row = qkv + (size_t)t * qkv_stride;
+    const int job = blockIdx.y * warps + warp;
+    if (job >= jobs)
+        return;
+    const TX* src = qkv + (size_t)t * qkv_stride + (size_t)job * d;   // q | k | v are consecutive columns
+    const bool is_q = job < nq;
+    const bool is_k = !is_q && job < nq + nkv;
+    const int head = is_q ? job : (is_k ? job - nq : job - nq - nkv);
 
     long long cache_base = -1;
-    if (append) {
+    if (!is_q) {
         const int seq = seq_of_token[t];
         const int table_row = seq_rows ? seq_rows[seq] : seq;
         const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
         if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0 && error)
+            if (lane == 0 && error)
                 atomicExch(error, 2);
-        } else {
-            cache_base = ((long long)page * nkv * page_size + (pos % page_size)) * d;
+            return;
         }
+        cache_base = (((long long)page * nkv + head) * page_size + (pos % page_size)) * d;
     }
-
-    for (int job = warp; job < jobs; job += warps) {
-        const bool is_q = job < nq;
-        const bool is_k = !is_q && job < nq + nkv;
-        const int head = is_q ? job : (is_k ? job - nq : job - nq - nkv);
-        const TX* src = row + (size_t)job * d; // q | k | v are consecutive columns
-        if (!is_q && !is_k) {
-            if (cache_base >= 0) {
-                TC* dst = v_cache + cache_base + (long long)head * page_size * d;
-                for (int j = lane; j < d; j += 32)
-                    dst[j] = from_f32<TC>(to_f32(src[j]));
-            }
-            continue;
-        }
-        const TW* w = is_q ? q_norm_w : k_norm_w;
-        float s = 0.f;
-        for (int j = lane; j < d; j += 32) {
-            const float v = to_f32(src[j]);
-            buf[j] = v;
-            s = fmaf(v, v, s);
-        }
-        s = warp_sum(s);
+    if (!is_q && !is_k) {
+        TC* dst = v_cache + cache_base;
+        for (int j = lane; j < d; j += 32)
+            dst[j] = from_f32<TC>(to_f32(src[j]));
+        return;
+    }
+    const TW* w = is_q ? q_norm_w : k_norm_w;
+    float s = 0.f;
+    for (int j = lane; j < d; j += 32) {
+        const float v = to_f32(src[j]);
+        buf[j] = v;
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    __syncwarp();
+    if (w) {
+        const float inv = rsqrtf(s / (float)d + eps);
+        for (int j = lane; j < d; j += 32)
+            buf[j] = (buf[j] * inv) * (to_f32(w[j]) + norm_offset);
         __syncwarp();
-        if (w) {
-            const float inv = rsqrtf(s / (float)d + eps);
-            for (int j = lane; j < d; j += 32)
-                buf[j] = (buf[j] * inv) * (to_f32(w[j]) + norm_offset);
-            __syncwarp();
-        }
-        const int half = rot >> 1;
-        // Every lane reads its pair before any lane writes.
-        float lo[4], hi[4]; // d <= 256 -> at most 4 pairs per lane
-        int cnt = 0;
-        for (int j = lane; j < half; j += 32, ++cnt) {
-            const float a = (float)pos * inv_freq[j];
-            const float c = cosf(a), sn = sinf(a);
-            const float x0 = buf[j], x1 = buf[j + half];
-            lo[cnt] = x0 * c - x1 * sn;
-            hi[cnt] = x1 * c + x0 * sn;
-        }
-        __syncwarp();
-        cnt = 0;
-        for (int j = lane; j < half; j += 32, ++cnt) {
-            buf[j] = lo[cnt];
-            buf[j + half] = hi[cnt];
-        }
-        __syncwarp();
-        if (is_q) {
-            TX* dst = q_out + ((size_t)t * nq + head) * d;
-            for (int j = lane; j < d; j += 32)
-                dst[j] = from_f32<TX>(buf[j]);
-        } else if (cache_base >= 0) {
-            TC* dst = k_cache + cache_base + (long long)head * page_size * d;
-            for (int j = lane; j < d; j += 32)
-                dst[j] = from_f32<TC>(buf[j]);
-        }
-        __syncwarp();
+    }
+    // every lane reads its pairs before any lane writes (d <= 256: at most 4 pairs per lane)
+    float lo[4], hi[4];
+    int cnt = 0;
+    for (int j = lane; j < half; j += 32, ++cnt) {
+        const float c = cs[j], sn = cs[half + j];
+        const float x0 = buf[j], x1 = buf[j + half];
+        lo[cnt] = x0 * c - x1 * sn;
+        hi[cnt] = x1 * c + x0 * sn;
+    }
+    __syncwarp();
+    cnt = 0;
+    for (int j = lane; j < half; j += 32, ++cnt) {
+        buf[j] = lo[cnt];
+        buf[j + half] = hi[cnt];
+    }
+    __syncwarp();
+    if (is_q) {
+        TX* dst = q_out + ((size_t)t * nq + head) * d;
+        for (int j = lane; j < d; j += 32)
+            dst[j] = from_f32<TX>(buf[j]);
+    } else {
+        TC* dst = k_cache + cache_base;
+        for (int j = lane; j < d; j += 32)
+            dst[j] = from_f32<TC>(buf[j]);
     }
 }
 
@@ -165,6 +209,29 @@ __global__ void swiglu_kernel(const TX* __restrict__ gate_up, TO* __restrict__ o
         const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
         out[i] = from_f32<TO>((g / (1.f + expf(-g))) * u);
     }
+}
+
+// bfloat16 in and out, inter a multiple of 8: eight values per thread.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
+                                     __nv_bfloat16* __restrict__ out, int inter)
+{
+    const int chunks = inter >> 3;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks)
+        return;
+    const size_t row = blockIdx.y;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + 8 * c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + inter + 8 * c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 gf = __bfloat1622float2(gp[i]), uf = __bfloat1622float2(up[i]);
+        op[i] = __floats2bfloat162_rn((gf.x / (1.f + expf(-gf.x))) * uf.x, (gf.y / (1.f + expf(-gf.y))) * uf.y);
+    }
+    *reinterpret_cast<uint4*>(out + row * inter + 8 * c) = o;
 }
 
 // ---------------------------------------------------------------- row gather
@@ -255,6 +322,20 @@ CHIBI_API int chibi_rmsnorm(const void* x, int x_type, const void* w, int w_type
     int block = 32;
     while (block < n && block < 512)
         block <<= 1;
+    if (x_type == CHIBI_F32 && w_type == CHIBI_BF16 && out_type == CHIBI_BF16 && n % 4 == 0
+        && n <= 16 * 512 && x_stride % 4 == 0 && out_stride % 4 == 0
+        && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0
+        && (reinterpret_cast<uintptr_t>(w) & 7) == 0 && x != out) {
+        int fast = 32;
+        while (fast * 16 < n)
+            fast <<= 1;
+        if (fast < 128 && n >= 512)
+            fast = 128;
+        rmsnorm_f32_bf16_kernel<<<(unsigned)groups, fast, 0, stream>>>(
+            (const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n, x_stride, out_stride, eps,
+            offset);
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
         rmsnorm_kernel<TX, TW, TO><<<(unsigned)groups, block, 0, stream>>>(
             (const TX*)x, (const TW*)w, (TO*)out, n, x_stride, out_stride, eps, offset);
@@ -275,10 +356,13 @@ CHIBI_API int chibi_qk_norm_rope_append(
     if (d <= 0 || d > 256 || rot < 0 || rot > d || (rot & 1))
         return CHIBI_ERR_UNSUPPORTED;
     const int jobs = append ? nq + 2 * nkv : nq;
-    int warps = jobs < 8 ? jobs : 8;
-    const size_t smem = (size_t)warps * d * sizeof(float);
+    const int warps = jobs < 8 ? jobs : 8;
+    const size_t smem = (size_t)(warps * d + rot) * sizeof(float);
+    const dim3 grid((unsigned)tokens, (unsigned)((jobs + warps - 1) / warps));
+    if (tokens > 2147483647LL || grid.y > 65535)
+        return CHIBI_ERR_UNSUPPORTED;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-        qk_norm_rope_append_kernel<TX, TW, TC><<<(unsigned)tokens, warps * 32, smem, stream>>>(
+        qk_norm_rope_append_kernel<TX, TW, TC><<<grid, warps * 32, smem, stream>>>(
             (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
             (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
             block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
@@ -292,6 +376,12 @@ CHIBI_API int chibi_swiglu(const void* gate_up, int x_type, void* out, int out_t
 {
     if (rows <= 0)
         return CHIBI_OK;
+    if (x_type == CHIBI_BF16 && out_type == CHIBI_BF16 && inter % 8 == 0 && rows <= 65535
+        && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const dim3 grid((unsigned)((inter / 8 + 255) / 256), (unsigned)rows);
+        swiglu_bf16x8_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
         swiglu_kernel<TX, TO><<<grid_for(rows * inter, 256), 256, 0, stream>>>(
             (const TX*)gate_up, (TO*)out, rows, inter);

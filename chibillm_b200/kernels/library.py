@@ -29,7 +29,7 @@ _SIGNATURES = {
         "chibi_gemm_bf16_splits": [I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
-        "chibi_sample": [P, L, L, I, P, P, P, P],
+        "chibi_sample": [P, L, L, I, P, P, P, P, L, P],
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],

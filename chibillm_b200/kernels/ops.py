@@ -337,7 +337,9 @@ class CudaKernels:
         for t in (temperature, uniform):
             if t is not None and (t.dtype != torch.float32 or t.numel() != logits.shape[0]):
                 raise KernelError("sample: temperature / uniform must be float32 [R]")
-        self.launches += 1
+        scratch = self._scratch(logits.shape[0] * 128) if temperature is None else None
+        self.launches += 2 if temperature is None else 1
         _check(self.lib.chibi_sample(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
-                                     _ptr(temperature), _ptr(uniform), _ptr(out), self._stream()),
+                                     _ptr(temperature), _ptr(uniform), _ptr(out), _ptr(scratch),
+                                     scratch.numel() if scratch is not None else 0, self._stream()),
                "sample")
