@@ -29,6 +29,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                          long long tokens, int nq, int nkv, int d, int page_size, int num_pages,
                          float scale, int window, int* __restrict__ error)
 {
+    pdl_enter();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long job = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -131,7 +132,7 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
         return CHIBI_ERR_UNSUPPORTED;
     const size_t smem = (size_t)warps * d * sizeof(float);
     CHIBI_DISPATCH_TYPE(q_type, TQ, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-        attention_generic_kernel<TQ, TC><<<(unsigned)blocks, warps * 32, smem, stream>>>(
+        launch(attention_generic_kernel<TQ, TC>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 
             (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
             table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, page_size,
             num_pages, scale, window, error);

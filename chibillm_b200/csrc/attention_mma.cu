@@ -252,6 +252,7 @@ constexpr size_t DEC_SMEM = DEC_SMEM_PIPE > DEC_SMEM_MERGE ? DEC_SMEM_PIPE : DEC
 
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p)
 {
+    pdl_enter();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* pipe = q_tile + DEC_Q_ELEMS;
@@ -380,6 +381,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
 // Merges the key ranges of one (sequence, head): one block of D threads.
 __global__ void attn_decode_merge_kernel(const AttnParams p)
 {
+    pdl_enter();
     const int seq = blockIdx.y, head = blockIdx.x, c = threadIdx.x;
     const int t = p.q_start[seq];
     if (p.q_start[seq + 1] - t != 1)
@@ -407,6 +409,7 @@ constexpr size_t PRE_SMEM = (size_t)(PRE_ROWS * DPAD + 2 * 2 * PRE_KEYS * DPAD) 
 
 __global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const AttnParams p)
 {
+    pdl_enter();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* kv = q_tile + PRE_ROWS * DPAD;        // [stage][K | V][PRE_KEYS][DPAD]
@@ -584,12 +587,12 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
         }
         const int row_blocks = (p.group + 15) / 16;
         const dim3 grid(splits, nkv * row_blocks, seqs);
-        attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(p);
+        launch(attn_decode_kernel, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, p);
         int st = launch_status();
         if (st != CHIBI_OK)
             return st;
         if (splits > 1) {
-            attn_decode_merge_kernel<<<dim3(nq, seqs), D, 0, stream>>>(p);
+            launch(attn_decode_merge_kernel, dim3(dim3(nq, seqs)), dim3(D), 0, stream, p);
             st = launch_status();
             if (st != CHIBI_OK)
                 return st;
@@ -598,7 +601,7 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     if (mode & 2) {
         const long long rows = (long long)max_q_len * p.group;
         const dim3 grid((unsigned)((rows + PRE_ROWS - 1) / PRE_ROWS), nkv, seqs);
-        attn_prefill_kernel<<<grid, PRE_WARPS * 32, PRE_SMEM, stream>>>(p);
+        launch(attn_prefill_kernel, dim3(grid), dim3(PRE_WARPS * 32), PRE_SMEM, stream, p);
         return launch_status();
     }
     return CHIBI_OK;

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 // Element type codes used by every C entry point.
 #define CHIBI_F32 0
@@ -84,6 +85,93 @@ __device__ __forceinline__ float block_max(float v, float* scratch)
     }
     __syncthreads();
     return scratch[32];
+}
+
+// Programmatic dependent launch: a kernel lets the next kernel of its stream be
+// scheduled as soon as all of its own CTAs run (pdl_trigger), and the next
+// kernel waits (pdl_wait) for this one to finish, with its writes visible,
+// before it touches global memory.  That hides the launch latency between the
+// many short kernels of a decode step.  Both instructions do nothing in a kernel
+// that was launched without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter()
+{
+    pdl_trigger();
+    pdl_wait();
+}
+
+// CHIBI_PDL=0 in the environment launches every kernel the ordinary way.
+inline bool pdl_enabled()
+{
+    static const bool on = [] {
+        const char* v = getenv("CHIBI_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
+// Launches with a thread-block cluster of (1, 1, cluster_z) CTAs when cluster_z > 1.
+template <typename... KArgs, typename... Args>
+inline void launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                           cudaStream_t stream, int cluster_z, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Launches with a thread-block cluster of (cluster_x, 1, 1) CTAs.
+template <typename... KArgs, typename... Args>
+inline void launch_cluster_x(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, int cluster_x, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                   Args&&... args)
+{
+    launch_cluster(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 inline int launch_status()

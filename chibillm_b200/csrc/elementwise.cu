@@ -15,6 +15,7 @@ template <typename TW, typename TO>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              TO* __restrict__ out, int hidden, int vocab, int* __restrict__ error)
 {
+    pdl_enter();
     const int t = blockIdx.x;
     const int id = tokens[t];
     const bool ok = id >= 0 && id < vocab;
@@ -34,6 +35,7 @@ __global__ void rmsnorm_kernel(const TX* x, const TW* __restrict__ w, TO* out,  
                                int n, long long x_stride,
                                long long out_stride, float eps, float offset)
 {
+    pdl_enter();
     __shared__ float scratch[33];
     const TX* row = x + (size_t)blockIdx.x * x_stride;
     TO* dst = out + (size_t)blockIdx.x * out_stride;
@@ -56,6 +58,7 @@ __global__ void __launch_bounds__(512)
 rmsnorm_f32_bf16_kernel(const float* x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* out, int n,
                         long long x_stride, long long out_stride, float eps, float offset)
 {
+    pdl_enter();
     __shared__ float scratch[33];
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * x_stride);
     __nv_bfloat16* dst = out + (size_t)blockIdx.x * out_stride;
@@ -111,6 +114,7 @@ __global__ void qk_norm_rope_append_kernel(
     int nkv, int d, int rot, int page_size, int num_pages, float eps, float norm_offset, int append,
     int* __restrict__ error)
 {
+    pdl_enter();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,12 +198,154 @@ __global__ void qk_norm_rope_append_kernel(
     }
 }
 
+// The same with four features per lane (d a multiple of 4) and, optionally, the
+// input given as the partial sums of a split matrix product: `splits` arrays of
+// 32-bit [tokens, row stride], `split_stride` values apart, added in split order.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4])
+    {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4])
+    {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4])
+    {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4])
+    {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 q;
+        q.x = *reinterpret_cast<const uint32_t*>(&a);
+        q.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = q;
+    }
+};
+
+template <typename TX, typename TQ, typename TW, typename TC>
+__global__ void qk_norm_rope_append_vec4_kernel(
+    const TX* __restrict__ qkv, long long qkv_stride, int splits, long long split_stride,
+    TQ* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+    const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
+    const int* __restrict__ block_table, int table_stride, int nq, int nkv, int d, int rot,
+    int page_size, int num_pages, float eps, float norm_offset, int append, int* __restrict__ error)
+{
+    pdl_enter();
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    const int half = rot >> 1;
+    float* cs = smem;
+    float* buf = smem + 2 * half + (size_t)warp * d;
+    const int pos = positions[t];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float a = (float)pos * inv_freq[j];
+        cs[j] = cosf(a);
+        cs[half + j] = sinf(a);
+    }
+    __syncthreads();
+    const int jobs = append ? nq + 2 * nkv : nq;
+    const int job = blockIdx.y * warps + warp;
+    if (job >= jobs)
+        return;
+    const TX* src = qkv + (size_t)t * qkv_stride + (size_t)job * d;
+    const bool is_q = job < nq;
+    const bool is_k = !is_q && job < nq + nkv;
+    const int head = is_q ? job : (is_k ? job - nq : job - nq - nkv);
+    long long cache_base = -1;
+    if (!is_q) {
+        const int seq = seq_of_token[t];
+        const int table_row = seq_rows ? seq_rows[seq] : seq;
+        const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && error)
+                atomicExch(error, 2);
+            return;
+        }
+        cache_base = (((long long)page * nkv + head) * page_size + (pos % page_size)) * d;
+    }
+    float s = 0.f;
+    for (int j = lane * 4; j < d; j += 128) {
+        float v[4];
+        Vec4<TX>::load(src + j, v);
+        for (int sp0 = 1; sp0 < splits; sp0 += 8) {          // eight loads in flight, added in split order
+            float q[8][4];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (sp0 + u < splits)
+                    Vec4<TX>::load(src + (sp0 + u) * split_stride + j, q[u]);
+                else
+                    q[u][0] = q[u][1] = q[u][2] = q[u][3] = 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                v[0] += q[u][0]; v[1] += q[u][1]; v[2] += q[u][2]; v[3] += q[u][3];
+            }
+        }
+        if (!is_q && !is_k) {
+            Vec4<TC>::store(v_cache + cache_base + j, v);
+        } else {
+            buf[j] = v[0]; buf[j + 1] = v[1]; buf[j + 2] = v[2]; buf[j + 3] = v[3];
+            s = fmaf(v[0], v[0], s);
+            s = fmaf(v[1], v[1], s);
+            s = fmaf(v[2], v[2], s);
+            s = fmaf(v[3], v[3], s);
+        }
+    }
+    if (!is_q && !is_k)
+        return;
+    const TW* w = is_q ? q_norm_w : k_norm_w;
+    s = warp_sum(s);
+    __syncwarp();
+    if (w) {
+        const float inv = rsqrtf(s / (float)d + eps);
+        for (int j = lane; j < d; j += 32)
+            buf[j] = (buf[j] * inv) * (to_f32(w[j]) + norm_offset);
+        __syncwarp();
+    }
+    float lo[4], hi[4];
+    int cnt = 0;
+    for (int j = lane; j < half; j += 32, ++cnt) {
+        const float c = cs[j], sn = cs[half + j];
+        const float x0 = buf[j], x1 = buf[j + half];
+        lo[cnt] = x0 * c - x1 * sn;
+        hi[cnt] = x1 * c + x0 * sn;
+    }
+    __syncwarp();
+    cnt = 0;
+    for (int j = lane; j < half; j += 32, ++cnt) {
+        buf[j] = lo[cnt];
+        buf[j + half] = hi[cnt];
+    }
+    __syncwarp();
+    for (int j = lane * 4; j < d; j += 128) {
+        const float v[4] = { buf[j], buf[j + 1], buf[j + 2], buf[j + 3] };
+        if (is_q)
+            Vec4<TQ>::store(q_out + ((size_t)t * nq + head) * d + j, v);
+        else
+            Vec4<TC>::store(k_cache + cache_base + j, v);
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // gate_up[t, 0:I] = gate, gate_up[t, I:2I] = up; out = gate / (1 + exp(-gate)) * up.
 template <typename TX, typename TO>
 __global__ void swiglu_kernel(const TX* __restrict__ gate_up, TO* __restrict__ out, long long rows,
                               int inter)
 {
+    pdl_enter();
     const long long total = rows * inter;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -215,6 +361,7 @@ __global__ void swiglu_kernel(const TX* __restrict__ gate_up, TO* __restrict__ o
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
                                      __nv_bfloat16* __restrict__ out, int inter)
 {
+    pdl_enter();
     const int chunks = inter >> 3;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= chunks)
@@ -239,6 +386,7 @@ template <typename TX, typename TO>
 __global__ void gather_rows_kernel(const TX* __restrict__ x, const int* __restrict__ rows,
                                    TO* __restrict__ out, int n, long long x_rows)
 {
+    pdl_enter();
     const int r = rows[blockIdx.x];
     const bool ok = r >= 0 && r < x_rows;
     for (int j = threadIdx.x; j < n; j += blockDim.x)
@@ -249,6 +397,7 @@ __global__ void gather_rows_kernel(const TX* __restrict__ x, const int* __restri
 template <typename TX, typename TO>
 __global__ void cast_kernel(const TX* __restrict__ x, TO* __restrict__ out, long long total)
 {
+    pdl_enter();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x)
         out[i] = from_f32<TO>(to_f32(x[i]));
@@ -258,6 +407,7 @@ __global__ void cast_kernel(const TX* __restrict__ x, TO* __restrict__ out, long
 template <typename TX>
 __global__ void add_into_kernel(float* __restrict__ acc, const TX* __restrict__ x, long long total)
 {
+    pdl_enter();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x)
         acc[i] += to_f32(x[i]);
@@ -268,6 +418,7 @@ __global__ void apply_table_updates_kernel(int* __restrict__ table, int table_st
                                            const int* __restrict__ updates, int capacity,
                                            int* __restrict__ error)
 {
+    pdl_enter();
     int n = updates[0];
     if (n > capacity) {
         n = capacity;
@@ -307,7 +458,7 @@ CHIBI_API int chibi_embed(const int* tokens, const void* table, int table_type, 
         return CHIBI_OK;
     const int block = hidden >= 1024 ? 256 : 128;
     CHIBI_DISPATCH_TYPE(table_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        embed_kernel<TW, TO><<<(unsigned)rows, block, 0, stream>>>(
+        launch(embed_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream, 
             tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
     }));
     return launch_status();
@@ -331,13 +482,13 @@ CHIBI_API int chibi_rmsnorm(const void* x, int x_type, const void* w, int w_type
             fast <<= 1;
         if (fast < 128 && n >= 512)
             fast = 128;
-        rmsnorm_f32_bf16_kernel<<<(unsigned)groups, fast, 0, stream>>>(
+        launch(rmsnorm_f32_bf16_kernel, dim3((unsigned)groups), dim3(fast), 0, stream, 
             (const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n, x_stride, out_stride, eps,
             offset);
         return launch_status();
     }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        rmsnorm_kernel<TX, TW, TO><<<(unsigned)groups, block, 0, stream>>>(
+        launch(rmsnorm_kernel<TX, TW, TO>, dim3((unsigned)groups), dim3(block), 0, stream, 
             (const TX*)x, (const TW*)w, (TO*)out, n, x_stride, out_stride, eps, offset);
     })));
     return launch_status();
@@ -361,13 +512,57 @@ CHIBI_API int chibi_qk_norm_rope_append(
     const dim3 grid((unsigned)tokens, (unsigned)((jobs + warps - 1) / warps));
     if (tokens > 2147483647LL || grid.y > 65535)
         return CHIBI_ERR_UNSUPPORTED;
+    const bool aligned = d % 4 == 0 && qkv_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(q_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
+    if (aligned) {
+        CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
+            launch(qk_norm_rope_append_vec4_kernel<TX, TX, TW, TC>, dim3(grid), dim3(warps * 32), smem, stream, 
+                (const TX*)qkv, qkv_stride, 1, 0, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
+                (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
+                block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
+                append, error);
+        })));
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-        qk_norm_rope_append_kernel<TX, TW, TC><<<grid, warps * 32, smem, stream>>>(
+        launch(qk_norm_rope_append_kernel<TX, TW, TC>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
             (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
             block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
             append, error);
     })));
+    return launch_status();
+}
+
+// The same on the partial sums of a split matrix product ([splits][tokens][width]
+// 32-bit); q_out and the caches are bfloat16.
+CHIBI_API int chibi_qk_norm_rope_append_partial(
+    const float* partial, int splits, long long tokens, long long width, void* q_out, void* k_cache,
+    void* v_cache, const void* q_norm_w, const void* k_norm_w, int w_type, const float* inv_freq,
+    const int* positions, const int* seq_of_token, const int* seq_rows, const int* block_table,
+    int table_stride, int nq, int nkv, int d, int rot, int page_size, int num_pages, float eps,
+    float norm_offset, int append, int* error, cudaStream_t stream)
+{
+    if (tokens <= 0)
+        return CHIBI_OK;
+    if (d <= 0 || d > 256 || d % 4 != 0 || rot < 0 || rot > d || (rot & 1) || width % 4 != 0
+        || splits < 1 || (reinterpret_cast<uintptr_t>(partial) & 15))
+        return CHIBI_ERR_UNSUPPORTED;
+    const int jobs = append ? nq + 2 * nkv : nq;
+    const int warps = jobs < 8 ? jobs : 8;
+    const size_t smem = (size_t)(warps * d + rot) * sizeof(float);
+    const dim3 grid((unsigned)tokens, (unsigned)((jobs + warps - 1) / warps));
+    if (tokens > 65535 || grid.y > 65535)
+        return CHIBI_ERR_UNSUPPORTED;
+    CHIBI_DISPATCH_TYPE(w_type, TW, {
+        launch(qk_norm_rope_append_vec4_kernel<float, __nv_bfloat16, TW, __nv_bfloat16>, dim3(grid),
+               dim3(warps * 32), smem, stream,
+                partial, width, splits, tokens * width, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                (__nv_bfloat16*)v_cache, (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions,
+                seq_of_token, seq_rows, block_table, table_stride, nq, nkv, d, rot, page_size, num_pages,
+                eps, norm_offset, append, error);
+    });
     return launch_status();
 }
 
@@ -379,11 +574,11 @@ CHIBI_API int chibi_swiglu(const void* gate_up, int x_type, void* out, int out_t
     if (x_type == CHIBI_BF16 && out_type == CHIBI_BF16 && inter % 8 == 0 && rows <= 65535
         && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
         const dim3 grid((unsigned)((inter / 8 + 255) / 256), (unsigned)rows);
-        swiglu_bf16x8_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+        launch(swiglu_bf16x8_kernel, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
         return launch_status();
     }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        swiglu_kernel<TX, TO><<<grid_for(rows * inter, 256), 256, 0, stream>>>(
+        launch(swiglu_kernel<TX, TO>, dim3(grid_for(rows * inter, 256)), dim3(256), 0, stream, 
             (const TX*)gate_up, (TO*)out, rows, inter);
     }));
     return launch_status();
@@ -396,7 +591,7 @@ CHIBI_API int chibi_gather_rows(const void* x, int x_type, const int* rows, void
     if (count <= 0)
         return CHIBI_OK;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        gather_rows_kernel<TX, TO><<<(unsigned)count, 256, 0, stream>>>(
+        launch(gather_rows_kernel<TX, TO>, dim3((unsigned)count), dim3(256), 0, stream, 
             (const TX*)x, rows, (TO*)out, n, x_rows);
     }));
     return launch_status();
@@ -408,7 +603,7 @@ CHIBI_API int chibi_cast(const void* x, int x_type, void* out, int out_type, lon
     if (total <= 0)
         return CHIBI_OK;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        cast_kernel<TX, TO><<<grid_for(total, 256), 256, 0, stream>>>((const TX*)x, (TO*)out, total);
+        launch(cast_kernel<TX, TO>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const TX*)x, (TO*)out, total);
     }));
     return launch_status();
 }
@@ -419,7 +614,7 @@ CHIBI_API int chibi_add_into(float* acc, const void* x, int x_type, long long to
     if (total <= 0)
         return CHIBI_OK;
     CHIBI_DISPATCH_TYPE(x_type, TX, {
-        add_into_kernel<TX><<<grid_for(total, 256), 256, 0, stream>>>(acc, (const TX*)x, total);
+        launch(add_into_kernel<TX>, dim3(grid_for(total, 256)), dim3(256), 0, stream, acc, (const TX*)x, total);
     });
     return launch_status();
 }
@@ -431,7 +626,7 @@ CHIBI_API int chibi_apply_table_updates(int* table, int table_stride, int table_
     if (capacity <= 0)
         return CHIBI_OK;
     const int blocks = capacity > 4096 ? 16 : 1;
-    apply_table_updates_kernel<<<blocks, 256, 0, stream>>>(table, table_stride, table_rows, updates,
+    launch(apply_table_updates_kernel, dim3(blocks), dim3(256), 0, stream, table, table_stride, table_rows, updates,
                                                            capacity, error);
     return launch_status();
 }

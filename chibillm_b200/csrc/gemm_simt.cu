@@ -17,6 +17,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
                  const float* __restrict__ residual, int M, int N, int K, long long x_stride,
                  long long w_stride, long long out_stride, long long res_stride)
 {
+    pdl_enter();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -99,7 +100,7 @@ CHIBI_API int chibi_gemm_simt(const void* x, int x_type, const void* w, int w_ty
     if (grid.y > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        gemm_simt_kernel<TX, TW, TO><<<grid, 256, 0, stream>>>(
+        launch(gemm_simt_kernel<TX, TW, TO>, dim3(grid), dim3(256), 0, stream, 
             (const TX*)x, (const TW*)w, (TO*)out, residual, M, N, K, x_stride, w_stride,
             out_stride, res_stride);
     })));

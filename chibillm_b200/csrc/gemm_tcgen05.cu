@@ -38,7 +38,11 @@ struct GemmParams {
     long long out_stride;
     const float* residual;
     long long res_stride;
-    float* partial;        // [splits][M][N] when the K range is split, else null
+    float* partial;        // [splits][M][N] when the K range is split through global memory, else null
+    int cluster;           // > 0: swapped operands, the gridDim.z CTAs of a cluster add their partial
+                           // sums through distributed shared memory (1 = a cluster of one)
+    int swiglu;            // the rows of w come in blocks of 64 gate rows then 64 up rows; out[M, N / 2] =
+                           // silu(gate) * up
     int* error;
 };
 
@@ -66,6 +70,7 @@ __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b, const GemmParams p)
 {
+    pdl_trigger();
     using S = GemmSmem<BN>;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -105,11 +110,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
             tma_prefetch_descriptor(&map_a);
             tma_prefetch_descriptor(&map_b);
-            for (int i = 0; i < kb_count; ++i) {
+            // The weights do not depend on the kernel before this one: their first
+            // tiles are on their way before we wait for it.  (Weights are the A
+            // operand when the operands are swapped, else the B operand.)
+            const int early = kb_count < STAGES ? kb_count : STAGES;
+            for (int i = 0; i < early; ++i) {
+                uint8_t* a_dst = smem + i * S::STAGE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[i], S::STAGE_BYTES);
+                const int k = (kb_begin + i) * TILE_K;
+                if (p.swap)
+                    tma_load_2d(a_dst, &map_a, &full_bar[i], k, tile_a * TILE_A);
+                else
+                    tma_load_2d(a_dst + S::A_BYTES, &map_b, &full_bar[i], k, tile_b * BN);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i) {
+                uint8_t* a_dst = smem + i * S::STAGE_BYTES;
+                const int k = (kb_begin + i) * TILE_K;
+                if (p.swap)
+                    tma_load_2d(a_dst + S::A_BYTES, &map_b, &full_bar[i], k, tile_b * BN);
+                else
+                    tma_load_2d(a_dst, &map_a, &full_bar[i], k, tile_a * TILE_A);
+            }
+            for (int i = early; i < kb_count; ++i) {
                 const int s = i % STAGES;
                 const uint32_t round = i / STAGES;
-                if (round > 0)
-                    mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 11);
+                mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 11);
                 uint8_t* a_dst = smem + s * S::STAGE_BYTES;
                 uint8_t* b_dst = a_dst + S::A_BYTES;
                 mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
@@ -143,10 +169,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int quarter = warp & 3;
         const int a_row = tile_a * TILE_A + quarter * 32 + lane;
         bool ok = true;
+        pdl_wait();        // before this warp reads or writes global memory
         if (kb_count > 0)
             ok = mbar_wait(tmem_full_bar, 0, p.error, 13);
         tcgen05_fence_after();
         constexpr int CHUNK = BN < 32 ? 16 : 32;
+        if (p.cluster > 0) {
+            // this CTA's partial sums -> shared memory, [column][row] (the stages are free now)
+            float* part = reinterpret_cast<float*>(smem);
+            const int row = quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+                uint32_t r[CHUNK];
+                if (kb_count > 0 && ok) {
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
+                    if constexpr (CHUNK == 32)
+                        tmem_load_32x32(taddr, r);
+                    else
+                        tmem_load_32x16(taddr, r);
+                    tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CHUNK; ++j)
+                        r[j] = 0;
+                }
+#pragma unroll
+                for (int j = 0; j < CHUNK; ++j)
+                    part[(c0 + j) * TILE_A + row] = __uint_as_float(r[j]);
+            }
+        } else if (p.swiglu) {
+            // x is the A operand: this thread has row m and the BN columns of w's rows, which come
+            // as [64 gate | 64 up] blocks
+            const int m = a_row;
+            if constexpr (BN >= 128) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if ((c0 & 64) != 0)
+                        continue;                       // the up halves are read with their gate halves
+                    uint32_t g[32], u[32];
+                    if (kb_count > 0 && ok) {
+                        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
+                        tmem_load_32x32(taddr, g);
+                        tmem_load_32x32(taddr + 64, u);
+                        tmem_load_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            g[j] = u[j] = 0;
+                    }
+                    // w rows tile_b * BN + c0 .. are gate rows of feature (tile_b * BN + c0) / 2 + (c0 % 64)
+                    const int w_row = tile_b * BN + c0;
+                    const int feat0 = (w_row >> 7) * 64 + (w_row & 63);
+                    const int inter = p.N >> 1;
+                    if (m < p.M) {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + feat0;
+                        if (feat0 + 32 <= inter && p.out_stride % 8 == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 h[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const float g0 = __uint_as_float(g[8 * j + 2 * q]), g1 = __uint_as_float(g[8 * j + 2 * q + 1]);
+                                    const float u0 = __uint_as_float(u[8 * j + 2 * q]), u1 = __uint_as_float(u[8 * j + 2 * q + 1]);
+                                    h[q] = __floats2bfloat162_rn((g0 / (1.f + expf(-g0))) * u0, (g1 / (1.f + expf(-g1))) * u1);
+                                }
+                                reinterpret_cast<uint4*>(dst)[j] = *reinterpret_cast<uint4*>(h);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (feat0 + j < inter) {
+                                    const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                                    dst[j] = __float2bfloat16_rn((gv / (1.f + expf(-gv))) * uv);
+                                }
+                        }
+                    }
+                }
+            }
+        } else
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CHUNK) {
             uint32_t r[CHUNK];
@@ -214,6 +313,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
         }
     }
+    if (p.cluster > 0) {
+        // Add the cluster's partial sums: CTA `rank` takes the rows (or gate/up pairs) whose index is
+        // rank modulo the cluster size and reads them from every CTA, in rank order.
+        const int csize = gridDim.z;
+        cluster_sync();
+        if (warp >= 2) {
+            const uint32_t rank = cluster_cta_rank();
+            const uint32_t part_addr = smem_addr(smem);
+            const int et = threadIdx.x - 64;                       // 0 .. 127
+            const int units = p.swiglu ? 64 : TILE_A;              // rows, or gate/up pairs
+            const int mine = (units - (int)rank + csize - 1) / csize;
+            for (int e = et; e < mine * BN; e += 128) {
+                const int c = e / mine, row = (int)rank + (e - c * mine) * csize;
+                const int m = tile_b * BN + c;
+                // all loads first (they are independent), then the sums in rank order
+                float pv[16], pu[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    pv[j] = j < csize ? ld_peer_shared_f32(part_addr + (uint32_t)(c * TILE_A + row) * 4, j) : 0.f;
+                    pu[j] = (p.swiglu && j < csize)
+                        ? ld_peer_shared_f32(part_addr + (uint32_t)(c * TILE_A + 64 + row) * 4, j) : 0.f;
+                }
+                float v = 0.f, u = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    v += pv[j];
+                    u += pu[j];
+                }
+                if (p.swiglu) {
+                    const int feat = tile_a * 64 + row;
+                    if (m < p.M && feat < (p.N >> 1))
+                        static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + feat] =
+                            __float2bfloat16_rn((v / (1.f + expf(-v))) * u);
+                } else {
+                    store_value(p, m, tile_a * TILE_A + row, v);
+                }
+            }
+        }
+        cluster_sync();          // nobody leaves while its shared memory may still be read
+    }
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -227,6 +366,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
                                      int out_type, long long out_stride, const float* residual,
                                      long long res_stride, int M, int N)
 {
+    pdl_enter();
     const long long total = (long long)M * N;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -320,7 +460,7 @@ static bool tensor_map_2d(const void* ptr, long long rows, long long cols, long 
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
-                       cudaStream_t stream)
+                       cudaStream_t stream, int cluster_z = 1)
 {
     constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
@@ -331,7 +471,16 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
             return (int)e;
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, stream>>>(ma, mb, p);
+    static bool wide_clusters = false;
+    if (cluster_z > 8 && !wide_clusters) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
+                                                   cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess)
+            return (int)e;
+        wide_clusters = true;
+    }
+    launch_cluster(gemm_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, stream, cluster_z,
+                   ma, mb, p);
     return launch_status();
 }
 
@@ -341,6 +490,25 @@ using namespace chibi;
 
 // How many K splits chibi_gemm_bf16 would use (0: it does not take the shape),
 // so that a caller can size the scratch array: splits * M * N floats.
+static int sm_count()
+{
+    static int count = 0;
+    if (count == 0) {
+        int device = 0, n = 0;
+        if (cudaGetDevice(&device) == cudaSuccess
+            && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && n > 0)
+            count = n;
+        else
+            return 148;
+    }
+    return count;
+}
+
+// For few rows (M <= 64) the K range is split so that the CTAs of one launch
+// fill the SMs once, evenly: with three stages four CTAs of the 16-token variant
+// (three of the wider ones) fit an SM.  The partial sums must stay a small part
+// of the traffic (they are written and read once, 8 bytes per value, against
+// 2 N K bytes of weights), and a split has at least two K blocks.
 CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K)
 {
     if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0)
@@ -349,12 +517,15 @@ CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K)
         return 1;
     const int tiles = (N + TILE_A - 1) / TILE_A;
     const int k_blocks = (K + TILE_K - 1) / TILE_K;
-    int splits = (2 * 148 + tiles - 1) / tiles;
-    const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
-    if (splits > most)
-        splits = most;
-    if (splits > 16)
-        splits = 16;
+    const int resident = sm_count() * (M <= 16 ? 4 : 3);
+    int splits = tiles >= resident ? 1 : resident / tiles;
+    const int traffic_cap = (int)(0.15 * K / (4.0 * M));
+    if (splits > traffic_cap)
+        splits = traffic_cap;
+    if (splits > k_blocks / 2)
+        splits = k_blocks / 2;
+    if (splits > 24)
+        splits = 24;
     if (splits < 1)
         splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
@@ -363,11 +534,11 @@ CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K)
 
 // Returns CHIBI_ERR_UNSUPPORTED for shapes or alignments it does not take; the
 // caller then uses the plain kernel.
-CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_type,
-                              const float* residual, int M, int N, int K, long long x_stride,
-                              long long w_stride, long long out_stride, long long res_stride,
-                              float* scratch, long long scratch_floats, int* error,
-                              cudaStream_t stream)
+static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
+                         const float* residual, int M, int N, int K, long long x_stride,
+                         long long w_stride, long long out_stride, long long res_stride,
+                         float* scratch, long long scratch_floats, int* error, cudaStream_t stream,
+                         bool reduce)
 {
     if (M <= 0 || N <= 0)
         return CHIBI_OK;
@@ -414,11 +585,11 @@ CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_t
             return CHIBI_ERR_UNSUPPORTED;
         const dim3 grid((N + TILE_A - 1) / TILE_A, 1, splits);
         if (bn == 16)
-            status = launch_gemm<16, 6>(ma, mb, p, grid, stream);
+            status = launch_gemm<16, 3>(ma, mb, p, grid, stream);
         else if (bn == 32)
-            status = launch_gemm<32, 5>(ma, mb, p, grid, stream);
+            status = launch_gemm<32, 3>(ma, mb, p, grid, stream);
         else
-            status = launch_gemm<64, 4>(ma, mb, p, grid, stream);
+            status = launch_gemm<64, 3>(ma, mb, p, grid, stream);
     } else {
         p.swap = 0;
         p.rows_a = M;
@@ -438,16 +609,357 @@ CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_t
     }
     if (status != CHIBI_OK)
         return status;
-    if (splits > 1) {
+    if (splits > 1 && reduce) {
         const long long total = (long long)M * N;
         int blocks = (int)((total + 255) / 256);
         if (blocks > 148 * 8)
             blocks = 148 * 8;
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(scratch, splits, out, out_type, out_stride,
+        launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, scratch, splits, out, out_type, out_stride,
                                                          residual, res_stride, M, N);
         return launch_status();
     }
     return CHIBI_OK;
+}
+
+CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_type,
+                              const float* residual, int M, int N, int K, long long x_stride,
+                              long long w_stride, long long out_stride, long long res_stride,
+                              float* scratch, long long scratch_floats, int* error,
+                              cudaStream_t stream)
+{
+    return gemm_bf16_impl(x, w, out, out_type, residual, M, N, K, x_stride, w_stride, out_stride,
+                          res_stride, scratch, scratch_floats, error, stream, true);
+}
+
+// How many CTAs share one tile's K range in chibi_gemm_bf16_fused (1 for M > 64).
+CHIBI_API int chibi_gemm_bf16_cluster_size(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || M > 64)
+        return 1;
+    const int tiles = (N + TILE_A - 1) / TILE_A;
+    const int k_blocks = (K + TILE_K - 1) / TILE_K;
+    const int resident = sm_count() * (M <= 16 ? 4 : 3);
+    int size = tiles >= resident ? 1 : resident / tiles;
+    static const int cap = [] {
+        const char* v = getenv("CHIBI_MAX_CLUSTER");
+        const int n = v ? atoi(v) : 16;
+        return n < 1 ? 1 : (n > 16 ? 16 : n);
+    }();
+    if (size > cap)
+        size = cap;
+    if (size > k_blocks / 2)
+        size = k_blocks / 2;
+    return size < 1 ? 1 : size;
+}
+
+// out = x * w^T with what follows it done in the same kernel: + residual, or
+// (epilogue 1) SwiGLU over w's rows arranged as blocks of 64 gate rows followed
+// by their 64 up rows (out is then [M, N / 2], bfloat16).  For M <= 64 the K range
+// of a tile is shared by the CTAs of a thread-block cluster, which add their
+// partial sums through distributed shared memory in a fixed order: no scratch in
+// global memory and no second kernel.
+CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int out_type,
+                                    const float* residual, int M, int N, int K, long long x_stride,
+                                    long long w_stride, long long out_stride, long long res_stride,
+                                    int epilogue, int* error, cudaStream_t stream)
+{
+    if (M <= 0 || N <= 0)
+        return CHIBI_OK;
+    if (K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
+        || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
+        || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
+        return CHIBI_ERR_UNSUPPORTED;
+    if (out_type != CHIBI_F32 && out_type != CHIBI_BF16)
+        return CHIBI_ERR_ARGUMENT;
+    if (epilogue == 1 && (N % 128 != 0 || out_type != CHIBI_BF16 || residual))
+        return CHIBI_ERR_UNSUPPORTED;
+    GemmParams p {};
+    p.K = K;
+    p.M = M;
+    p.N = N;
+    p.out = out;
+    p.out_type = out_type;
+    p.out_stride = out_stride;
+    p.residual = residual;
+    p.res_stride = res_stride;
+    p.error = error;
+    p.swiglu = epilogue == 1 ? 1 : 0;
+    p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
+    CUtensorMap ma, mb;
+    if (M <= 64) {
+        const int size = chibi_gemm_bf16_cluster_size(M, N, K);
+        p.k_blocks_per_split = (p.k_blocks_total + size - 1) / size;
+        const int used = (p.k_blocks_total + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        p.swap = 1;
+        p.cluster = used;
+        p.rows_a = N;
+        p.rows_b = M;
+        if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &ma) || !tensor_map_2d(x, M, K, x_stride, bn, &mb))
+            return CHIBI_ERR_UNSUPPORTED;
+        const dim3 grid((N + TILE_A - 1) / TILE_A, 1, used);
+        if (bn == 16)
+            return launch_gemm<16, 3>(ma, mb, p, grid, stream, used);
+        if (bn == 32)
+            return launch_gemm<32, 3>(ma, mb, p, grid, stream, used);
+        return launch_gemm<64, 3>(ma, mb, p, grid, stream, used);
+    }
+    p.k_blocks_per_split = p.k_blocks_total;
+    p.swap = 0;
+    p.rows_a = M;
+    p.rows_b = N;
+    const int bn = N >= 256 ? 256 : (N > 64 || p.swiglu ? 128 : 64);
+    if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
+        return CHIBI_ERR_UNSUPPORTED;
+    const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
+    if (grid.y > 65535)
+        return CHIBI_ERR_UNSUPPORTED;
+    if (bn == 256)
+        return launch_gemm<256, 4>(ma, mb, p, grid, stream);
+    if (bn == 128)
+        return launch_gemm<128, 4>(ma, mb, p, grid, stream);
+    return launch_gemm<64, 4>(ma, mb, p, grid, stream);
+}
+
+// The first half only, for shapes that chibi_gemm_bf16_splits splits (> 1): the
+// partial sums [splits][M][N] stay in `scratch` for a kernel that adds them up
+// together with what follows the product (chibi_reduce_* below and elsewhere).
+CHIBI_API int chibi_gemm_bf16_partial(const void* x, const void* w, int M, int N, int K,
+                                      long long x_stride, long long w_stride, float* scratch,
+                                      long long scratch_floats, int* error, cudaStream_t stream)
+{
+    if (chibi_gemm_bf16_splits(M, N, K) <= 1 || (reinterpret_cast<uintptr_t>(scratch) & 15))
+        return CHIBI_ERR_UNSUPPORTED;
+    return gemm_bf16_impl(x, w, scratch, CHIBI_F32, nullptr, M, N, K, x_stride, w_stride, N, 0, scratch,
+                          scratch_floats, error, stream, false);
+}
+
+// ------------------------------------------------------------------ kernels that finish a split product
+namespace chibi {
+
+// residual[m, :] += sum over splits (in split order); then, if a norm weight is
+// given, normed[m, :] = RMSNorm(residual[m, :]).  One block per row; the row
+// stays in registers (N <= 16 * blockDim.x, N a multiple of 4).
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(512)
+reduce_residual_rmsnorm_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                               float* residual, long long res_stride, const TW* __restrict__ w,
+                               TO* __restrict__ normed, long long normed_stride, float eps, float offset)
+{
+    pdl_enter();
+    __shared__ float scratch[33];
+    const int m = blockIdx.x;
+    const int n4 = N >> 2;
+    const size_t total4 = ((size_t)M * N) >> 2;
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)m * res_stride);
+    const float4* part = reinterpret_cast<const float4*>(partial) + (size_t)m * n4;
+    float4 v[4];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        if (j < n4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp = 0; sp < splits; ++sp) {
+                const float4 q = part[(size_t)sp * total4 + j];
+                acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+            }
+            const float4 r = res[j];
+            acc.x = r.x + acc.x; acc.y = r.y + acc.y; acc.z = r.z + acc.z; acc.w = r.w + acc.w;
+            res[j] = acc;
+            v[i] = acc;
+            s = fmaf(acc.x, acc.x, s);
+            s = fmaf(acc.y, acc.y, s);
+            s = fmaf(acc.z, acc.z, s);
+            s = fmaf(acc.w, acc.w, s);
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (!w)
+        return;
+    s = block_sum(s, scratch);
+    const float inv = rsqrtf(s / (float)N + eps);
+    TO* dst = normed + (size_t)m * normed_stride;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        if (j < n4) {
+            const float o0 = (v[i].x * inv) * (to_f32(w[4 * j]) + offset);
+            const float o1 = (v[i].y * inv) * (to_f32(w[4 * j + 1]) + offset);
+            const float o2 = (v[i].z * inv) * (to_f32(w[4 * j + 2]) + offset);
+            const float o3 = (v[i].w * inv) * (to_f32(w[4 * j + 3]) + offset);
+            dst[4 * j] = from_f32<TO>(o0);
+            dst[4 * j + 1] = from_f32<TO>(o1);
+            dst[4 * j + 2] = from_f32<TO>(o2);
+            dst[4 * j + 3] = from_f32<TO>(o3);
+        }
+    }
+}
+
+// The same with a cluster of CTAs per row, each taking a run of columns (one
+// float4 per thread, the splits' loads issued eight at a time); the CTAs exchange
+// their sums of squares through distributed shared memory.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(1024)
+reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                       float* residual, long long res_stride, const TW* __restrict__ w,
+                                       TO* __restrict__ normed, long long normed_stride, float eps,
+                                       float offset)
+{
+    pdl_enter();
+    __shared__ float scratch[33];
+    __shared__ float my_sum;
+    const int m = blockIdx.y;
+    const int parts = gridDim.x;                     // CTAs per row = cluster size
+    const int n4 = N >> 2;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;   // float4 index within the row
+    const size_t total4 = ((size_t)M * N) >> 2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float s = 0.f;
+    if (j < n4) {
+        const float4* part = reinterpret_cast<const float4*>(partial) + (size_t)m * n4 + j;
+        for (int sp0 = 0; sp0 < splits; sp0 += 8) {
+            float4 q[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                q[u] = sp0 + u < splits ? part[(size_t)(sp0 + u) * total4] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                acc.x += q[u].x; acc.y += q[u].y; acc.z += q[u].z; acc.w += q[u].w;
+            }
+        }
+        float4* res = reinterpret_cast<float4*>(residual + (size_t)m * res_stride) + j;
+        const float4 r = *res;
+        acc.x = r.x + acc.x; acc.y = r.y + acc.y; acc.z = r.z + acc.z; acc.w = r.w + acc.w;
+        *res = acc;
+        s = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+    if (!w)
+        return;
+    s = block_sum(s, scratch);
+    if (threadIdx.x == 0)
+        my_sum = s;
+    cluster_sync();
+    float total = 0.f;
+    for (int r = 0; r < parts; ++r)
+        total += ld_peer_shared_f32(smem_addr(&my_sum), r);
+    cluster_sync();                                  // nobody leaves while its sum may still be read
+    const float inv = rsqrtf(total / (float)N + eps);
+    if (j < n4) {
+        TO* dst = normed + (size_t)m * normed_stride + 4 * j;
+        dst[0] = from_f32<TO>((acc.x * inv) * (to_f32(w[4 * j]) + offset));
+        dst[1] = from_f32<TO>((acc.y * inv) * (to_f32(w[4 * j + 1]) + offset));
+        dst[2] = from_f32<TO>((acc.z * inv) * (to_f32(w[4 * j + 2]) + offset));
+        dst[3] = from_f32<TO>((acc.w * inv) * (to_f32(w[4 * j + 3]) + offset));
+    }
+}
+
+// act[m, c] = silu(gate) * up with gate = sum of partial[s][m][c] and up = sum of
+// partial[s][m][I + c], in split order.  Two columns per thread.
+template <typename TO>
+__global__ void reduce_swiglu_kernel(const float* __restrict__ partial, int splits, int M, int inter,
+                                     TO* __restrict__ out, int interleaved)
+{
+    pdl_enter();
+    const int half = inter >> 1;
+    const int c2 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c2 >= half)
+        return;
+    const int m = blockIdx.y;
+    const size_t total = (size_t)M * 2 * inter;
+    const float* row = partial + (size_t)m * 2 * inter;
+    // columns of gate and up for features 2 c2, 2 c2 + 1: [gate | up], or blocks of 64 gate
+    // columns each followed by its 64 up columns
+    const int f = 2 * c2;
+    const int g_col = interleaved ? ((f >> 6) << 7) + (f & 63) : f;
+    const int u_col = interleaved ? g_col + 64 : inter + f;
+    float2 g = make_float2(0.f, 0.f), u = make_float2(0.f, 0.f);
+    for (int sp0 = 0; sp0 < splits; sp0 += 4) {
+        float2 gq[4], uq[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const bool on = sp0 + k < splits;
+            gq[k] = on ? *reinterpret_cast<const float2*>(row + (sp0 + k) * total + g_col) : make_float2(0.f, 0.f);
+            uq[k] = on ? *reinterpret_cast<const float2*>(row + (sp0 + k) * total + u_col) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            g.x += gq[k].x; g.y += gq[k].y; u.x += uq[k].x; u.y += uq[k].y;
+        }
+    }
+    out[(size_t)m * inter + 2 * c2] = from_f32<TO>((g.x / (1.f + expf(-g.x))) * u.x);
+    out[(size_t)m * inter + 2 * c2 + 1] = from_f32<TO>((g.y / (1.f + expf(-g.y))) * u.y);
+}
+
+} // namespace chibi
+
+CHIBI_API int chibi_reduce_residual_rmsnorm(const float* partial, int splits, int M, int N,
+                                            float* residual, long long res_stride, const void* w,
+                                            int w_type, void* normed, int normed_type,
+                                            long long normed_stride, float eps, float offset,
+                                            cudaStream_t stream)
+{
+    if (M <= 0)
+        return CHIBI_OK;
+    if (N % 4 != 0 || N > 16 * 512 || res_stride % 4 != 0 || splits < 1
+        || (reinterpret_cast<uintptr_t>(partial) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15))
+        return CHIBI_ERR_UNSUPPORTED;
+    // a cluster of CTAs per row when the row divides evenly into runs of 128..1024 columns
+    int parts = 0;
+    for (int cand = 8; cand >= 2; --cand)
+        if ((N / 4) % cand == 0 && N / 4 / cand >= 32 && N / 4 / cand <= 256 && (N / 4 / cand) % 32 == 0) {
+            parts = cand;
+            break;
+        }
+    if (parts > 0 && M <= 65535) {
+        const dim3 grid(parts, M);
+        const int threads = N / 4 / parts;
+        if (!w) {
+            launch_cluster_x(reduce_residual_rmsnorm_cluster_kernel<float, float>, grid, dim3(threads), 0, stream,
+                             parts, partial, splits, M, N, residual, res_stride, (const float*)nullptr,
+                             (float*)nullptr, (long long)0, eps, offset);
+            return launch_status();
+        }
+        CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(normed_type, TO, {
+            launch_cluster_x(reduce_residual_rmsnorm_cluster_kernel<TW, TO>, grid, dim3(threads), 0, stream, parts,
+                             partial, splits, M, N, residual, res_stride, (const TW*)w, (TO*)normed,
+                             normed_stride, eps, offset);
+        }));
+        return launch_status();
+    }
+    int block = 32;
+    while (block * 16 < N)
+        block <<= 1;
+    if (block < 128 && N >= 512)
+        block = 128;
+    if (!w) {
+        launch(reduce_residual_rmsnorm_kernel<float, float>, dim3(M), dim3(block), 0, stream, 
+            partial, splits, M, N, residual, res_stride, nullptr, nullptr, 0, eps, offset);
+        return launch_status();
+    }
+    CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(normed_type, TO, {
+        launch(reduce_residual_rmsnorm_kernel<TW, TO>, dim3(M), dim3(block), 0, stream, 
+            partial, splits, M, N, residual, res_stride, (const TW*)w, (TO*)normed, normed_stride, eps,
+            offset);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_reduce_swiglu(const float* partial, int splits, int M, int inter, void* out,
+                                  int out_type, int interleaved, cudaStream_t stream)
+{
+    if (M <= 0)
+        return CHIBI_OK;
+    if (inter % 2 != 0 || M > 65535 || splits < 1 || (reinterpret_cast<uintptr_t>(partial) & 7)
+        || (interleaved && inter % 64 != 0))
+        return CHIBI_ERR_UNSUPPORTED;
+    const dim3 grid((inter / 2 + 255) / 256, M);
+    CHIBI_DISPATCH_TYPE(out_type, TO, {
+        launch(reduce_swiglu_kernel<TO>, dim3(grid), dim3(256), 0, stream, partial, splits, M, inter, (TO*)out,
+               interleaved);
+    });
+    return launch_status();
 }
 
 // ------------------------------------------------------------------ no-allocation entry point

@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_slices_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int slice,
                      float* __restrict__ part_v, int* __restrict__ part_i)
 {
+    pdl_enter();
     __shared__ float sv[32];
     __shared__ int si[32];
     const int row = blockIdx.y;
@@ -75,6 +76,7 @@ argmax_slices_kernel(const float* __restrict__ logits, long long row_stride, int
 __global__ void argmax_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                    int slices, int* __restrict__ out)
 {
+    pdl_enter();
     const int row = blockIdx.x, lane = threadIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -96,6 +98,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
               const float* __restrict__ temperature, const float* __restrict__ uniform,
               int* __restrict__ out)
 {
+    pdl_enter();
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float totals[SAMPLE_WARPS];
@@ -192,12 +195,12 @@ CHIBI_API int chibi_sample(const float* logits, long long row_stride, long long 
         slices = (vocab + slice - 1) / slice;
         float* part_v = scratch;
         int* part_i = reinterpret_cast<int*>(scratch + rows * ARGMAX_MAX_SLICES);
-        argmax_slices_kernel<<<dim3(slices, (unsigned)rows), ARGMAX_THREADS, 0, stream>>>(
+        launch(argmax_slices_kernel, dim3(dim3(slices, (unsigned)rows)), dim3(ARGMAX_THREADS), 0, stream, 
             logits, row_stride, vocab, slice, part_v, part_i);
-        argmax_pick_kernel<<<(unsigned)rows, 32, 0, stream>>>(part_v, part_i, slices, out);
+        launch(argmax_pick_kernel, dim3((unsigned)rows), dim3(32), 0, stream, part_v, part_i, slices, out);
         return launch_status();
     }
-    sample_kernel<<<(unsigned)rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab,
+    launch(sample_kernel, dim3((unsigned)rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, vocab,
                                                                  temperature, uniform, out);
     return launch_status();
 }

@@ -82,8 +82,11 @@ class DecoderModel:
         hidden = self.spec.hidden_size
         residual = ctx.workspace.get("model.residual", (T, hidden), torch.float32)
         k.embed(ctx.tokens, self.embedding, residual)
+        pending = None      # a last product that a block left to be added to the residual
         for i, step in enumerate(self.spec.run_order):
-            self.blocks[step.layer].forward(residual, ctx, cache_views[i])
+            pending = self.blocks[step.layer].forward(residual, ctx, cache_views[i], pending)
+        if pending is not None:
+            pending.add_into(residual)
         R = ctx.logit_rows.numel()
         if R == 0:
             return None

@@ -28,6 +28,13 @@ _SIGNATURES = {
         "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
         "chibi_gemm_bf16_splits": [I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
+        "chibi_gemm_bf16_cluster_size": [I, I, I],
+        "chibi_gemm_bf16_fused": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P],
+        "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, P, P],
+        "chibi_reduce_residual_rmsnorm": [P, I, I, I, P, L, P, I, P, I, L, F, F, P],
+        "chibi_reduce_swiglu": [P, I, I, I, P, I, I, P],
+        "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,
+                                              I, I, F, F, I, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
         "chibi_sample": [P, L, L, I, P, P, P, P, L, P],
     },

@@ -55,6 +55,20 @@ def _rows_contiguous(t: torch.Tensor, what: str) -> None:
                           f"strides {t.stride()}")
 
 
+class PendingSum:
+    """The partial sums [splits, M, N] (32-bit) of a matrix product whose K range
+    was split over CTAs, waiting for a kernel that adds them up together with what
+    follows the product (residual and norm, SwiGLU, per-head norm and rotation).
+    It must be consumed before two more split products are started."""
+
+    def __init__(self, kernels, partial: torch.Tensor, splits: int, M: int, N: int):
+        self.kernels, self.partial, self.splits, self.M, self.N = kernels, partial, splits, M, N
+
+    def add_into(self, residual: torch.Tensor) -> None:
+        """residual += the product."""
+        self.kernels.reduce_residual_rmsnorm(self, residual, None, 0.0, 0.0, None)
+
+
 class CudaKernels:
     """The one set of operations of the product path."""
 
@@ -75,6 +89,15 @@ class CudaKernels:
         self.scratch_generation = 0
         self.supports_graphs = True     # every op is a plain launch on the current stream
         self._attention_libs = {}
+        self._partial_bufs = [None, None]
+        self._partial_turn = 0
+        # The K range of a product with few rows is split over CTAs.  Their partial sums go through
+        # global scratch to a second kernel that also does what follows the product (the default), or
+        # the CTAs form a cluster and add up through distributed shared memory (use_clusters; measured
+        # slower on B200: clusters of 8..16 CTAs are scheduled together and lose the overlap of
+        # consecutive kernels).
+        self.use_clusters = False
+        self.fuse_split_products = True
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     def _scratch(self, floats: int) -> torch.Tensor:
@@ -132,9 +155,159 @@ class CudaKernels:
                                       _code(out), x.shape[0], n, x.stride(0), out.stride(0),
                                       float(eps), float(offset), self._stream()), "rmsnorm")
 
+    def _partial_buffer(self, floats: int) -> torch.Tensor:
+        self._partial_turn ^= 1
+        buf = self._partial_bufs[self._partial_turn]
+        if buf is None or buf.numel() < floats:
+            buf = torch.empty(max(floats, 1 << 21), dtype=torch.float32, device=self.device)
+            self._partial_bufs[self._partial_turn] = buf
+            self.scratch_generation += 1
+        return buf
+
+    def linear_partial(self, x: torch.Tensor, w: torch.Tensor) -> Optional[PendingSum]:
+        """Start x @ w^T with the K range split over CTAs and leave the partial
+        sums for a fused consumer; None if this product is not one that is split
+        (then use ``linear``)."""
+        if not (self.use_tensor_cores and self.fuse_split_products and x.is_cuda
+                and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            return None
+        _rows_contiguous(x, "linear: x")
+        _rows_contiguous(w, "linear: w")
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"linear: shapes x {tuple(x.shape)} w {tuple(w.shape)}")
+        splits = self.lib.chibi_gemm_bf16_splits(M, N, K)
+        if splits <= 1 or N % 4 != 0:
+            return None
+        buf = self._partial_buffer(splits * M * N)
+        status = self.lib.chibi_gemm_bf16_partial(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
+                                                  _ptr(buf), buf.numel(), _ptr(self.error), self._stream())
+        if status == -2:
+            return None
+        _check(status, "linear (split product)")
+        self.launches += 1
+        self.tensor_core_calls += 1
+        return PendingSum(self, buf[:splits * M * N].view(splits, M, N), splits, M, N)
+
+    @staticmethod
+    def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> Optional[torch.Tensor]:
+        """[gate; up] rearranged for ``linear_swiglu``: blocks of 64 gate rows, each
+        followed by the 64 up rows of the same features.  None if the sizes do not
+        allow it (the number of features must be a multiple of 64)."""
+        inter, k = gate.shape
+        if gate.shape != up.shape or inter % 64 != 0 or k % 8 != 0 or gate.dtype != torch.bfloat16 \
+                or up.dtype != torch.bfloat16:
+            return None
+        return torch.stack([gate.view(inter // 64, 64, k), up.view(inter // 64, 64, k)], dim=1).reshape(2 * inter, k).contiguous()
+
+    def linear_swiglu(self, x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> bool:
+        """out[M, I] = silu(x @ gate^T) * (x @ up^T) in one kernel, with the weights
+        as ``interleave_gate_up`` arranges them.  False if the kernel refuses the
+        shapes (the caller then takes the two-kernel way)."""
+        _need_cuda(x, w_interleaved, out)
+        _rows_contiguous(x, "linear_swiglu: x")
+        _rows_contiguous(w_interleaved, "linear_swiglu: w")
+        _rows_contiguous(out, "linear_swiglu: out")
+        M, K = x.shape
+        N = w_interleaved.shape[0]
+        if w_interleaved.shape[1] != K or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 \
+                or x.dtype != torch.bfloat16 or w_interleaved.dtype != torch.bfloat16:
+            raise KernelError("linear_swiglu: shapes or element types")
+        if not self.use_tensor_cores:
+            return False
+        if M <= 64 and not self.use_clusters:
+            pending = self.linear_partial(x, w_interleaved)
+            if pending is not None:
+                self.reduce_swiglu(pending, out, interleaved=True)
+                return True
+        status = self.lib.chibi_gemm_bf16_fused(
+            _ptr(x), _ptr(w_interleaved), _ptr(out), BF16, None, M, N, K, x.stride(0),
+            w_interleaved.stride(0), out.stride(0), 0, 1, _ptr(self.error), self._stream())
+        if status == -2:
+            return False
+        _check(status, "linear_swiglu")
+        self.launches += 1
+        self.tensor_core_calls += 1
+        return True
+
+    def reduce_residual_rmsnorm(self, pending: PendingSum, residual: torch.Tensor,
+                                weight: Optional[torch.Tensor], eps: float, offset: float,
+                                out: Optional[torch.Tensor]) -> None:
+        """residual += pending; out = RMSNorm(residual) if a weight is given."""
+        _need_cuda(residual, weight, out)
+        _rows_contiguous(residual, "reduce_residual_rmsnorm: residual")
+        if residual.dtype != torch.float32 or residual.shape != (pending.M, pending.N):
+            raise KernelError("reduce_residual_rmsnorm: residual must be float32 [M, N]")
+        if weight is not None:
+            _rows_contiguous(out, "reduce_residual_rmsnorm: out")
+            if weight.shape != (pending.N,) or out.shape != residual.shape:
+                raise KernelError("reduce_residual_rmsnorm: weight / out shapes")
+        status = self.lib.chibi_reduce_residual_rmsnorm(
+            _ptr(pending.partial), pending.splits, pending.M, pending.N, _ptr(residual), residual.stride(0),
+            _ptr(weight), _code(weight) if weight is not None else F32, _ptr(out),
+            _code(out) if out is not None else F32, out.stride(0) if out is not None else 0,
+            float(eps), float(offset), self._stream())
+        if status == -2:
+            # a width the fused kernel does not take: add up, then normalise
+            self.launches += 1
+            _check(self.lib.chibi_add_into(_ptr(residual), _ptr(pending.partial[0]), F32,
+                                           residual.numel(), self._stream()), "add_into")
+            for s in range(1, pending.splits):
+                self.launches += 1
+                _check(self.lib.chibi_add_into(_ptr(residual), _ptr(pending.partial[s]), F32,
+                                               residual.numel(), self._stream()), "add_into")
+            if weight is not None:
+                self.rmsnorm(residual, weight, eps, offset, out)
+            return
+        self.launches += 1
+        _check(status, "reduce_residual_rmsnorm")
+
+    def reduce_swiglu(self, pending: PendingSum, out: torch.Tensor, interleaved: bool = False) -> None:
+        """out = silu(gate) * up from the pending [gate | up] product (or, with
+        ``interleaved``, from a product with ``interleave_gate_up`` weights)."""
+        _need_cuda(out)
+        inter = pending.N // 2
+        if not out.is_contiguous() or out.shape != (pending.M, inter):
+            raise KernelError("reduce_swiglu: out must be contiguous [M, N / 2]")
+        self.launches += 1
+        _check(self.lib.chibi_reduce_swiglu(_ptr(pending.partial), pending.splits, pending.M, inter,
+                                            _ptr(out), _code(out), 1 if interleaved else 0,
+                                            self._stream()), "reduce_swiglu")
+
+    def qk_norm_rope_append_partial(self, pending: PendingSum, q_out, k_cache, v_cache, q_norm_w, k_norm_w,
+                                    inv_freq, rotary_dim, eps, norm_offset, positions, seq_of_token,
+                                    block_table, nq, nkv, d, page_size, seq_rows=None) -> None:
+        """qk_norm_rope_append on a pending q | k | v product (bfloat16 outputs)."""
+        _need_cuda(q_out, k_cache, v_cache, q_norm_w, k_norm_w, inv_freq, positions, seq_of_token,
+                   block_table, seq_rows)
+        T = pending.M
+        append = k_cache is not None
+        width = (nq + 2 * nkv) * d if append else nq * d
+        if pending.N != width or q_out.shape != (T, nq * d) or q_out.dtype != torch.bfloat16 \
+                or not q_out.is_contiguous():
+            raise KernelError("qk_norm_rope_append_partial: shapes")
+        if append and (k_cache.dtype != torch.bfloat16 or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                       or not k_cache.is_contiguous() or not v_cache.is_contiguous()):
+            raise KernelError("qk_norm_rope_append_partial: cache")
+        w_type = _code(q_norm_w) if q_norm_w is not None else F32
+        self.launches += 1
+        _check(self.lib.chibi_qk_norm_rope_append_partial(
+            _ptr(pending.partial), pending.splits, T, width, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+            _ptr(q_norm_w), _ptr(k_norm_w), w_type, _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token),
+            _ptr(seq_rows), _ptr(block_table), block_table.stride(0) if append else 0, nq, nkv, d,
+            int(rotary_dim), page_size, k_cache.shape[0] if append else 0, float(eps), float(norm_offset),
+            1 if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append_partial")
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-               residual: Optional[torch.Tensor] = None) -> None:
-        """out[M, N] = x[M, K] @ w[N, K]^T (+ residual, 32-bit, may alias out)."""
+               residual: Optional[torch.Tensor] = None, defer: bool = False) -> Optional[PendingSum]:
+        """out[M, N] = x[M, K] @ w[N, K]^T (+ residual, 32-bit, may alias out).
+        With ``defer`` (only together with a residual that aliases out) a split
+        product is left pending -- the caller adds it later -- and is returned."""
+        if defer and residual is not None and residual is out:
+            pending = self.linear_partial(x, w)
+            if pending is not None:
+                return pending
         _need_cuda(x, w, out, residual)
         _rows_contiguous(x, "linear: x")
         _rows_contiguous(w, "linear: w")
@@ -147,6 +320,18 @@ class CudaKernels:
             _rows_contiguous(residual, "linear: residual")
             if residual.dtype != torch.float32 or residual.shape != (M, N):
                 raise KernelError("linear: residual must be float32 [M, N]")
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.use_tensor_cores \
+                and self.use_clusters and M <= 64:
+            status = self.lib.chibi_gemm_bf16_fused(
+                _ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(residual), M, N, K, x.stride(0),
+                w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, 0,
+                _ptr(self.error), self._stream())
+            if status == 0:
+                self.launches += 1
+                self.tensor_core_calls += 1
+                return
+            if status != -2:
+                _check(status, "linear (tensor cores)")
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.use_tensor_cores:
             splits = self.lib.chibi_gemm_bf16_splits(M, N, K)
             if splits > 0:

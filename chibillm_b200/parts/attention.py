@@ -80,15 +80,20 @@ class PagedAttention(Mixer):
         qw, kw = nq * d, nkv * d
         writes = cache.writes
         width = qw + 2 * kw if writes else qw
-        qkv = ctx.workspace.get("attn.qkv", (T, width), rt.dtype)
-        k.linear(x, self.qkv if writes else self.qkv[:qw], qkv)
+        fused = self.position.fused_rotation()
+        split = getattr(k, "linear_partial", None)
+        pending = None
+        if split is not None and fused is not None and d % 4 == 0:
+            pending = split(x, self.qkv if writes else self.qkv[:qw])
+        if pending is None:
+            qkv = ctx.workspace.get("attn.qkv", (T, width), rt.dtype)
+            k.linear(x, self.qkv if writes else self.qkv[:qw], qkv)
 
         q = ctx.workspace.get("attn.q", (T, qw), rt.dtype)
         table = ctx.tables[cache.group]
         norm = s.qk_norm
         q_norm_w = self.q_norm if norm is not None else None
         k_norm_w = self.k_norm if norm is not None else None
-        fused = self.position.fused_rotation()
         if fused is None:
             # An encoding the kernels do not know: normalise head by head in
             # place, let the encoding transform q and k, then only copy and append.
@@ -102,8 +107,9 @@ class PagedAttention(Mixer):
             q_norm_w = k_norm_w = None
             fused = (None, 0)
         inv_freq, rotary_dim = fused
-        k.qk_norm_rope_append(
-            qkv, q, cache.keys if writes else None, cache.values if writes else None,
+        (k.qk_norm_rope_append_partial if pending is not None else k.qk_norm_rope_append)(
+            pending if pending is not None else qkv, q, cache.keys if writes else None,
+            cache.values if writes else None,
             q_norm_w, k_norm_w, inv_freq, rotary_dim, norm.eps if norm is not None else 0.0,
             norm.weight_offset if norm is not None else 0.0,
             ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size,
@@ -112,7 +118,7 @@ class PagedAttention(Mixer):
         k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
                     s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows)
-        k.linear(att, self.o_proj, residual, residual=residual)
+        return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
 
 
 register_mixer("attention", PagedAttention, replace=True)

@@ -83,6 +83,13 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         raise NotImplementedError
 
+    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor) -> None:
+        """residual += pending (a matrix product that its producer left for us to
+        add, or None); out = norm(residual).  A norm may do both in one kernel."""
+        if pending is not None:
+            pending.add_into(residual)
+        self.forward(residual, out)
+
 
 class PositionEncoding(Part):
     """Position information applied to queries and keys inside a mixer.
@@ -105,7 +112,9 @@ class Mixer(Part):
     ``forward`` reads the normalised input ``x`` [T, hidden] and adds its result
     into the 32-bit ``residual`` [T, hidden].  ``cache`` is what the cache
     manager made for this run step from ``cache_need()`` (a PagedKVView, a
-    FixedStateView or None).
+    FixedStateView or None).  It returns None -- or an object with
+    ``add_into(residual)`` for a last product that it has not added yet (the
+    block hands it to the next norm, which may add and normalise in one kernel).
     """
 
     def cache_need(self):
@@ -116,7 +125,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """Per-token transformation; adds its result into ``residual``."""
+    """Per-token transformation; adds its result into ``residual`` (or returns it
+    pending, as a mixer may)."""
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         raise NotImplementedError
@@ -127,7 +137,9 @@ class Block(Part):
 
     mixer: Mixer
 
-    def forward(self, residual: torch.Tensor, ctx, cache) -> None:
+    def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
+        """``pending``: what the block before left to be added to the residual.
+        Returns what this block leaves pending (or None)."""
         raise NotImplementedError
 
 

@@ -36,12 +36,12 @@ class PreNormBlock(Block):
         a, b = self.mixer.launch_key(ctx), self.feed_forward.launch_key(ctx)
         return None if a is None or b is None else (a, b)
 
-    def forward(self, residual: torch.Tensor, ctx, cache) -> None:
+    def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
         x = ctx.workspace.get("block.normed", tuple(residual.shape), self.runtime.dtype)
-        self.mixer_norm.forward(residual, x)
-        self.mixer.forward(x, residual, ctx, cache)
-        self.feed_forward_norm.forward(residual, x)
-        self.feed_forward.forward(x, residual, ctx)
+        self.mixer_norm.forward_fused(residual, pending, x)
+        pending = self.mixer.forward(x, residual, ctx, cache)
+        self.feed_forward_norm.forward_fused(residual, pending, x)
+        return self.feed_forward.forward(x, residual, ctx)
 
 
 register_block("prenorm", PreNormBlock, replace=True)

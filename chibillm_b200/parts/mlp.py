@@ -18,6 +18,7 @@ class GatedMLP(FeedForward):
         self.names = names
         self.runtime = runtime
         self.gate_up: torch.Tensor = None
+        self.gate_up_interleaved: torch.Tensor = None
         self.down: torch.Tensor = None
 
     def expected_tensors(self) -> List[TensorSpec]:
@@ -30,7 +31,11 @@ class GatedMLP(FeedForward):
         gate, up = tensors[self.names["gate_proj"]], tensors[self.names["up_proj"]]
         if gate.dtype != up.dtype:
             up = up.to(gate.dtype)
-        self.gate_up = torch.cat([gate, up], dim=0).contiguous()
+        interleave = getattr(self.runtime.kernels, "interleave_gate_up", None)
+        self.gate_up_interleaved = interleave(gate, up) if interleave is not None else None
+        # one of the two layouts is kept: blocks of 64 gate rows and their 64 up rows for the kernel
+        # that applies SwiGLU itself, else gate rows followed by up rows
+        self.gate_up = None if self.gate_up_interleaved is not None else torch.cat([gate, up], dim=0).contiguous()
         self.down = tensors[self.names["down_proj"]].contiguous()
 
     def launch_key(self, ctx):
@@ -40,11 +45,20 @@ class GatedMLP(FeedForward):
         k = self.runtime.kernels
         T = x.shape[0]
         inter = self.spec.intermediate_size
-        gate_up = ctx.workspace.get("mlp.gate_up", (T, 2 * inter), self.runtime.dtype)
-        k.linear(x, self.gate_up, gate_up)
         act = ctx.workspace.get("mlp.act", (T, inter), self.runtime.dtype)
-        k.swiglu(gate_up, act)
-        k.linear(act, self.down, residual, residual=residual)
+        if self.gate_up_interleaved is not None:
+            if not k.linear_swiglu(x, self.gate_up_interleaved, act):
+                raise RuntimeError("gated_mlp: the fused kernel refused a shape it was prepared for")
+            return k.linear(act, self.down, residual, residual=residual, defer=True)
+        split = getattr(k, "linear_partial", None)
+        pending = split(x, self.gate_up) if split is not None else None
+        if pending is not None:
+            k.reduce_swiglu(pending, act)            # adds the partial sums and applies SwiGLU
+        else:
+            gate_up = ctx.workspace.get("mlp.gate_up", (T, 2 * inter), self.runtime.dtype)
+            k.linear(x, self.gate_up, gate_up)
+            k.swiglu(gate_up, act)
+        return k.linear(act, self.down, residual, residual=residual, defer=True)
 
 
 register_feed_forward("gated_mlp", GatedMLP, replace=True)

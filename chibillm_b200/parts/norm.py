@@ -34,4 +34,13 @@ class RMSNorm(Norm):
                                          self.spec.weight_offset, out.view(-1, n))
 
 
+    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor) -> None:
+        k = self.runtime.kernels
+        fused = getattr(k, "reduce_residual_rmsnorm", None)
+        if pending is None or fused is None or residual.shape[-1] != self.spec.size \
+                or not hasattr(pending, "partial"):
+            return super().forward_fused(residual, pending, out)
+        fused(pending, residual, self.weight, self.spec.eps, self.spec.weight_offset, out)
+
+
 register_norm("rmsnorm", RMSNorm, replace=True)

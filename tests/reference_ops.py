@@ -38,7 +38,10 @@ class ReferenceKernels:
         inv = torch.rsqrt((xf * xf).sum(-1, keepdim=True) / n + eps)
         out.copy_(((xf * inv) * (weight.float() + offset)).to(out.dtype))
 
-    def linear(self, x, w, out, residual=None):
+    def linear_partial(self, x, w):
+        return None
+
+    def linear(self, x, w, out, residual=None, defer=False):
         self._count("linear")
         y = x.float() @ w.float().t()
         if residual is not None:

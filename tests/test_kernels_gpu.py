@@ -280,10 +280,22 @@ def test_sample_temperature(k, vocab):
 
 @pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64, 65, 128, 300])
 @pytest.mark.parametrize("N,K", [(203, 96), (256, 512), (1000, 1000), (384, 4096)])
-def test_linear_tensor_cores(k, ref, M, N, K):
+@pytest.mark.parametrize("clusters", [False, True])
+def test_linear_tensor_cores(k, ref, M, N, K, clusters):
     """The tcgen05 kernel at sizes that are no multiple of its tiles: rows and
-    features past the edge, a K tail, K ranges split over CTAs for few rows, and
-    enough K blocks that the ring of stages wraps several times."""
+    features past the edge, a K tail, K ranges split over CTAs for few rows
+    (through global scratch, or through a cluster's shared memory), and enough K
+    blocks that the ring of stages wraps several times."""
+    if clusters and M > 64:
+        pytest.skip("clusters share a K range only for few rows")
+    k.use_clusters = clusters
+    try:
+        _linear_tensor_cores(k, ref, M, N, K)
+    finally:
+        k.use_clusters = False
+
+
+def _linear_tensor_cores(k, ref, M, N, K):
     x = rnd(M, K, dtype=torch.bfloat16, seed=30)
     w = rnd(N, K, dtype=torch.bfloat16, seed=31, scale=0.05)
     before = k.tensor_core_calls
@@ -319,3 +331,101 @@ def test_linear_falls_back_when_unaligned(k, ref):
     ref.linear(x, w, exp)
     assert k.tensor_core_calls == before
     close(out, exp, torch.float32, "fallback linear", rel=2e-5)
+
+
+@pytest.mark.parametrize("M", [1, 8, 33, 64])
+def test_split_product_with_fused_consumers(k, ref, M):
+    """A product whose K range is split over CTAs, finished by the kernels that
+    add the partial sums together with what follows: residual + RMSNorm, SwiGLU,
+    per-head norm + rotation + cache append."""
+    K = 4096
+    k.fuse_split_products = True
+    x = rnd(M, K, dtype=torch.bfloat16, seed=40)
+    # residual + norm (and residual alone)
+    N = 1024
+    w = rnd(N, K, dtype=torch.bfloat16, seed=41, scale=0.05)
+    nw = (1 + 0.1 * rnd(N, seed=42)).to(torch.bfloat16)
+    res = rnd(M, N, seed=43)
+    pending = k.linear_partial(x, w)
+    assert pending is not None and pending.splits > 1
+    got_res = res.clone()
+    got_norm = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k.reduce_residual_rmsnorm(pending, got_res, nw, 1e-5, 0.0, got_norm)
+    exp_res = torch.empty_like(res)
+    ref.linear(x, w, exp_res, residual=res)
+    exp_norm = torch.empty_like(got_norm)
+    ref.rmsnorm(exp_res, nw, 1e-5, 0.0, exp_norm)
+    close(got_res, exp_res, torch.float32, "split product + residual", rel=2e-5)
+    close(got_norm, exp_norm, torch.bfloat16, "split product + residual + norm", rel=8e-3)
+    pending = k.linear(x, w, res, residual=res, defer=True)
+    assert pending is not None
+    pending.add_into(res)
+    close(res, exp_res, torch.float32, "deferred residual add", rel=2e-5)
+    # SwiGLU
+    inter = 768
+    wgu = rnd(2 * inter, K, dtype=torch.bfloat16, seed=44, scale=0.03)
+    pending = k.linear_partial(x, wgu)
+    assert pending is not None
+    act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k.reduce_swiglu(pending, act)
+    gu = torch.empty(M, 2 * inter, dtype=torch.float32, device="cuda")
+    ref.linear(x, wgu, gu)
+    exp_act = torch.empty_like(act)
+    ref.swiglu(gu, exp_act)
+    close(act, exp_act, torch.bfloat16, "split product + SwiGLU", rel=8e-3)
+    # per-head norm + rotation + append
+    nq, nkv, d, page, pages = 6, 2, 64, 16, 40
+    seq_ctx = [min(5 + 7 * i, 600) for i in range(M)]
+    table, positions, seq_of_token, _, _ = _paged_setup(seq_ctx, [1] * M, page, max(pages, sum((c + 15) // 16 for c in seq_ctx) + 1), seed=45)
+    pages = max(pages, int(table.max()) + 1)
+    wqkv = rnd((nq + 2 * nkv) * d, K, dtype=torch.bfloat16, seed=46, scale=0.03)
+    qn = (1 + 0.1 * rnd(d, seed=47)).to(torch.bfloat16)
+    kn = (1 + 0.1 * rnd(d, seed=48)).to(torch.bfloat16)
+    inv_freq = torch.pow(torch.tensor(1e6), -2 * torch.arange(d // 2, dtype=torch.float32) / d).cuda()
+    pending = k.linear_partial(x, wqkv)
+    assert pending is not None
+    q_got = torch.full((M, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros(pages, nkv, page, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    k.qk_norm_rope_append_partial(pending, q_got, kc, vc, qn, kn, inv_freq, d, 1e-6, 0.0, positions,
+                                  seq_of_token, table, nq, nkv, d, page)
+    qkv = torch.empty(M, (nq + 2 * nkv) * d, dtype=torch.float32, device="cuda")
+    ref.linear(x, wqkv, qkv)
+    q_exp = torch.empty(M, nq * d, dtype=torch.float32, device="cuda")
+    kc_exp = torch.zeros(pages, nkv, page, d, dtype=torch.float32, device="cuda")
+    vc_exp = torch.zeros_like(kc_exp)
+    ref.qk_norm_rope_append(qkv, q_exp, kc_exp, vc_exp, qn, kn, inv_freq, d, 1e-6, 0.0, positions,
+                            seq_of_token, table, nq, nkv, d, page)
+    close(q_got, q_exp, torch.bfloat16, "split product -> q", rel=8e-3)
+    close(kc, kc_exp, torch.bfloat16, "split product -> key cache", rel=8e-3)
+    close(vc, vc_exp, torch.bfloat16, "split product -> value cache", rel=8e-3)
+    k.check_error_word()
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 65, 300])
+@pytest.mark.parametrize("inter,K", [(64, 512), (192, 4096), (768, 1000)])
+def test_linear_swiglu(k, ref, M, inter, K):
+    """SwiGLU inside the matrix product: the weights come as blocks of 64 gate
+    rows and their 64 up rows; for few rows the CTAs of a cluster add their
+    partial sums through distributed shared memory."""
+    gate = rnd(inter, K, dtype=torch.bfloat16, seed=50, scale=0.05)
+    up = rnd(inter, K, dtype=torch.bfloat16, seed=51, scale=0.05)
+    x = rnd(M, K, dtype=torch.bfloat16, seed=52)
+    w = k.interleave_gate_up(gate, up)
+    assert w is not None and w.shape == (2 * inter, K)
+    assert torch.equal(w[:64], gate[:64]) and torch.equal(w[64:128], up[:64])
+    out = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert k.linear_swiglu(x, w, out)
+    if M <= 64:        # the other way for few rows: a cluster of CTAs adds up through shared memory
+        k.use_clusters = True
+        out2 = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert k.linear_swiglu(x, w, out2)
+        k.use_clusters = False
+        close(out2, out, torch.bfloat16, "cluster vs split product", rel=8e-3)
+    gu = torch.empty(M, 2 * inter, dtype=torch.float32, device="cuda")
+    ref.linear(x, torch.cat([gate, up]), gu)
+    exp = torch.empty_like(out)
+    ref.swiglu(gu, exp)
+    close(out, exp, torch.bfloat16, "product + SwiGLU", rel=8e-3)
+    k.check_error_word()
+    assert k.interleave_gate_up(gate[:40], up[:40]) is None
