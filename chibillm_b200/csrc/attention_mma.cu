@@ -194,6 +194,20 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILE
 {
     const int tig = lane & 3;
     float mx[2] = { -INFINITY, -INFINITY };
+    // a tile that every row of the warp sees whole needs no masks (most tiles of a long prompt)
+    const int last_key = key0 + NT * 8 - 1;
+    const bool whole = __all_sync(0xffffffffu, last_key < key_end && last_key <= pos_lo && last_key <= pos_hi
+                                                   && key0 >= first_lo && key0 >= first_hi);
+    if (whole) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[nt][e] *= scale_log2;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+            }
+        }
+    } else
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
