@@ -361,6 +361,212 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 }
 
+// ------------------------------------------------------------------ many rows: one CTA per SM
+// The epilogue of one 128 x BN tile whose rows are tokens (x is the A operand):
+// this thread owns row `m`; `taddr` is the TMEM address of its lane at the tile's
+// first column.
+template <int BN>
+__device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m, int tile_b)
+{
+    if (p.swiglu) {
+        // the BN columns are rows of w, which come as [64 gate | 64 up] blocks
+        const int inter = p.N >> 1;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            if ((c0 & 64) != 0)
+                continue;                           // the up halves are read with their gate halves
+            uint32_t g[32], u[32];
+            tmem_load_32x32(taddr + c0, g);
+            tmem_load_32x32(taddr + c0 + 64, u);
+            tmem_load_wait();
+            const int w_row = tile_b * BN + c0;
+            const int feat0 = (w_row >> 7) * 64 + (w_row & 63);
+            if (m >= p.M)
+                continue;
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + feat0;
+            if (feat0 + 32 <= inter && p.out_stride % 8 == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 h[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float g0 = __uint_as_float(g[8 * j + 2 * q]), g1 = __uint_as_float(g[8 * j + 2 * q + 1]);
+                        const float u0 = __uint_as_float(u[8 * j + 2 * q]), u1 = __uint_as_float(u[8 * j + 2 * q + 1]);
+                        h[q] = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * u0,
+                                                     __fdividef(g1, 1.f + __expf(-g1)) * u1);
+                    }
+                    reinterpret_cast<uint4*>(dst)[j] = *reinterpret_cast<uint4*>(h);
+                }
+            } else {
+                for (int j = 0; j < 32; ++j)
+                    if (feat0 + j < inter) {
+                        const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                        dst[j] = __float2bfloat16_rn((gv / (1.f + expf(-gv))) * uv);
+                    }
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_load_32x32(taddr + c0, r);
+        tmem_load_wait();
+        const int n0 = tile_b * BN + c0;
+        const bool vec = m < p.M && n0 + 32 <= p.N && (p.out_stride % 8 == 0)
+            && (!p.residual || p.res_stride % 4 == 0);
+        if (vec && p.out_type == CHIBI_F32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)m * p.out_stride + n0);
+            const float4* res = p.residual
+                ? reinterpret_cast<const float4*>(p.residual + (size_t)m * p.res_stride + n0) : nullptr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (res) {
+                    const float4 q = res[j];
+                    v.x = q.x + v.x; v.y = q.y + v.y; v.z = q.z + v.z; v.w = q.w + v.w;
+                }
+                dst[j] = v;
+            }
+        } else if (vec && p.out_type == CHIBI_BF16 && !p.residual) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + n0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    h[q] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * q]), __uint_as_float(r[8 * j + 2 * q + 1]));
+                dst[j] = *reinterpret_cast<uint4*>(h);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                store_value(p, m, n0 + j, __uint_as_float(r[j]));
+        }
+    }
+}
+
+// x is the A operand (many rows).  One CTA per SM walks over the output tiles
+// (tile t -> row block t % tiles_m, column block t / tiles_m, so that CTAs working
+// at the same time share a block of w).  Two accumulators in TMEM: while the four
+// epilogue warps read one tile out, the MMA thread already fills the other.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                               const __grid_constant__ CUtensorMap map_b, const GemmParams p,
+                               int tiles_m, int tiles_total)
+{
+    pdl_trigger();
+    using S = GemmSmem<BN>;
+    static_assert(2 * BN <= 512, "two accumulators must fit the 512 TMEM columns");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;     // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;     // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb_count = p.k_blocks_total;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full_bar[b], 1);
+            mbar_init(&tmem_empty_bar[b], 128);       // every epilogue thread arrives
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            tma_prefetch_descriptor(&map_a);
+            tma_prefetch_descriptor(&map_b);
+            uint32_t it = 0;
+            bool waited = false;
+            for (int t = blockIdx.x; t < tiles_total; t += gridDim.x) {
+                const int tile_a = t % tiles_m, tile_b = t / tiles_m;
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0)
+                        mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 11);
+                    uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                    // w does not depend on the kernel before this one; x does
+                    tma_load_2d(a_dst + S::A_BYTES, &map_b, &full_bar[s], kb * TILE_K, tile_b * BN);
+                    if (!waited) {
+                        pdl_wait();
+                        waited = true;
+                    }
+                    tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TILE_K, tile_a * TILE_A);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc_bf16_f32(TILE_A, BN);
+            uint32_t it = 0, lt = 0;
+            for (int t = blockIdx.x; t < tiles_total; t += gridDim.x, ++lt) {
+                const uint32_t buf = lt & 1, use = lt >> 1;
+                if (use > 0)
+                    mbar_wait(&tmem_empty_bar[buf], (use - 1) & 1, p.error, 14);
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    mbar_wait(&full_bar[s], round & 1, p.error, 12);
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                        const uint64_t a_desc = make_kmajor_sw128_desc(a_addr + k * UMMA_K * 2);
+                        const uint64_t b_desc = make_kmajor_sw128_desc(b_addr + k * UMMA_K * 2);
+                        tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(&empty_bar[s]);
+                }
+                tcgen05_commit(&tmem_full_bar[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();
+        uint32_t lt = 0;
+        for (int t = blockIdx.x; t < tiles_total; t += gridDim.x, ++lt) {
+            const int tile_a = t % tiles_m, tile_b = t / tiles_m;
+            const uint32_t buf = lt & 1, use = lt >> 1;
+            mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 13);
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+            epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32 + lane, tile_b);
+            tcgen05_fence_before();
+            mbar_arrive(&tmem_empty_bar[buf]);
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // out = (residual +) sum over splits, in split order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, void* out,
                                      int out_type, long long out_stride, const float* residual,
@@ -484,6 +690,29 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     return launch_status();
 }
 
+template <int BN, int STAGES>
+static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                                  int tiles_m, int tiles_n, cudaStream_t stream)
+{
+    constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    const int tiles = tiles_m * tiles_n;
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int ctas = tiles < sms ? tiles : sms;
+    launch(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(GEMM_THREADS), smem, stream, ma, mb, p,
+           tiles_m, tiles);
+    return launch_status();
+}
+
 } // namespace chibi
 
 using namespace chibi;
@@ -601,7 +830,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         if (grid.y > 65535)
             return CHIBI_ERR_UNSUPPORTED;
         if (bn == 256)
-            status = launch_gemm<256, 4>(ma, mb, p, grid, stream);
+            status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
         else if (bn == 128)
             status = launch_gemm<128, 4>(ma, mb, p, grid, stream);
         else
@@ -715,7 +944,7 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     if (grid.y > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     if (bn == 256)
-        return launch_gemm<256, 4>(ma, mb, p, grid, stream);
+        return launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
     if (bn == 128)
         return launch_gemm<128, 4>(ma, mb, p, grid, stream);
     return launch_gemm<64, 4>(ma, mb, p, grid, stream);

@@ -122,7 +122,8 @@ class CudaKernels:
                     4: "a block-table update outside the table",
                     11: "a wait that ran out (matrix product: loader)",
                     12: "a wait that ran out (matrix product: tensor-core issuer)",
-                    13: "a wait that ran out (matrix product: epilogue)"}.get(code, f"code {code}")
+                    13: "a wait that ran out (matrix product: epilogue)",
+                    14: "a wait that ran out (matrix product: accumulator hand-over)"}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
     # ------------------------------------------------------------------ ops
