@@ -419,14 +419,19 @@ constexpr int PRE_WARPS = 4;
 constexpr int PRE_ROWS = PRE_WARPS * 16;      // query rows per CTA
 constexpr int PRE_KEYS = D <= 128 ? 64 : 32;  // keys per tile
 constexpr int PRE_NT = PRE_KEYS / 8;
-constexpr size_t PRE_SMEM = (size_t)(PRE_ROWS * DPAD + 2 * 2 * PRE_KEYS * DPAD) * 2;
+// When the query fragments stay in registers the query tile is only needed until
+// they are loaded: it then shares the memory of the second K/V stage, which is
+// first written after that.  Three CTAs fit an SM that way.
+constexpr bool PRE_Q_ALIASED = Q_IN_REGS && PRE_ROWS <= 2 * PRE_KEYS;
+constexpr size_t PRE_SMEM = (size_t)((PRE_Q_ALIASED ? 0 : PRE_ROWS * DPAD) + 2 * 2 * PRE_KEYS * DPAD) * 2;
 
-__global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const AttnParams p)
+__global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_prefill_kernel(const AttnParams p)
 {
     pdl_enter();
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* kv = q_tile + PRE_ROWS * DPAD;        // [stage][K | V][PRE_KEYS][DPAD]
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* kv = PRE_Q_ALIASED ? base : base + PRE_ROWS * DPAD;   // [stage][K | V][PRE_KEYS][DPAD]
+    __nv_bfloat16* q_tile = PRE_Q_ALIASED ? kv + 2 * PRE_KEYS * DPAD : base;
 
     const int seq = blockIdx.z, kv_head = blockIdx.y;
     const int t0 = p.q_start[seq];
@@ -492,6 +497,8 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attn_prefill_kernel(const Attn
     const __nv_bfloat16* my_q = q_tile + warp * 16 * DPAD;
     if constexpr (Q_IN_REGS)
         load_q_frags(qf, my_q, lane);
+    if constexpr (PRE_Q_ALIASED)
+        __syncthreads();                   // every warp has its fragments: the second stage may be filled
 
     float o[NTILES_D][4];
 #pragma unroll
