@@ -1,0 +1,97 @@
+"""Layer sizes of real checkpoints (Qwen3-0.6B and a slice of Qwen3-8B: head size
+128, vocabulary 151,936, tied or untied output) with random weights and two
+layers: the bfloat16 engine against the 32-bit engine, whole prompts against
+portions and decoded tokens, and a long context whose decode steps are replayed
+from CUDA graphs.  These sizes take the tensor-core kernels (tcgen05 products
+with split K ranges, tensor-core attention) that the tiny configurations do
+not reach."""
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def base(**kw):
+    d = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "attention_bias": False,
+         "hidden_act": "silu", "rope_scaling": None, "torch_dtype": "bfloat16", "head_dim": 128,
+         "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
+         "use_sliding_window": False, "sliding_window": None, "num_hidden_layers": 2}
+    d.update(kw)
+    return d
+
+
+SHAPES = {
+    "0.6B": base(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, intermediate_size=3072,
+                 tie_word_embeddings=True),
+    "8B": base(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, intermediate_size=12288,
+               tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("shape", list(SHAPES))
+def test_bfloat16_engine_against_32_bit_engine(shape):
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = SHAPES[shape]
+    reqs = helpers.random_requests(cfg["vocab_size"], [300, 70, 1, 129], seed=3)
+    # only a few places are wanted: a row of logits is 600 KB
+    want = {rid: sorted({0, len(ids) // 2, len(ids) - 1}) for rid, ids in reqs.items()}
+
+    def run(dtype, trace_fn):
+        runner = ModelRunner.from_random(cfg, seed=5, dtype=dtype, page_size=16, pool_tokens=1024, max_requests=4)
+        out = {}
+        for rid, ids in reqs.items():
+            rows = {}
+            fed = 0
+            for portion in trace_fn(ids):
+                places = [w - fed for w in want[rid] if fed <= w < fed + len(portion)]
+                from chibillm_b200.engine.batch import StepEntry
+                logits = runner.step([StepEntry(rid, portion, places)])
+                for k, w in enumerate(places):
+                    rows[fed + w] = logits[k].float().cpu().clone()
+                fed += len(portion)
+            runner.end(rid)
+            out[rid] = torch.stack([rows[w] for w in want[rid]])
+        replays = runner.graph_replays
+        del runner
+        torch.cuda.empty_cache()
+        return out, replays
+
+    whole = lambda ids: [ids]
+
+    def cut(ids):          # a big portion, small ones, then the last 20 tokens one by one
+        head = max(1, len(ids) - 20)
+        parts = [ids[:head // 2], ids[head // 2:head]] if head > 1 else [ids[:head]]
+        return [p for p in parts if p] + [[t] for t in ids[head:]]
+
+    ref32, _ = run("float32", whole)
+    bf_whole, _ = run("bfloat16", whole)
+    bf_cut, replays = run("bfloat16", cut)
+    assert replays > 0, "decode steps were not replayed from a graph"
+    f32_cut, _ = run("float32", cut)
+    helpers.assert_logits_close(f32_cut, ref32, helpers.TOL["float32"], f"{shape} float32 cut vs whole")
+    helpers.assert_logits_close(bf_whole, ref32, helpers.TOL["bfloat16"], f"{shape} bfloat16 vs float32")
+    helpers.assert_logits_close(bf_cut, ref32, helpers.TOL["bfloat16"], f"{shape} bfloat16 cut vs float32")
+    helpers.assert_logits_close(bf_cut, bf_whole, helpers.TOL_SAME_DTYPE["bfloat16"], f"{shape} bfloat16 cut vs whole")
+
+
+def test_long_context_decode():
+    """A context of 3,000 tokens at the 0.6B layer sizes, then 16 decoded tokens:
+    the bfloat16 engine's logits stay close to the 32-bit engine's, so no key of
+    the long context is lost by the split attention or at a page's edge."""
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = dict(SHAPES["0.6B"], num_hidden_layers=1)
+    ids = helpers.random_requests(cfg["vocab_size"], [3016], seed=9)["r0"]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        runner = ModelRunner.from_random(cfg, seed=6, dtype=dtype, page_size=16, pool_tokens=3072, max_requests=2)
+        runner.step([StepEntry("a", ids[:3000], [])])
+        rows = []
+        for t in ids[3000:]:
+            rows.append(runner.step([StepEntry("a", [t], [0])])[0].float().cpu().clone())
+        outs[dtype] = {"a": torch.stack(rows)}
+        del runner
+        torch.cuda.empty_cache()
+    helpers.assert_logits_close(outs["bfloat16"], outs["float32"], helpers.TOL["bfloat16"], "long context decode")
