@@ -1,0 +1,412 @@
+// Causal grouped-query attention for prompt portions on the 5th-generation
+// tensor cores, for one head size per compiled library (-DCHIBI_HEAD_DIM=d,
+// d = 64 or 128).
+//
+// One CTA owns 128 query rows of one kv head -- the rows are (token, head of the
+// group) pairs, so the group's heads share every key and value tile -- and walks
+// over the keys in tiles of 128:
+//
+//   warp 0      loads K and V tiles with TMA, one box per cache page and 64-wide
+//               half of the head (128-byte swizzle);
+//   warp 1      issues the MMAs:  S = Q K^T  (both K-major) into one of two TMEM
+//               buffers, and  O_tile = P V  with P from shared memory and V as the
+//               MN-major operand (V is stored [key][d]) into a third TMEM buffer;
+//   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from
+//               TMEM, keeps the running maximum and sum in registers, writes
+//               P = exp2(S * scale - max) as bfloat16 into shared memory in the
+//               swizzled K-major layout, and adds each O_tile to its 32-bit
+//               output row in registers after rescaling.
+//
+// The MMA of the next S tile is issued before the P V product of the current
+// one, so it runs while the softmax threads work.  All waits are bounded.
+#include "common.cuh"
+#include "sm100.cuh"
+#include "tensor_map.cuh"
+
+#ifndef CHIBI_HEAD_DIM
+#define CHIBI_HEAD_DIM 128
+#endif
+
+namespace chibi {
+
+using namespace sm100;
+
+constexpr int D = CHIBI_HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
+constexpr int ROWS = 128;                    // query rows per CTA = UMMA M
+constexpr int KEYS = 128;                    // keys per tile
+constexpr int HALVES = D / 64;               // 64-wide (128-byte) slices of a head
+constexpr int ATC_THREADS = 192;
+constexpr int Q_BYTES = ROWS * D * 2;
+constexpr int KV_TILE_BYTES = KEYS * D * 2;  // one K or V tile
+constexpr int P_BYTES = ROWS * KEYS * 2;
+constexpr int SMEM_TILES = Q_BYTES + 4 * KV_TILE_BYTES + P_BYTES;
+constexpr int NUM_BARS = 14;
+constexpr size_t ATC_SMEM = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;
+constexpr uint32_t TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256;
+
+struct AttnTcParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* block_table;
+    int table_stride;
+    const int* seq_rows;
+    const int* q_start;
+    const int* ctx_len;
+    int nq, nkv, group;
+    int page_size;
+    long long cache_rows;        // pages * nkv * page_size: rows of the [rows, D] view of a cache
+    int num_pages;
+    float scale_log2;
+    int window;
+    int skip_single;
+    int* error;
+};
+
+// Byte offset of element (row, col) of a [rows][64] bf16 tile laid out with the
+// 128-byte swizzle (what TMA writes and tcgen05.mma reads): 16-byte chunk c of
+// row r sits at chunk position c ^ (r % 8).
+__device__ __forceinline__ uint32_t swizzled_chunk(int row, int chunk)
+{
+    return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+
+// MN-major operand (here V: [key][d], d contiguous) in the same swizzled tiles:
+// leading byte offset = distance between the 64-wide slices of d, stride byte
+// offset = 8 keys * 128 B.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_byte_addr, uint32_t lbo_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_byte_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(ATC_THREADS)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const AttnTcParams p)
+{
+    pdl_enter();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + Q_BYTES;                  // two stages
+    uint8_t* v_s = k_s + 2 * KV_TILE_BYTES;        // two stages
+    uint8_t* p_s = v_s + 2 * KV_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
+    uint64_t* k_full = bars;          // [2] TMA
+    uint64_t* v_full = bars + 2;      // [2] TMA
+    uint64_t* k_empty = bars + 4;     // [2] MMA commit
+    uint64_t* v_empty = bars + 6;     // [2] MMA commit
+    uint64_t* s_full = bars + 8;      // [2] MMA commit
+    uint64_t* s_free = bars + 10;     // [2] 128 threads
+    uint64_t* p_full = bars + 12;     // 128 threads
+    uint64_t* o_full = bars + 13;     // MMA commit (also frees P)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+
+    const int seq = blockIdx.z, kv_head = blockIdx.y;
+    const int t0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - t0;
+    const int rows_total = q_len * p.group;
+    const int row0 = blockIdx.x * ROWS;
+    if (q_len <= 0 || (q_len == 1 && p.skip_single) || row0 >= rows_total)
+        return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos0 = p.ctx_len[seq] - q_len;
+    const int* table = p.block_table + (size_t)(p.seq_rows ? p.seq_rows[seq] : seq) * p.table_stride;
+
+    const int last_row = min(rows_total, row0 + ROWS) - 1;
+    const int min_pos = pos0 + row0 / p.group, max_pos = pos0 + last_row / p.group;
+    int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    key_begin = key_begin / p.page_size * p.page_size;           // tiles start on a page
+    const int key_end = max_pos + 1;
+    const int n_tiles = (key_end - key_begin + KEYS - 1) / KEYS;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_free[i], 128);
+        }
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    // query rows -> shared memory in the swizzled K-major layout (all threads help)
+    for (int c = threadIdx.x; c < ROWS * (D / 8); c += ATC_THREADS) {
+        const int row = c / (D / 8), chunk = c - row * (D / 8);
+        const int r = row0 + row;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_total) {
+            const int tok = r / p.group, h = r - tok * p.group;
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(t0 + tok) * p.nq + kv_head * p.group + h) * D + chunk * 8);
+        }
+        *reinterpret_cast<uint4*>(q_s + (chunk >> 3) * (ROWS * 128) + swizzled_chunk(row, chunk & 7)) = v;
+    }
+    fence_proxy_async();               // the tensor core reads what these threads wrote
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            tma_prefetch_descriptor(&map_k);
+            tma_prefetch_descriptor(&map_v);
+            const int pages_per_tile = KEYS / p.page_size;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j & 1;
+                const uint32_t round = j >> 1;
+                for (int which = 0; which < 2; ++which) {       // keys, then values
+                    uint64_t* full = which ? &v_full[st] : &k_full[st];
+                    uint64_t* empty = which ? &v_empty[st] : &k_empty[st];
+                    uint8_t* dst = (which ? v_s : k_s) + st * KV_TILE_BYTES;
+                    if (round > 0)
+                        mbar_wait(empty, (round - 1) & 1, p.error, 21);
+                    mbar_arrive_expect_tx(full, KV_TILE_BYTES);
+                    for (int pg = 0; pg < pages_per_tile; ++pg) {
+                        const int key = key_begin + j * KEYS + pg * p.page_size;
+                        int page = -1;
+                        if (key < key_end)
+                            page = table[key / p.page_size];
+                        if (key < key_end && (page < 0 || page >= p.num_pages) && p.error)
+                            atomicExch(p.error, 3);
+                        // a page past the context (or a bad one) is read outside the array: zeros
+                        const long long row = (page >= 0 && page < p.num_pages)
+                            ? ((long long)page * p.nkv + kv_head) * p.page_size : p.cache_rows;
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(dst + h * (KEYS * 128) + pg * p.page_size * 128, which ? &map_v : &map_k,
+                                        full, h * 64, (int)row);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = make_idesc_bf16_f32(ROWS, KEYS);
+            constexpr uint32_t idesc_pv = make_idesc_bf16_f32(ROWS, D) | (1u << 16);    // B is MN-major
+            const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s);
+            auto issue_qk = [&](int j) {
+                const int st = j & 1;
+                mbar_wait(&k_full[st], (j >> 1) & 1, p.error, 22);
+                if (j >= 2)
+                    mbar_wait(&s_free[st], ((j >> 1) - 1) & 1, p.error, 23);
+                tcgen05_fence_after();
+                const uint32_t k_addr = smem_addr(k_s + st * KV_TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
+                    tcgen05_mma_bf16(tmem_base + (st ? TMEM_S1 : TMEM_S0), make_kmajor_sw128_desc(q_addr + off),
+                                     make_kmajor_sw128_desc(k_addr + off), idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tcgen05_commit(&s_full[st]);
+                tcgen05_commit(&k_empty[st]);
+            };
+            if (n_tiles > 0)
+                issue_qk(0);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j + 1 < n_tiles)
+                    issue_qk(j + 1);                      // runs while the softmax threads work on tile j
+                const int st = j & 1;
+                mbar_wait(p_full, j & 1, p.error, 24);    // P(j) is written, O_tile(j-1) has been read
+                mbar_wait(&v_full[st], (j >> 1) & 1, p.error, 25);
+                tcgen05_fence_after();
+                const uint32_t v_addr = smem_addr(v_s + st * KV_TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < KEYS / 16; ++ks) {
+                    const uint32_t a_off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
+                    tcgen05_mma_bf16(tmem_base + TMEM_O, make_kmajor_sw128_desc(p_addr + a_off),
+                                     make_mnmajor_sw128_desc(v_addr + ks * 16 * 128, KEYS * 128), idesc_pv,
+                                     ks > 0 ? 1u : 0u);
+                }
+                tcgen05_commit(o_full);
+                tcgen05_commit(&v_empty[st]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // this thread's query row = its TMEM lane
+        const int r = row0 + row;
+        const bool live = r < rows_total;
+        const int tok = live ? r / p.group : 0;
+        const int pos = live ? pos0 + tok : -1;
+        const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        float acc[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i)
+            acc[i] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            const int key0 = key_begin + j * KEYS;
+            mbar_wait(&s_full[st], (j >> 1) & 1, p.error, 26);
+            tcgen05_fence_after();
+            const uint32_t s_addr = lane_addr + (st ? TMEM_S1 : TMEM_S0);
+            // pass 1: the row's maximum over the visible keys of this tile
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KEYS; c0 += 32) {
+                uint32_t sv[32];
+                tmem_load_32x32(s_addr + c0, sv);
+                tmem_load_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c0 + i;
+                    const bool vis = key <= pos && key >= first;
+                    mx = fmaxf(mx, vis ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float base = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = exp2f(m - base);
+            m = m_new;
+            // the P buffer is free once the product with tile j-1 has completed
+            if (j > 0)
+                mbar_wait(o_full, (j - 1) & 1, p.error, 27);
+            // pass 2: probabilities -> shared memory (swizzled K-major), row sum
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KEYS; c0 += 32) {
+                uint32_t sv[32];
+                tmem_load_32x32(s_addr + c0, sv);
+                tmem_load_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = key0 + c0 + i;
+                    const bool v0 = key <= pos && key >= first, v1 = key + 1 <= pos && key + 1 >= first;
+                    const float p0 = v0 ? exp2f(__uint_as_float(sv[i]) * p.scale_log2 - base) : 0.f;
+                    const float p1 = v1 ? exp2f(__uint_as_float(sv[i + 1]) * p.scale_log2 - base) : 0.f;
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    // the sum is taken over the rounded values that the second product uses
+                    sum += __low2float(h) + __high2float(h);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int chunk = (c0 >> 3) + cc;            // 16-byte chunk of the row: 8 keys
+                    *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * (ROWS * 128) + swizzled_chunk(row, chunk & 7)) =
+                        make_uint4(packed[4 * cc], packed[4 * cc + 1], packed[4 * cc + 2], packed[4 * cc + 3]);
+                }
+            }
+            l = l * corr + sum;
+            // values past the context may be anything (a page is loaded whole): make them zero, so
+            // that 0 * value stays 0.  Only the last tile can hold such keys.
+            if (key0 + KEYS > key_end) {
+                mbar_wait(&v_full[st], (j >> 1) & 1, p.error, 28);
+                uint8_t* v_tile = v_s + st * KV_TILE_BYTES;
+                for (int c = row; c < (key0 + KEYS - key_end) * (D / 8); c += 128) {
+                    const int krow = key_end - key0 + c / (D / 8), chunk = c % (D / 8);
+                    *reinterpret_cast<uint4*>(v_tile + (chunk >> 3) * (KEYS * 128) + swizzled_chunk(krow, chunk & 7)) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_proxy_async();
+            tcgen05_fence_before();
+            mbar_arrive(p_full);
+            mbar_arrive(&s_free[st]);
+            // the product of this tile, added to the running output
+            mbar_wait(o_full, j & 1, p.error, 29);
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t ov[32];
+                tmem_load_32x32(lane_addr + TMEM_O + c0, ov);
+                tmem_load_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    acc[c0 + i] = acc[c0 + i] * corr + __uint_as_float(ov[i]);
+            }
+            tcgen05_fence_before();
+        }
+        if (live) {
+            const int head = kv_head * p.group + (r - tok * p.group);
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)(t0 + tok) * p.nq + head) * D);
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    h[q] = __floats2bfloat162_rn(acc[8 * c + 2 * q] * inv, acc[8 * c + 2 * q + 1] * inv);
+                dst[c] = *reinterpret_cast<uint4*>(h);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+} // namespace chibi
+
+using namespace chibi;
+
+CHIBI_API int chibi_attention_tc_head_dim() { return D; }
+
+// Attention of the sequences that bring more than one token (all sequences when
+// skip_single is 0).  Returns CHIBI_ERR_UNSUPPORTED for page sizes it does not
+// take (the page size must divide 128 and be at least 8).
+CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         const int* block_table, int table_stride, const int* seq_rows,
+                                         const int* q_start, const int* ctx_len, int seqs, int nq, int nkv,
+                                         int page_size, int num_pages, float scale, int window,
+                                         int skip_single, int max_q_len, int* error, cudaStream_t stream)
+{
+    if (seqs <= 0)
+        return CHIBI_OK;
+    if (nkv <= 0 || nq % nkv != 0 || window < 0)
+        return CHIBI_ERR_ARGUMENT;
+    if (page_size < 8 || page_size > 128 || KEYS % page_size != 0
+        || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)
+        || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return CHIBI_ERR_UNSUPPORTED;
+    AttnTcParams p {};
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.seq_rows = seq_rows;
+    p.q_start = q_start;
+    p.ctx_len = ctx_len;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.group = nq / nkv;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.cache_rows = (long long)num_pages * nkv * page_size;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.skip_single = skip_single;
+    p.error = error;
+    CUtensorMap mk, mv;
+    if (!tensor_map_2d(k_cache, p.cache_rows, D, D, page_size, &mk)
+        || !tensor_map_2d(v_cache, p.cache_rows, D, D, page_size, &mv))
+        return CHIBI_ERR_UNSUPPORTED;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)ATC_SMEM);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    const long long rows = (long long)max_q_len * p.group;
+    const dim3 grid((unsigned)((rows + ROWS - 1) / ROWS), nkv, seqs);
+    launch(attn_prefill_tc_kernel, grid, dim3(ATC_THREADS), ATC_SMEM, stream, mk, mv, p);
+    return launch_status();
+}

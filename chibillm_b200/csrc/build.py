@@ -32,7 +32,10 @@ LIBRARIES: Dict[str, List[str]] = {
                       "sampling.cu"],
     # one library per head size: built with -DCHIBI_HEAD_DIM=<d> when a model needs it
     "chibi_attention_mma": ["attention_mma.cu"],
+    # prompt attention on tcgen05, head sizes 64 and 128
+    "chibi_attention_tc": ["attention_tcgen05.cu"],
 }
+TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
 # head sizes whose attention library build_all() makes ahead of time
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
@@ -158,10 +161,15 @@ def attention_library(head_dim: int, verbose: bool = True) -> str:
     return ensure_library("chibi_attention_mma", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
 
 
+def attention_tc_library(head_dim: int, verbose: bool = True) -> str:
+    return ensure_library("chibi_attention_tc", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
+
+
 def build_all(verbose: bool = True) -> List[str]:
     out = [ensure_library("chibi_kernels", verbose=verbose)]
     with ThreadPoolExecutor(max_workers=4) as pool:
         out += list(pool.map(lambda d: attention_library(d, verbose), PREBUILT_HEAD_DIMS))
+        out += list(pool.map(lambda d: attention_tc_library(d, verbose), TCGEN05_ATTENTION_HEAD_DIMS))
     return out
 
 

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from . import library
+from ..csrc import build
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
@@ -89,6 +90,8 @@ class CudaKernels:
         self.scratch_generation = 0
         self.supports_graphs = True     # every op is a plain launch on the current stream
         self._attention_libs = {}
+        self._attention_tc_libs = {}
+        self.use_tcgen05_attention = True
         self._partial_bufs = [None, None]
         self._partial_turn = 0
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
@@ -123,7 +126,8 @@ class CudaKernels:
                     11: "a wait that ran out (matrix product: loader)",
                     12: "a wait that ran out (matrix product: tensor-core issuer)",
                     13: "a wait that ran out (matrix product: epilogue)",
-                    14: "a wait that ran out (matrix product: accumulator hand-over)"}.get(code, f"code {code}")
+                    14: "a wait that ran out (matrix product: accumulator hand-over)",
+                    **{c: f"a wait that ran out (tcgen05 attention, point {c})" for c in range(21, 30)}}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
     # ------------------------------------------------------------------ ops
@@ -451,6 +455,27 @@ class CudaKernels:
             self._attention_libs[d] = lib
         seqs = ctx_len.numel()
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
+        if mode & 2 and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
+                and page_size >= 8 and 128 % page_size == 0:
+            # prompt portions on tcgen05; one-token sequences stay with the split-key kernel
+            tc = self._attention_tc_libs.get(d)
+            if tc is None:
+                tc = library.load("chibi_attention_tc", (f"CHIBI_HEAD_DIM={d}",))
+                if tc.chibi_attention_tc_head_dim() != d:
+                    raise KernelError(f"the tcgen05 attention library for head size {d} was built for another size")
+                self._attention_tc_libs[d] = tc
+            status = tc.chibi_attention_prefill_tc(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
+                float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len), _ptr(self.error),
+                self._stream())
+            if status == 0:
+                self.launches += 1
+                mode &= 1
+                if mode == 0:
+                    return
+            elif status != -2:
+                _check(status, "attention (tcgen05)")
         splits, scratch = 1, None
         if mode & 1:
             splits = self.decode_attention_splits(seqs, nq, nkv, max_ctx_len)

@@ -429,3 +429,38 @@ def test_linear_swiglu(k, ref, M, inter, K):
     close(out, exp, torch.bfloat16, "product + SwiGLU", rel=8e-3)
     k.check_error_word()
     assert k.interleave_gate_up(gate[:40], up[:40]) is None
+
+
+@pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, None), (5, 1, 128, 200), (4, 4, 64, None), (6, 2, 64, 130)])
+@pytest.mark.parametrize("page", [8, 16, 64])
+def test_attention_tcgen05_prompts(k, ref, nq, nkv, d, window, page):
+    """Prompt attention on tcgen05 (S and the per-tile output in TMEM, V as the
+    MN-major operand): several 128-key tiles, a portion that continues a long
+    context, rows of several tokens and heads in one tile, a window; and the same
+    through the mma.sync kernel."""
+    seq_ctx, q_lens = [700, 300, 130], [700, 45, 2]
+    pages = sum((c + page - 1) // page for c in seq_ctx) + 3
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, q_lens, page, pages, seed=60)
+    T = sum(q_lens)
+    q = rnd(T, nq * d, dtype=torch.bfloat16, seed=61)
+    kc = torch.full((pages, nkv, page, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    vc = torch.full((pages, nkv, page, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for s, c in enumerate(seq_ctx):
+        idx = torch.arange(c, device="cuda")
+        pg = table[s, idx // page].long()
+        kc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=torch.bfloat16, seed=2000 + s)
+        vc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=torch.bfloat16, seed=6000 + s)
+    args = (table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, 1.0 / math.sqrt(d), window,
+            max(q_lens), max(seq_ctx), min(q_lens))
+    exp = torch.empty(T, nq * d, dtype=torch.bfloat16, device="cuda")
+    ref.attention(q, kc, vc, exp, *args)
+    outs = {}
+    for tc in (True, False):
+        k.use_tcgen05_attention = tc
+        out = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        before = k.launches
+        k.attention(q, kc, vc, out, *args)
+        k.check_error_word()
+        close(out, exp, torch.bfloat16, f"prompt attention (tcgen05={tc})", rel=1.2e-2)
+        outs[tc] = out
+    k.use_tcgen05_attention = True
