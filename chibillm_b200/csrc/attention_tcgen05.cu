@@ -9,13 +9,14 @@
 //   warp 0      loads K and V tiles with TMA, one box per cache page and 64-wide
 //               half of the head (128-byte swizzle);
 //   warp 1      issues the MMAs:  S = Q K^T  (both K-major) into one of two TMEM
-//               buffers, and  O_tile = P V  with P from shared memory and V as the
-//               MN-major operand (V is stored [key][d]) into a third TMEM buffer;
+//               buffers, and  O += P V  with P from shared memory and V as the
+//               MN-major operand (V is stored [key][d]), accumulating in a third TMEM buffer;
 //   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from
-//               TMEM, keeps the running maximum and sum in registers, writes
+//               TMEM, keeps the running maximum and sum in registers and writes
 //               P = exp2(S * scale - max) as bfloat16 into shared memory in the
-//               swizzled K-major layout, and adds each O_tile to its 32-bit
-//               output row in registers after rescaling.
+//               swizzled K-major layout.  The output accumulates in TMEM over all
+//               tiles; it is rescaled there only when a row's maximum has grown by
+//               more than 2^8, and read out once at the end.
 //
 // The MMA of the next S tile is issued before the P V product of the current
 // one, so it runs while the softmax threads work.  All waits are bounded.
@@ -71,6 +72,13 @@ __device__ __forceinline__ uint32_t swizzled_chunk(int row, int chunk)
     return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
 
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // MN-major operand (here V: [key][d], d contiguous) in the same swizzled tiles:
 // leading byte offset = distance between the 64-wide slices of d, stride byte
 // offset = 8 keys * 128 B.
@@ -111,7 +119,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int t0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - t0;
     const int rows_total = q_len * p.group;
-    const int row0 = blockIdx.x * ROWS;
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * ROWS;      // the tiles with the most keys start first
     if (q_len <= 0 || (q_len == 1 && p.skip_single) || row0 >= rows_total)
         return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -227,7 +235,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     const uint32_t a_off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
                     tcgen05_mma_bf16(tmem_base + TMEM_O, make_kmajor_sw128_desc(p_addr + a_off),
                                      make_mnmajor_sw128_desc(v_addr + ks * 16 * 128, KEYS * 128), idesc_pv,
-                                     ks > 0 ? 1u : 0u);
+                                     (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(o_full);
                 tcgen05_commit(&v_empty[st]);
@@ -242,10 +250,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int pos = live ? pos0 + tok : -1;
         const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        float acc[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i)
-            acc[i] = 0.f;
+        // The output accumulates in TMEM over all tiles.  `m` is the maximum that the exponents are
+        // taken against; it follows the true maximum only when that has grown by more than 2^8
+        // (then the output so far is rescaled in TMEM, a rare event after the first tiles), so
+        // the probabilities stay below 2^8 and most tiles need no rescaling at all.
         float m = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
@@ -253,58 +261,78 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_wait(&s_full[st], (j >> 1) & 1, p.error, 26);
             tcgen05_fence_after();
             const uint32_t s_addr = lane_addr + (st ? TMEM_S1 : TMEM_S0);
-            // pass 1: the row's maximum over the visible keys of this tile
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KEYS; c0 += 32) {
-                uint32_t sv[32];
-                tmem_load_32x32(s_addr + c0, sv);
-                tmem_load_wait();
+            // the whole row of S comes into registers with one wait
+            uint32_t sv[KEYS];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c0 + i;
-                    const bool vis = key <= pos && key >= first;
-                    mx = fmaxf(mx, vis ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY);
+            for (int c0 = 0; c0 < KEYS; c0 += 32)
+                tmem_load_32x32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+            tmem_load_wait();
+            tcgen05_fence_before();
+            mbar_arrive(&s_free[st]);                        // the MMA thread may fill this buffer again
+            // masks only where a row's visible range ends inside the tile; the warp takes one path
+            const bool masked = __any_sync(0xffffffffu, key0 + KEYS - 1 > pos || key0 < first);
+            float mx = -INFINITY;
+            if (masked) {
+#pragma unroll
+                for (int i = 0; i < KEYS; ++i) {
+                    const int key = key0 + i;
+                    if (!(key <= pos && key >= first))
+                        sv[i] = 0xff800000u;                 // -inf
+                    mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < KEYS; ++i)
+                    mx = fmaxf(mx, __uint_as_float(sv[i]));
             }
-            const float m_new = fmaxf(m, mx);
-            const float base = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = exp2f(m - base);
-            m = m_new;
+            mx *= p.scale_log2;                              // the scale is positive
+            const bool grow = mx > m + 8.f;                  // also true for the first visible key (m = -inf)
+            if (__any_sync(0xffffffffu, grow && m != -INFINITY && j > 0)) {
+                // rescale what has accumulated: the product of tile j-1 must have landed first
+                mbar_wait(o_full, (j - 1) & 1, p.error, 27);
+                tcgen05_fence_after();
+                const float f = (grow && m != -INFINITY) ? fast_exp2(m - mx) : 1.f;
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_load_32x32(lane_addr + TMEM_O + c0, ov);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                    tmem_store_32x32(lane_addr + TMEM_O + c0, ov);
+                }
+                tmem_store_wait();
+                tcgen05_fence_before();
+            }
+            if (grow) {
+                l *= (m == -INFINITY) ? 0.f : fast_exp2(m - mx);
+                m = mx;
+            }
+            const float base = m == -INFINITY ? 0.f : m;
             // the P buffer is free once the product with tile j-1 has completed
             if (j > 0)
-                mbar_wait(o_full, (j - 1) & 1, p.error, 27);
-            // pass 2: probabilities -> shared memory (swizzled K-major), row sum
+                mbar_wait(o_full, (j - 1) & 1, p.error, 28);
             float sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KEYS; c0 += 32) {
-                uint32_t sv[32];
-                tmem_load_32x32(s_addr + c0, sv);
-                tmem_load_wait();
-                uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = key0 + c0 + i;
-                    const bool v0 = key <= pos && key >= first, v1 = key + 1 <= pos && key + 1 >= first;
-                    const float p0 = v0 ? exp2f(__uint_as_float(sv[i]) * p.scale_log2 - base) : 0.f;
-                    const float p1 = v1 ? exp2f(__uint_as_float(sv[i + 1]) * p.scale_log2 - base) : 0.f;
+            for (int c = 0; c < KEYS / 8; ++c) {             // 16-byte chunk of the row: 8 keys
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i]), p.scale_log2, -base));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), p.scale_log2, -base));
+                    sum += p0 + p1;
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum is taken over the rounded values that the second product uses
-                    sum += __low2float(h) + __high2float(h);
-                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int chunk = (c0 >> 3) + cc;            // 16-byte chunk of the row: 8 keys
-                    *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * (ROWS * 128) + swizzled_chunk(row, chunk & 7)) =
-                        make_uint4(packed[4 * cc], packed[4 * cc + 1], packed[4 * cc + 2], packed[4 * cc + 3]);
-                }
+                *reinterpret_cast<uint4*>(p_s + (c >> 3) * (ROWS * 128) + swizzled_chunk(row, c & 7)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l = l * corr + sum;
+            l += sum;
             // values past the context may be anything (a page is loaded whole): make them zero, so
             // that 0 * value stays 0.  Only the last tile can hold such keys.
             if (key0 + KEYS > key_end) {
-                mbar_wait(&v_full[st], (j >> 1) & 1, p.error, 28);
+                mbar_wait(&v_full[st], (j >> 1) & 1, p.error, 29);
                 uint8_t* v_tile = v_s + st * KV_TILE_BYTES;
                 for (int c = row; c < (key0 + KEYS - key_end) * (D / 8); c += 128) {
                     const int krow = key_end - key0 + c / (D / 8), chunk = c % (D / 8);
@@ -315,32 +343,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             fence_proxy_async();
             tcgen05_fence_before();
             mbar_arrive(p_full);
-            mbar_arrive(&s_free[st]);
-            // the product of this tile, added to the running output
-            mbar_wait(o_full, j & 1, p.error, 29);
-            tcgen05_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t ov[32];
-                tmem_load_32x32(lane_addr + TMEM_O + c0, ov);
-                tmem_load_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    acc[c0 + i] = acc[c0 + i] * corr + __uint_as_float(ov[i]);
-            }
-            tcgen05_fence_before();
         }
-        if (live) {
-            const int head = kv_head * p.group + (r - tok * p.group);
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)(t0 + tok) * p.nq + head) * D);
+        // the last product has landed: normalise and write the rows out
+        if (n_tiles > 0)
+            mbar_wait(o_full, (n_tiles - 1) & 1, p.error, 30);
+        tcgen05_fence_after();
+        const int head = kv_head * p.group + (r - tok * p.group);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst_row = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
-                __nv_bfloat162 h[4];
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32];
+            tmem_load_32x32(lane_addr + TMEM_O + c0, ov);
+            tmem_load_wait();
+            if (live) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    h[q] = __floats2bfloat162_rn(acc[8 * c + 2 * q] * inv, acc[8 * c + 2 * q + 1] * inv);
-                dst[c] = *reinterpret_cast<uint4*>(h);
+                for (int c = 0; c < 4; ++c) {
+                    __nv_bfloat162 h[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        h[q] = __floats2bfloat162_rn(__uint_as_float(ov[8 * c + 2 * q]) * inv,
+                                                     __uint_as_float(ov[8 * c + 2 * q + 1]) * inv);
+                    reinterpret_cast<uint4*>(dst_row + c0)[c] = *reinterpret_cast<uint4*>(h);
+                }
             }
         }
     }
