@@ -359,6 +359,100 @@ __global__ void qk_norm_rope_append_vec4_kernel(
     }
 }
 
+// Many tokens, heads of 128 features rotated whole: one block of eight warps per
+// token, no shared memory.  A lane holds features 4*lane .. 4*lane+3 of a head, so
+// the partner of a feature in the rotation (64 features away) sits 16 lanes away
+// and comes by one shuffle.  Warp w takes heads w, w+8, ...; their loads all go
+// out before the token's cosines and sines are computed.
+constexpr int ROWS_KERNEL_WARPS = 8;
+constexpr int ROWS_KERNEL_MAX_JOBS = 8;       // heads per warp: nq + 2 * nkv <= 64
+
+template <typename TX, typename TW, typename TC>
+__global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d128_kernel(
+    const TX* __restrict__ qkv, long long qkv_stride, TX* __restrict__ q_out, TC* __restrict__ k_cache,
+    TC* __restrict__ v_cache, const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
+    const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
+    int num_pages, float eps, float norm_offset, int append, int* __restrict__ error)
+{
+    pdl_enter();
+    constexpr int D = 128;
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    const int jobs = append ? nq + 2 * nkv : nq;
+    long long cache_base = -1;
+    if (append) {
+        const int seq = seq_of_token[t];
+        const int table_row = seq_rows ? seq_rows[seq] : seq;
+        const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && error)
+                atomicExch(error, 2);
+        } else {
+            cache_base = ((long long)page * nkv * page_size + (pos % page_size)) * D;
+        }
+    }
+    const TX* src = qkv + (size_t)t * qkv_stride + lane * 4;
+    float v[ROWS_KERNEL_MAX_JOBS][4];
+#pragma unroll
+    for (int jj = 0; jj < ROWS_KERNEL_MAX_JOBS; ++jj) {
+        const int job = warp + jj * ROWS_KERNEL_WARPS;
+        if (job < jobs && (job < nq || cache_base >= 0))
+            Vec4<TX>::load(src + (size_t)job * D, v[jj]);
+        else
+            v[jj][0] = v[jj][1] = v[jj][2] = v[jj][3] = 0.f;
+    }
+    float wq[4], wk[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        wq[u] = q_norm_w ? to_f32(q_norm_w[lane * 4 + u]) + norm_offset : 1.f;
+        wk[u] = k_norm_w ? to_f32(k_norm_w[lane * 4 + u]) + norm_offset : 1.f;
+    }
+    float c[4], s[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        sincosf((float)pos * inv_freq[(lane & 15) * 4 + u], &s[u], &c[u]);
+        if (lane < 16)
+            s[u] = -s[u];                      // low half: x0 * c - x1 * s; high half: x1 * c + x0 * s
+    }
+#pragma unroll
+    for (int jj = 0; jj < ROWS_KERNEL_MAX_JOBS; ++jj) {
+        const int job = warp + jj * ROWS_KERNEL_WARPS;
+        if (job >= jobs || (job >= nq && cache_base < 0))
+            continue;
+        if (job >= nq + nkv) {
+            Vec4<TC>::store(v_cache + cache_base + (long long)(job - nq - nkv) * page_size * D + lane * 4, v[jj]);
+            continue;
+        }
+        const bool is_q = job < nq;
+        const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
+        float x[4] = { v[jj][0], v[jj][1], v[jj][2], v[jj][3] };
+        if (normed) {
+            float sum = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                sum = fmaf(x[u], x[u], sum);
+            sum = warp_sum(sum);
+            const float inv = rsqrtf(sum / (float)D + eps);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                x[u] = (x[u] * inv) * (is_q ? wq[u] : wk[u]);
+        }
+        float out[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float partner = __shfl_xor_sync(0xffffffffu, x[u], 16);
+            out[u] = x[u] * c[u] + partner * s[u];
+        }
+        if (is_q)
+            Vec4<TX>::store(q_out + ((size_t)t * nq + job) * D + lane * 4, out);
+        else
+            Vec4<TC>::store(k_cache + cache_base + (long long)(job - nq) * page_size * D + lane * 4, out);
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // gate_up[t, 0:I] = gate, gate_up[t, I:2I] = up; out = gate / (1 + exp(-gate)) * up.
 template <typename TX, typename TO>
@@ -535,24 +629,26 @@ CHIBI_API int chibi_qk_norm_rope_append(
     const bool aligned = d % 4 == 0 && qkv_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0
         && (reinterpret_cast<uintptr_t>(q_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0
         && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
-    if (aligned) {
-        const int jpw = 1;      // four jobs per warp measured slower at 2,048 tokens (68 us against 51 us)
-        const int per_block = warps * jpw;
-        const dim3 grid4((unsigned)tokens, (unsigned)((jobs + per_block - 1) / per_block));
-        const size_t smem4 = (size_t)(per_block * d + rot) * sizeof(float);
+    if (aligned && d == 128 && rot == d && tokens >= 32 && jobs <= ROWS_KERNEL_WARPS * ROWS_KERNEL_MAX_JOBS) {
         CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-            if (jpw == 4)
-                launch(qk_norm_rope_append_vec4_kernel<4, TX, TX, TW, TC>, dim3(grid4), dim3(warps * 32), smem4,
-                       stream, (const TX*)qkv, qkv_stride, 1, 0, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
-                       (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
-                       block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
-                       append, error);
-            else
-                launch(qk_norm_rope_append_vec4_kernel<1, TX, TX, TW, TC>, dim3(grid4), dim3(warps * 32), smem4,
-                       stream, (const TX*)qkv, qkv_stride, 1, 0, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
-                       (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
-                       block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
-                       append, error);
+            launch(qk_norm_rope_append_d128_kernel<TX, TW, TC>, dim3((unsigned)tokens),
+                   dim3(ROWS_KERNEL_WARPS * 32), 0, stream, (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache,
+                   (TC*)v_cache, (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token,
+                   seq_rows, block_table, table_stride, nq, nkv, page_size, num_pages, eps, norm_offset, append,
+                   error);
+        })));
+        return launch_status();
+    }
+    if (aligned) {
+        // one head per warp: four per warp measured slower at 2,048 tokens (68 us against 51 us)
+        const dim3 grid4((unsigned)tokens, (unsigned)((jobs + warps - 1) / warps));
+        const size_t smem4 = (size_t)(warps * d + rot) * sizeof(float);
+        CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
+            launch(qk_norm_rope_append_vec4_kernel<1, TX, TX, TW, TC>, dim3(grid4), dim3(warps * 32), smem4,
+                   stream, (const TX*)qkv, qkv_stride, 1, 0, (TX*)q_out, (TC*)k_cache, (TC*)v_cache,
+                   (const TW*)q_norm_w, (const TW*)k_norm_w, inv_freq, positions, seq_of_token, seq_rows,
+                   block_table, table_stride, nq, nkv, d, rot, page_size, num_pages, eps, norm_offset,
+                   append, error);
         })));
         return launch_status();
     }

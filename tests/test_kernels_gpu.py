@@ -118,10 +118,12 @@ def _paged_setup(seq_ctx, q_lens, page_size, num_pages, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,rot,norms", [(6, 2, 48, 48, True), (4, 4, 16, 8, True),
-                                                (5, 1, 128, 128, False), (2, 1, 32, 0, True)])
-def test_qk_norm_rope_append(k, ref, dtype, nq, nkv, d, rot, norms):
+                                                (5, 1, 128, 128, False), (2, 1, 32, 0, True),
+                                                (9, 3, 128, 128, True)])
+@pytest.mark.parametrize("seq_ctx,q_lens", [([19, 8, 70], [19, 1, 7]),
+                                            ([70, 8, 90], [40, 1, 33])])   # many tokens: the per-token kernel
+def test_qk_norm_rope_append(k, ref, dtype, nq, nkv, d, rot, norms, seq_ctx, q_lens):
     page, pages = 8, 40
-    seq_ctx, q_lens = [19, 8, 70], [19, 1, 7]
     table, positions, seq_of_token, _, _ = _paged_setup(seq_ctx, q_lens, page, pages, seed=7)
     T = sum(q_lens)
     qkv = rnd(T, (nq + 2 * nkv) * d, dtype=dtype, seed=8)
