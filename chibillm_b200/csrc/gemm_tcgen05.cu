@@ -363,14 +363,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 }
 
 // ------------------------------------------------------------------ many rows: one CTA per SM
-// The epilogue of one 128 x BN tile whose rows are tokens (x is the A operand):
-// this thread owns row `m`; `taddr` is the TMEM address of its lane at the tile's
-// first column.
-template <int BN>
-__device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m, int tile_b)
+// The epilogue of one 128 x BN tile whose rows are tokens (x is the A operand).
+// tcgen05.ld gives a thread one row of the tile; written out like that, every
+// store instruction of a warp would touch 32 rows with 16 bytes each.  So a warp
+// passes each 32 x 128-byte piece through a staging buffer in shared memory
+// (16-byte units, XOR-swizzled by row so that neither side has bank conflicts)
+// and writes it with eight lanes per row: four whole 128-byte lines per
+// instruction.  `taddr` is the TMEM address of this thread's lane at the tile's
+// first column, `m0` the matrix row of the warp's first lane.
+constexpr int EPILOGUE_STAGE_BYTES = 32 * 128;     // per epilogue warp
+
+__device__ __forceinline__ uint4* stage_unit(uint8_t* stage, int row, int unit)
 {
-    if (p.swiglu) {
+    return reinterpret_cast<uint4*>(stage + row * 128 + ((unit ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u)
+{
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m0, int lane,
+                                                    int tile_b, uint8_t* stage)
+{
+    const int m = m0 + lane;
+    const int sub = lane >> 3, unit = lane & 7;      // the write-out: rows 4 * i + sub, 16-byte unit `unit`
+    const bool inside = (tile_b + 1) * BN <= p.N && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    // every branch below is taken by whole warps: tcgen05.ld is a warp-wide instruction
+    if (p.swiglu && inside && p.out_stride % 8 == 0) {
         // the BN columns are rows of w, which come as [64 gate | 64 up] blocks
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 128) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t g[32], u[32];
+                tmem_load_32x32(taddr + c0 + 32 * h, g);
+                tmem_load_32x32(taddr + c0 + 64 + 32 * h, u);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        v[q] = __floats2bfloat162_rn(
+                            silu_mul(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q])),
+                            silu_mul(__uint_as_float(g[8 * j + 2 * q + 1]), __uint_as_float(u[8 * j + 2 * q + 1])));
+                    *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
+                }
+            }
+            __syncwarp();
+            const int feat0 = (tile_b * BN + c0) >> 1;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + sub;
+                const uint4 v = *stage_unit(stage, r, unit);
+                if (m0 + r < p.M)
+                    *reinterpret_cast<uint4*>(out + (size_t)(m0 + r) * p.out_stride + feat0 + unit * 8) = v;
+            }
+            __syncwarp();
+        }
+        return;
+    }
+    if (p.swiglu) {
         const int inter = p.N >> 1;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -382,29 +438,92 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
             tmem_load_wait();
             const int w_row = tile_b * BN + c0;
             const int feat0 = (w_row >> 7) * 64 + (w_row & 63);
-            if (m >= p.M)
-                continue;
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + feat0;
-            if (feat0 + 32 <= inter && p.out_stride % 8 == 0) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 h[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float g0 = __uint_as_float(g[8 * j + 2 * q]), g1 = __uint_as_float(g[8 * j + 2 * q + 1]);
-                        const float u0 = __uint_as_float(u[8 * j + 2 * q]), u1 = __uint_as_float(u[8 * j + 2 * q + 1]);
-                        h[q] = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * u0,
-                                                     __fdividef(g1, 1.f + __expf(-g1)) * u1);
-                    }
-                    reinterpret_cast<uint4*>(dst)[j] = *reinterpret_cast<uint4*>(h);
-                }
-            } else {
+            if (m < p.M) {
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + feat0;
                 for (int j = 0; j < 32; ++j)
                     if (feat0 + j < inter) {
                         const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
                         dst[j] = __float2bfloat16_rn((gv / (1.f + expf(-gv))) * uv);
                     }
             }
+            __syncwarp();
+        }
+        return;
+    }
+    if (p.out_type == CHIBI_F32 && inside && p.out_stride % 4 == 0
+        && (!p.residual || (p.res_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0))) {
+        // out may be the residual itself: the residual of the next 32 columns is
+        // fetched before this piece is stored (the compiler may not move it up)
+        float* out = static_cast<float*>(p.out);
+        const float* res = p.residual;
+        const int n_tile = tile_b * BN;
+        float4 q[8], qn[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = m0 + 4 * i + sub;
+            q[i] = (res && r < p.M) ? *reinterpret_cast<const float4*>(res + (size_t)r * p.res_stride + n_tile + unit * 4)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r32[32];
+            tmem_load_32x32(taddr + c0, r32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = m0 + 4 * i + sub;
+                qn[i] = (res && r < p.M && c0 + 32 < BN)
+                    ? *reinterpret_cast<const float4*>(res + (size_t)r * p.res_stride + n_tile + c0 + 32 + unit * 4)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            tmem_load_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *stage_unit(stage, lane, j) = make_uint4(r32[4 * j], r32[4 * j + 1], r32[4 * j + 2], r32[4 * j + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + sub;
+                const uint4 v = *stage_unit(stage, r, unit);
+                if (m0 + r < p.M)
+                    *reinterpret_cast<float4*>(out + (size_t)(m0 + r) * p.out_stride + n_tile + c0 + unit * 4) =
+                        make_float4(q[i].x + __uint_as_float(v.x), q[i].y + __uint_as_float(v.y),
+                                    q[i].z + __uint_as_float(v.z), q[i].w + __uint_as_float(v.w));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                q[i] = qn[i];
+        }
+        return;
+    }
+    if (p.out_type == CHIBI_BF16 && !p.residual && inside && p.out_stride % 8 == 0) {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t r32[32];
+                tmem_load_32x32(taddr + c0 + 32 * h, r32);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        v[q] = __floats2bfloat162_rn(__uint_as_float(r32[8 * j + 2 * q]),
+                                                     __uint_as_float(r32[8 * j + 2 * q + 1]));
+                    *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + sub;
+                const uint4 v = *stage_unit(stage, r, unit);
+                if (m0 + r < p.M)
+                    *reinterpret_cast<uint4*>(out + (size_t)(m0 + r) * p.out_stride + tile_b * BN + c0 + unit * 8) = v;
+            }
+            __syncwarp();
         }
         return;
     }
@@ -413,38 +532,10 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         uint32_t r[32];
         tmem_load_32x32(taddr + c0, r);
         tmem_load_wait();
-        const int n0 = tile_b * BN + c0;
-        const bool vec = m < p.M && n0 + 32 <= p.N && (p.out_stride % 8 == 0)
-            && (!p.residual || p.res_stride % 4 == 0);
-        if (vec && p.out_type == CHIBI_F32) {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)m * p.out_stride + n0);
-            const float4* res = p.residual
-                ? reinterpret_cast<const float4*>(p.residual + (size_t)m * p.res_stride + n0) : nullptr;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (res) {
-                    const float4 q = res[j];
-                    v.x = q.x + v.x; v.y = q.y + v.y; v.z = q.z + v.z; v.w = q.w + v.w;
-                }
-                dst[j] = v;
-            }
-        } else if (vec && p.out_type == CHIBI_BF16 && !p.residual) {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + n0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 h[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    h[q] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * q]), __uint_as_float(r[8 * j + 2 * q + 1]));
-                dst[j] = *reinterpret_cast<uint4*>(h);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                store_value(p, m, n0 + j, __uint_as_float(r[j]));
-        }
+        for (int j = 0; j < 32; ++j)
+            store_value(p, m, tile_b * BN + c0 + j, __uint_as_float(r[j]));
+        __syncwarp();
     }
 }
 
@@ -468,6 +559,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t* tmem_full_bar = empty_bar + STAGES;     // [2]
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;     // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    uint8_t* stage_base = reinterpret_cast<uint8_t*>(tmem_slot + 4);      // 16-byte aligned
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_count = p.k_blocks_total;
     constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -555,7 +647,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 13);
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32 + lane, tile_b);
+            epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
+                                    stage_base + quarter * EPILOGUE_STAGE_BYTES);
             tcgen05_fence_before();
             mbar_arrive(&tmem_empty_bar[buf]);
         }
@@ -621,7 +714,8 @@ template <int BN, int STAGES>
 static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
                                   int tiles_m, int tiles_n, cudaStream_t stream)
 {
-    constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16
+        + 4 * EPILOGUE_STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
