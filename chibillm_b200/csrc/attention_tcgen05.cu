@@ -13,8 +13,8 @@
 //               MN-major operand (V is stored [key][d]), accumulating in a third TMEM buffer;
 //   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from
 //               TMEM, keeps the running maximum and sum in registers and writes
-//               P = exp2(S * scale - max) as bfloat16 into shared memory in the
-//               swizzled K-major layout.  The output accumulates in TMEM over all
+//               P = exp2(S * scale - max) as bfloat16 into one of two buffers in
+//               shared memory, in the swizzled K-major layout.  The output accumulates in TMEM over all
 //               tiles; it is rescaled there only when a row's maximum has grown by
 //               more than 2^8, and read out once at the end.
 //
@@ -41,8 +41,8 @@ constexpr int ATC_THREADS = 192;
 constexpr int Q_BYTES = ROWS * D * 2;
 constexpr int KV_TILE_BYTES = KEYS * D * 2;  // one K or V tile
 constexpr int P_BYTES = ROWS * KEYS * 2;
-constexpr int SMEM_TILES = Q_BYTES + 4 * KV_TILE_BYTES + P_BYTES;
-constexpr int NUM_BARS = 14;
+constexpr int SMEM_TILES = Q_BYTES + 4 * KV_TILE_BYTES + 2 * P_BYTES;
+constexpr int NUM_BARS = 16;
 constexpr size_t ATC_SMEM = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;
 constexpr uint32_t TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256;
 
@@ -103,7 +103,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Q_BYTES;                  // two stages
     uint8_t* v_s = k_s + 2 * KV_TILE_BYTES;        // two stages
-    uint8_t* p_s = v_s + 2 * KV_TILE_BYTES;
+    uint8_t* p_s = v_s + 2 * KV_TILE_BYTES;        // two buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
     uint64_t* k_full = bars;          // [2] TMA
     uint64_t* v_full = bars + 2;      // [2] TMA
@@ -111,8 +111,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* v_empty = bars + 6;     // [2] MMA commit
     uint64_t* s_full = bars + 8;      // [2] MMA commit
     uint64_t* s_free = bars + 10;     // [2] 128 threads
-    uint64_t* p_full = bars + 12;     // 128 threads
-    uint64_t* o_full = bars + 13;     // MMA commit (also frees P)
+    uint64_t* p_full = bars + 12;     // [2] 128 threads
+    uint64_t* o_full = bars + 14;     // [2] MMA commit: O holds tile j, P buffer j % 2 is free
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
 
     const int seq = blockIdx.z, kv_head = blockIdx.y;
@@ -142,8 +142,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_init(&s_full[i], 1);
             mbar_init(&s_free[i], 128);
         }
-        mbar_init(p_full, 128);
-        mbar_init(o_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&p_full[i], 128);
+            mbar_init(&o_full[i], 1);
+        }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -168,42 +170,54 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (elect_one()) {
+        // Lane i brings page i of every 128-key tile (at most 16 pages: page_size >= 8).
+        // A lane looks its page up one tile ahead, so the dependent read of the block
+        // table is over by the time the stage is free.
+        if (lane == 0) {
             tma_prefetch_descriptor(&map_k);
             tma_prefetch_descriptor(&map_v);
-            const int pages_per_tile = KEYS / p.page_size;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int st = j & 1;
-                const uint32_t round = j >> 1;
-                for (int which = 0; which < 2; ++which) {       // keys, then values
-                    uint64_t* full = which ? &v_full[st] : &k_full[st];
-                    uint64_t* empty = which ? &v_empty[st] : &k_empty[st];
-                    uint8_t* dst = (which ? v_s : k_s) + st * KV_TILE_BYTES;
+        }
+        const int pages_per_tile = KEYS / p.page_size;
+        auto first_row_of = [&](int j) -> long long {
+            const int key = key_begin + j * KEYS + lane * p.page_size;
+            if (lane >= pages_per_tile || key >= key_end)
+                return p.cache_rows;      // past the context: read outside the array, zeros
+            const int page = table[key / p.page_size];
+            if (page < 0 || page >= p.num_pages) {
+                if (p.error)
+                    atomicExch(p.error, 3);
+                return p.cache_rows;
+            }
+            return ((long long)page * p.nkv + kv_head) * p.page_size;
+        };
+        long long row = n_tiles > 0 ? first_row_of(0) : 0;
+        for (int j = 0; j < n_tiles; ++j) {
+            const long long row_next = j + 1 < n_tiles ? first_row_of(j + 1) : 0;
+            const int st = j & 1;
+            const uint32_t round = j >> 1;
+            for (int which = 0; which < 2; ++which) {       // keys, then values
+                uint64_t* full = which ? &v_full[st] : &k_full[st];
+                uint64_t* empty = which ? &v_empty[st] : &k_empty[st];
+                uint8_t* dst = (which ? v_s : k_s) + st * KV_TILE_BYTES;
+                if (lane == 0) {
                     if (round > 0)
                         mbar_wait(empty, (round - 1) & 1, p.error, 21);
                     mbar_arrive_expect_tx(full, KV_TILE_BYTES);
-                    for (int pg = 0; pg < pages_per_tile; ++pg) {
-                        const int key = key_begin + j * KEYS + pg * p.page_size;
-                        int page = -1;
-                        if (key < key_end)
-                            page = table[key / p.page_size];
-                        if (key < key_end && (page < 0 || page >= p.num_pages) && p.error)
-                            atomicExch(p.error, 3);
-                        // a page past the context (or a bad one) is read outside the array: zeros
-                        const long long row = (page >= 0 && page < p.num_pages)
-                            ? ((long long)page * p.nkv + kv_head) * p.page_size : p.cache_rows;
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_2d(dst + h * (KEYS * 128) + pg * p.page_size * 128, which ? &map_v : &map_k,
-                                        full, h * 64, (int)row);
-                    }
+                }
+                __syncwarp();
+                if (lane < pages_per_tile) {
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(dst + h * (KEYS * 128) + lane * p.page_size * 128, which ? &map_v : &map_k,
+                                    full, h * 64, (int)row);
                 }
             }
+            row = row_next;
         }
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc_qk = make_idesc_bf16_f32(ROWS, KEYS);
             constexpr uint32_t idesc_pv = make_idesc_bf16_f32(ROWS, D) | (1u << 16);    // B is MN-major
-            const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s);
+            const uint32_t q_addr = smem_addr(q_s);
             auto issue_qk = [&](int j) {
                 const int st = j & 1;
                 mbar_wait(&k_full[st], (j >> 1) & 1, p.error, 22);
@@ -226,10 +240,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 if (j + 1 < n_tiles)
                     issue_qk(j + 1);                      // runs while the softmax threads work on tile j
                 const int st = j & 1;
-                mbar_wait(p_full, j & 1, p.error, 24);    // P(j) is written, O_tile(j-1) has been read
+                mbar_wait(&p_full[st], (j >> 1) & 1, p.error, 24);    // P(j) is written
                 mbar_wait(&v_full[st], (j >> 1) & 1, p.error, 25);
                 tcgen05_fence_after();
                 const uint32_t v_addr = smem_addr(v_s + st * KV_TILE_BYTES);
+                const uint32_t p_addr = smem_addr(p_s + st * P_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < KEYS / 16; ++ks) {
                     const uint32_t a_off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
@@ -237,7 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                                      make_mnmajor_sw128_desc(v_addr + ks * 16 * 128, KEYS * 128), idesc_pv,
                                      (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tcgen05_commit(o_full);
+                tcgen05_commit(&o_full[st]);
                 tcgen05_commit(&v_empty[st]);
             }
         }
@@ -289,7 +304,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const bool grow = mx > m + 8.f;                  // also true for the first visible key (m = -inf)
             if (__any_sync(0xffffffffu, grow && m != -INFINITY && j > 0)) {
                 // rescale what has accumulated: the product of tile j-1 must have landed first
-                mbar_wait(o_full, (j - 1) & 1, p.error, 27);
+                mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, p.error, 27);
                 tcgen05_fence_after();
                 const float f = (grow && m != -INFINITY) ? fast_exp2(m - mx) : 1.f;
 #pragma unroll
@@ -310,9 +325,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 m = mx;
             }
             const float base = m == -INFINITY ? 0.f : m;
-            // the P buffer is free once the product with tile j-1 has completed
-            if (j > 0)
-                mbar_wait(o_full, (j - 1) & 1, p.error, 28);
+            // this P buffer is free once the product with tile j-2 has completed
+            if (j >= 2)
+                mbar_wait(&o_full[st], ((j >> 1) - 1) & 1, p.error, 28);
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < KEYS / 8; ++c) {             // 16-byte chunk of the row: 8 keys
@@ -325,7 +340,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-                *reinterpret_cast<uint4*>(p_s + (c >> 3) * (ROWS * 128) + swizzled_chunk(row, c & 7)) =
+                *reinterpret_cast<uint4*>(p_s + st * P_BYTES + (c >> 3) * (ROWS * 128) + swizzled_chunk(row, c & 7)) =
                     make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l += sum;
@@ -342,11 +357,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             fence_proxy_async();
             tcgen05_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[st]);
         }
         // the last product has landed: normalise and write the rows out
         if (n_tiles > 0)
-            mbar_wait(o_full, (n_tiles - 1) & 1, p.error, 30);
+            mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, p.error, 30);
         tcgen05_fence_after();
         const int head = kv_head * p.group + (r - tok * p.group);
         const float inv = l > 0.f ? 1.f / l : 0.f;
