@@ -286,20 +286,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_arrive(&s_free[st]);                        // the MMA thread may fill this buffer again
             // masks only where a row's visible range ends inside the tile; the warp takes one path
             const bool masked = __any_sync(0xffffffffu, key0 + KEYS - 1 > pos || key0 < first);
-            float mx = -INFINITY;
             if (masked) {
 #pragma unroll
                 for (int i = 0; i < KEYS; ++i) {
                     const int key = key0 + i;
                     if (!(key <= pos && key >= first))
                         sv[i] = 0xff800000u;                 // -inf
-                    mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < KEYS; ++i)
-                    mx = fmaxf(mx, __uint_as_float(sv[i]));
             }
+            float mx4[4] = { -INFINITY, -INFINITY, -INFINITY, -INFINITY };   // four short chains, not one long one
+#pragma unroll
+            for (int i = 0; i < KEYS; i += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    mx4[u] = fmaxf(mx4[u], __uint_as_float(sv[i + u]));
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= p.scale_log2;                              // the scale is positive
             const bool grow = mx > m + 8.f;                  // also true for the first visible key (m = -inf)
             if (__any_sync(0xffffffffu, grow && m != -INFINITY && j > 0)) {
@@ -328,7 +330,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // this P buffer is free once the product with tile j-2 has completed
             if (j >= 2)
                 mbar_wait(&o_full[st], ((j >> 1) - 1) & 1, p.error, 28);
-            float sum = 0.f;
+            float sum4[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll
             for (int c = 0; c < KEYS / 8; ++c) {             // 16-byte chunk of the row: 8 keys
                 uint32_t packed[4];
@@ -336,14 +338,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 for (int i = 0; i < 4; ++i) {
                     const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i]), p.scale_log2, -base));
                     const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), p.scale_log2, -base));
-                    sum += p0 + p1;
+                    sum4[i] += p0 + p1;
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 *reinterpret_cast<uint4*>(p_s + st * P_BYTES + (c >> 3) * (ROWS * 128) + swizzled_chunk(row, c & 7)) =
                     make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // values past the context may be anything (a page is loaded whole): make them zero, so
             // that 0 * value stays 0.  Only the last tile can hold such keys.
             if (key0 + KEYS > key_end) {

@@ -64,11 +64,16 @@ rmsnorm_f32_bf16_kernel(const float* x, const __nv_bfloat16* __restrict__ w, __n
     __nv_bfloat16* dst = out + (size_t)blockIdx.x * out_stride;
     const int n4 = n >> 2;
     float4 v[4];
-    float s = 0.f;
+    uint2 wq[4];                  // the weights travel together with the row, not after the sum
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int j = threadIdx.x + i * blockDim.x;
         v[i] = j < n4 ? row[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        wq[i] = j < n4 ? *reinterpret_cast<const uint2*>(w + 4 * j) : make_uint2(0u, 0u);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
         s = fmaf(v[i].x, v[i].x, s);
         s = fmaf(v[i].y, v[i].y, s);
         s = fmaf(v[i].z, v[i].z, s);
@@ -80,7 +85,7 @@ rmsnorm_f32_bf16_kernel(const float* x, const __nv_bfloat16* __restrict__ w, __n
     for (int i = 0; i < 4; ++i) {
         const int j = threadIdx.x + i * blockDim.x;
         if (j < n4) {
-            const uint2 wv = *reinterpret_cast<const uint2*>(w + 4 * j);
+            const uint2 wv = wq[i];
             const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv.x);
             const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
             const __nv_bfloat162 o01 = __floats2bfloat162_rn((v[i].x * inv) * (__low2float(w01) + offset),
@@ -360,10 +365,11 @@ __global__ void qk_norm_rope_append_vec4_kernel(
 }
 
 // Many tokens, heads of 128 features rotated whole: one block of eight warps per
-// token, no shared memory.  A lane holds features 4*lane .. 4*lane+3 of a head, so
+// token; the heads stay in registers.  A lane holds features 4*lane .. 4*lane+3 of a head, so
 // the partner of a feature in the rotation (64 features away) sits 16 lanes away
 // and comes by one shuffle.  Warp w takes heads w, w+8, ...; their loads all go
-// out before the token's cosines and sines are computed.
+// out before the token's cosines and sines are computed (once per block, in
+// shared memory).
 constexpr int ROWS_KERNEL_WARPS = 8;
 constexpr int ROWS_KERNEL_MAX_JOBS = 8;       // heads per warp: nq + 2 * nkv <= 64
 
@@ -410,12 +416,22 @@ __global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d1
         wq[u] = q_norm_w ? to_f32(q_norm_w[lane * 4 + u]) + norm_offset : 1.f;
         wk[u] = k_norm_w ? to_f32(k_norm_w[lane * 4 + u]) + norm_offset : 1.f;
     }
+    // the token's 64 cosines and sines, each computed once per block
+    __shared__ __align__(16) float cs[D];
+    if (threadIdx.x < D / 2) {
+        float sn, cn;
+        sincosf((float)pos * inv_freq[threadIdx.x], &sn, &cn);
+        cs[threadIdx.x] = cn;
+        cs[D / 2 + threadIdx.x] = sn;
+    }
+    __syncthreads();
     float c[4], s[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        sincosf((float)pos * inv_freq[(lane & 15) * 4 + u], &s[u], &c[u]);
-        if (lane < 16)
-            s[u] = -s[u];                      // low half: x0 * c - x1 * s; high half: x1 * c + x0 * s
+    {
+        const float4 cv = *reinterpret_cast<const float4*>(cs + (lane & 15) * 4);
+        const float4 sv = *reinterpret_cast<const float4*>(cs + D / 2 + (lane & 15) * 4);
+        const float sign = lane < 16 ? -1.f : 1.f;     // low half: x0 * c - x1 * s; high half: x1 * c + x0 * s
+        c[0] = cv.x; c[1] = cv.y; c[2] = cv.z; c[3] = cv.w;
+        s[0] = sign * sv.x; s[1] = sign * sv.y; s[2] = sign * sv.z; s[3] = sign * sv.w;
     }
 #pragma unroll
     for (int jj = 0; jj < ROWS_KERNEL_MAX_JOBS; ++jj) {
