@@ -97,22 +97,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 // zeroed.  One warp: lanes 0..15 look up the page of one row each (one division
 // per row, shared by K and V), the row offsets travel by shuffle, and every lane
 // issues its 16-byte chunks.
-__device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
-                                               const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
-                                               const int* table, int kv_head, int nkv, int page_size,
-                                               int num_pages, int key0, int key_end, int lane, int* error)
+// The cache page of lane's key (lane % 16) of the 16-key tile at key0; -1 past the context.
+__device__ __forceinline__ int lookup_tile_page(const int* table, int page_size, int key0, int key_end, int lane)
+{
+    const int key = key0 + (lane & 15);
+    return key < key_end ? table[key / page_size] : -1;
+}
+
+// Issues the copies of a 16-key tile whose pages `lookup_tile_page` has fetched.
+__device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
+                                                     const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
+                                                     int page, int kv_head, int nkv, int page_size, int num_pages,
+                                                     int key0, int key_end, int lane, int* error)
 {
     long long off = -1;
     {
         const int key = key0 + (lane & 15);
         if (key < key_end) {
-            const int block = key / page_size;
-            const int page = table[block];
             if (page < 0 || page >= num_pages) {
                 if (error)
                     atomicExch(error, 3);
             } else {
-                off = (((long long)page * nkv + kv_head) * page_size + (key - block * page_size)) * D;
+                off = (((long long)page * nkv + kv_head) * page_size + key % page_size) * D;
             }
         }
     }
@@ -126,6 +132,15 @@ __device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat
         cp_async16(k_dst + row * DPAD + col * 8, k_cache + src, valid);
         cp_async16(v_dst + row * DPAD + col * 8, v_cache + src, valid);
     }
+}
+
+__device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
+                                               const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
+                                               const int* table, int kv_head, int nkv, int page_size,
+                                               int num_pages, int key0, int key_end, int lane, int* error)
+{
+    load_kv_tile16_paged(k_dst, v_dst, k_cache, v_cache, lookup_tile_page(table, page_size, key0, key_end, lane),
+                         kv_head, nkv, page_size, num_pages, key0, key_end, lane, error);
 }
 
 // Loads the A fragments of a 16-row query tile from shared memory.
@@ -314,12 +329,18 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     const int my_first_tile = tile_begin + warp;
     const int my_tiles = my_first_tile < tile_end ? (tile_end - my_first_tile + DEC_WARPS - 1) / DEC_WARPS : 0;
 
+    // the page of tile i + 1 is looked up when tile i is issued, so the dependent read of the
+    // block table is never waited for
+    auto key0_of = [&](int i) { return first + (my_first_tile + i * DEC_WARPS) * DEC_TILE; };
+    int page_ahead = my_tiles > 0 ? lookup_tile_page(table, p.page_size, key0_of(0), key_end, lane) : -1;
     auto issue = [&](int i) {
         if (i < my_tiles) {
-            const int key0 = first + (my_first_tile + i * DEC_WARPS) * DEC_TILE;
+            const int page = page_ahead;
+            if (i + 1 < my_tiles)
+                page_ahead = lookup_tile_page(table, p.page_size, key0_of(i + 1), key_end, lane);
             __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
-            load_kv_tile16(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, table, kv_head, p.nkv,
-                           p.page_size, p.num_pages, key0, key_end, lane, p.error);
+            load_kv_tile16_paged(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, page, kv_head, p.nkv,
+                                 p.page_size, p.num_pages, key0_of(i), key_end, lane, p.error);
         }
         cp_async_commit();
     };

@@ -440,10 +440,11 @@ class CudaKernels:
             float(scale), int(window or 0), _ptr(self.error), self._stream()), "attention")
 
     def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
-        """Key ranges per sequence of the decode attention kernel: enough CTAs to
-        fill the GPU twice, at least 64 keys per range."""
+        """Key ranges per sequence of the decode attention kernel: as many CTAs as
+        are resident at once (two per SM) and no more, so that no CTA waits for a
+        second round; at least 64 keys per range."""
         ctas = seqs * nkv * ((nq // nkv + 15) // 16)
-        return max(1, min(-(-2 * self.sm_count // ctas), -(-max_ctx_len // 64), 64))
+        return max(1, min(2 * self.sm_count // ctas, -(-max_ctx_len // 64), 64))
 
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:
