@@ -281,11 +281,14 @@ constexpr size_t DEC_SMEM = DEC_SMEM_PIPE > DEC_SMEM_MERGE ? DEC_SMEM_PIPE : DEC
 
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p)
 {
-    pdl_enter();
+    pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* pipe = q_tile + DEC_Q_ELEMS;
 
+    // The index arrays, the block table and every key before the newest one were written
+    // before this step's first kernel: the first tiles are on their way while the kernel
+    // that writes q and the newest key still runs.
     const int seq = blockIdx.z, split = blockIdx.x;
     const int row_blocks = (p.group + 15) / 16;
     const int kv_head = blockIdx.y / row_blocks, row_block = blockIdx.y - kv_head * row_blocks;
@@ -306,6 +309,38 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     const int rows = min(16, p.group - row_block * 16);          // query heads in this tile
     const int head0 = kv_head * p.group + row_block * 16;
 
+    __nv_bfloat16* my_pipe = pipe + (size_t)warp * DEC_STAGES * DEC_STAGE_ELEMS;
+    const int my_first_tile = tile_begin + warp;
+    const int my_tiles = my_first_tile < tile_end ? (tile_end - my_first_tile + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    // the page of tile i + 1 is looked up when tile i is issued, so the dependent read of the
+    // block table is never waited for
+    auto key0_of = [&](int i) { return first + (my_first_tile + i * DEC_WARPS) * DEC_TILE; };
+    int page_ahead = my_tiles > 0 ? lookup_tile_page(table, p.page_size, key0_of(0), key_end, lane) : -1;
+    bool waited = false;
+    auto issue = [&](int i) {
+        if (i < my_tiles) {
+            if (!waited && key0_of(i) + DEC_TILE > pos) {        // the tile with the newest key
+                pdl_wait();
+                waited = true;
+            }
+            const int page = page_ahead;
+            if (i + 1 < my_tiles)
+                page_ahead = lookup_tile_page(table, p.page_size, key0_of(i + 1), key_end, lane);
+            __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
+            load_kv_tile16_paged(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, page, kv_head, p.nkv,
+                                 p.page_size, p.num_pages, key0_of(i), key_end, lane, p.error);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i)
+        issue(i);
+    if (!waited) {
+        pdl_wait();
+        waited = true;
+    }
+
     // query rows -> shared memory (rows past the group are zero)
     for (int c = threadIdx.x; c < 16 * CHUNKS; c += blockDim.x) {
         const int row = c / CHUNKS, col = c - row * CHUNKS;
@@ -325,28 +360,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     float m[2] = { -INFINITY, -INFINITY }, l[2] = { 0.f, 0.f };
 
-    __nv_bfloat16* my_pipe = pipe + (size_t)warp * DEC_STAGES * DEC_STAGE_ELEMS;
-    const int my_first_tile = tile_begin + warp;
-    const int my_tiles = my_first_tile < tile_end ? (tile_end - my_first_tile + DEC_WARPS - 1) / DEC_WARPS : 0;
-
-    // the page of tile i + 1 is looked up when tile i is issued, so the dependent read of the
-    // block table is never waited for
-    auto key0_of = [&](int i) { return first + (my_first_tile + i * DEC_WARPS) * DEC_TILE; };
-    int page_ahead = my_tiles > 0 ? lookup_tile_page(table, p.page_size, key0_of(0), key_end, lane) : -1;
-    auto issue = [&](int i) {
-        if (i < my_tiles) {
-            const int page = page_ahead;
-            if (i + 1 < my_tiles)
-                page_ahead = lookup_tile_page(table, p.page_size, key0_of(i + 1), key_end, lane);
-            __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
-            load_kv_tile16_paged(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, page, kv_head, p.nkv,
-                                 p.page_size, p.num_pages, key0_of(i), key_end, lane, p.error);
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; ++i)
-        issue(i);
     for (int i = 0; i < my_tiles; ++i) {
         issue(i + DEC_STAGES - 1);
         cp_async_wait<DEC_STAGES - 1>();
@@ -416,21 +429,39 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
 // Merges the key ranges of one (sequence, head): one block of D threads.
 __global__ void attn_decode_merge_kernel(const AttnParams p)
 {
-    pdl_enter();
+    pdl_trigger();
     const int seq = blockIdx.y, head = blockIdx.x, c = threadIdx.x;
-    const int t = p.q_start[seq];
+    const int t = p.q_start[seq];                     // written before the step's first kernel
     if (p.q_start[seq + 1] - t != 1)
         return;
+    pdl_wait();
     const size_t slot0 = ((size_t)seq * p.nq + head) * p.splits;
-    float mmax = -INFINITY;
-    for (int s = 0; s < p.splits; ++s)
-        mmax = fmaxf(mmax, p.scratch_ml[(slot0 + s) * 2]);
-    const float base = mmax == -INFINITY ? 0.f : mmax;
-    float acc = 0.f, lsum = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-        const float f = exp2f(p.scratch_ml[(slot0 + s) * 2] - base);
-        acc += p.scratch_o[(slot0 + s) * D + c] * f;
-        lsum += p.scratch_ml[(slot0 + s) * 2 + 1] * f;
+    // eight key ranges at a time, all their loads in flight together
+    float m_run = -INFINITY, acc = 0.f, lsum = 0.f;
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+        float mv[8], lv[8], ov[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool in = s0 + u < p.splits;
+            mv[u] = in ? p.scratch_ml[(slot0 + s0 + u) * 2] : -INFINITY;
+            lv[u] = in ? p.scratch_ml[(slot0 + s0 + u) * 2 + 1] : 0.f;
+            ov[u] = in ? p.scratch_o[(slot0 + s0 + u) * D + c] : 0.f;
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            m_new = fmaxf(m_new, mv[u]);
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = exp2f(m_run - base);       // 0 while nothing has been seen
+        acc *= keep;
+        lsum *= keep;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float f = exp2f(mv[u] - base);
+            acc += ov[u] * f;
+            lsum += lv[u] * f;
+        }
+        m_run = m_new;
     }
     p.out[((size_t)t * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
 }

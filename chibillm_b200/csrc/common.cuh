@@ -101,6 +101,17 @@ __device__ __forceinline__ void pdl_enter()
     pdl_wait();
 }
 
+// Asks for the line at p in L2, and with it for the translation of its page.  A
+// kernel that was launched early does this for the addresses it will touch
+// before pdl_wait(): after a product has streamed hundreds of megabytes of
+// weights, the first access to a page otherwise waits for a page-table walk.
+// (L2 is where the GPU's memory is coherent, so a line fetched before its
+// producer wrote it is not stale.)
+__device__ __forceinline__ void prefetch_l2(const void* p)
+{
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // CHIBI_PDL=0 in the environment launches every kernel the ordinary way.
 inline bool pdl_enabled()
 {
@@ -112,9 +123,15 @@ inline bool pdl_enabled()
 }
 
 // Launches with a thread-block cluster of (1, 1, cluster_z) CTAs when cluster_z > 1.
+// `ordered`: an ordinary launch, which starts only after everything before it in
+// the stream has completed.
 template <typename... KArgs, typename... Args>
 inline void launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                           cudaStream_t stream, int cluster_z, Args&&... args)
+                           cudaStream_t stream, int cluster_z, Args&&... args);
+
+template <bool ORDERED, typename... KArgs, typename... Args>
+inline void launch_with(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                        cudaStream_t stream, int cluster_z, Args&&... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -123,7 +140,7 @@ inline void launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (pdl_enabled()) {
+    if (!ORDERED && pdl_enabled()) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
@@ -138,6 +155,25 @@ inline void launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     cfg.attrs = attr;
     cfg.numAttrs = n;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                           cudaStream_t stream, int cluster_z, Args&&... args)
+{
+    launch_with<false>(kernel, grid, block, smem, stream, cluster_z, static_cast<Args&&>(args)...);
+}
+
+// The step's first kernel (the embedding) is launched this way.  Every kernel
+// after it, however early programmatic dependent launch lets it start, therefore
+// runs after all that was written before the embedding: the step's index arrays
+// (positions, sequence of each token, lengths, block tables) and the cache
+// entries of earlier steps.  Kernels may read those before their pdl_wait().
+template <typename... KArgs, typename... Args>
+inline void launch_ordered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args&&... args)
+{
+    launch_with<true>(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 // Launches with a thread-block cluster of (cluster_x, 1, 1) CTAs.

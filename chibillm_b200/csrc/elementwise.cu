@@ -250,7 +250,7 @@ __global__ void qk_norm_rope_append_vec4_kernel(
     const int* __restrict__ block_table, int table_stride, int nq, int nkv, int d, int rot,
     int page_size, int num_pages, float eps, float norm_offset, int append, int* __restrict__ error)
 {
-    pdl_enter();
+    pdl_trigger();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -258,6 +258,9 @@ __global__ void qk_norm_rope_append_vec4_kernel(
     const int half = rot >> 1;
     float* cs = smem;
     float* buf = smem + 2 * half + (size_t)warp * JPW * d;
+    // The step's index arrays and the block table were written before the step's first
+    // kernel: the token's cache slot and its cosines and sines are worked out while the
+    // kernel before this one still runs.
     const int pos = positions[t];
     const int jobs = append ? nq + 2 * nkv : nq;
     const int job0 = (blockIdx.y * warps + warp) * JPW;
@@ -273,7 +276,14 @@ __global__ void qk_norm_rope_append_vec4_kernel(
             cache_base = ((long long)page * nkv * page_size + (pos % page_size)) * d;
         }
     }
-    // every load goes out first; the token's cosines and sines are computed while they travel
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float a = (float)pos * inv_freq[j];
+        float sn, c;
+        sincosf(a, &sn, &c);
+        cs[j] = c;
+        cs[half + j] = sn;
+    }
+    pdl_wait();
     float s[JPW];
 #pragma unroll
     for (int jj = 0; jj < JPW; ++jj) {
@@ -313,13 +323,6 @@ __global__ void qk_norm_rope_append_vec4_kernel(
                 s[jj] = fmaf(v[3], v[3], s[jj]);
             }
         }
-    }
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        const float a = (float)pos * inv_freq[j];
-        float sn, c;
-        sincosf(a, &sn, &c);
-        cs[j] = c;
-        cs[half + j] = sn;
     }
     __syncthreads();
 #pragma unroll
@@ -367,9 +370,9 @@ __global__ void qk_norm_rope_append_vec4_kernel(
 // Many tokens, heads of 128 features rotated whole: one block of eight warps per
 // token; the heads stay in registers.  A lane holds features 4*lane .. 4*lane+3 of a head, so
 // the partner of a feature in the rotation (64 features away) sits 16 lanes away
-// and comes by one shuffle.  Warp w takes heads w, w+8, ...; their loads all go
-// out before the token's cosines and sines are computed (once per block, in
-// shared memory).
+// and comes by one shuffle.  Warp w takes heads w, w+8, ...  The token's cache
+// slot, the norm weights and its cosines and sines (once per block, in shared
+// memory) are ready before the kernel waits for the q | k | v product.
 constexpr int ROWS_KERNEL_WARPS = 8;
 constexpr int ROWS_KERNEL_MAX_JOBS = 8;       // heads per warp: nq + 2 * nkv <= 64
 
@@ -382,7 +385,7 @@ __global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d1
     const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
     int num_pages, float eps, float norm_offset, int append, int* __restrict__ error)
 {
-    pdl_enter();
+    pdl_trigger();
     constexpr int D = 128;
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -400,16 +403,6 @@ __global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d1
             cache_base = ((long long)page * nkv * page_size + (pos % page_size)) * D;
         }
     }
-    const TX* src = qkv + (size_t)t * qkv_stride + lane * 4;
-    float v[ROWS_KERNEL_MAX_JOBS][4];
-#pragma unroll
-    for (int jj = 0; jj < ROWS_KERNEL_MAX_JOBS; ++jj) {
-        const int job = warp + jj * ROWS_KERNEL_WARPS;
-        if (job < jobs && (job < nq || cache_base >= 0))
-            Vec4<TX>::load(src + (size_t)job * D, v[jj]);
-        else
-            v[jj][0] = v[jj][1] = v[jj][2] = v[jj][3] = 0.f;
-    }
     float wq[4], wk[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -423,6 +416,18 @@ __global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d1
         sincosf((float)pos * inv_freq[threadIdx.x], &sn, &cn);
         cs[threadIdx.x] = cn;
         cs[D / 2 + threadIdx.x] = sn;
+    }
+    // all of the above reads what was there before the step's first kernel
+    pdl_wait();
+    const TX* src = qkv + (size_t)t * qkv_stride + lane * 4;
+    float v[ROWS_KERNEL_MAX_JOBS][4];
+#pragma unroll
+    for (int jj = 0; jj < ROWS_KERNEL_MAX_JOBS; ++jj) {
+        const int job = warp + jj * ROWS_KERNEL_WARPS;
+        if (job < jobs && (job < nq || cache_base >= 0))
+            Vec4<TX>::load(src + (size_t)job * D, v[jj]);
+        else
+            v[jj][0] = v[jj][1] = v[jj][2] = v[jj][3] = 0.f;
     }
     __syncthreads();
     float c[4], s[4];
@@ -588,7 +593,7 @@ CHIBI_API int chibi_embed(const int* tokens, const void* table, int table_type, 
         return CHIBI_OK;
     const int block = hidden >= 1024 ? 256 : 128;
     CHIBI_DISPATCH_TYPE(table_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        launch(embed_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream, 
+        launch_ordered(embed_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream, 
             tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
     }));
     return launch_status();

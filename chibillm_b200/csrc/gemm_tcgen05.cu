@@ -1048,8 +1048,9 @@ reduce_residual_rmsnorm_kernel(const float* __restrict__ partial, int splits, in
 }
 
 // The same with a cluster of CTAs per row, each taking a run of columns (one
-// float4 per thread, the splits' loads issued eight at a time); the CTAs exchange
-// their sums of squares through distributed shared memory.
+// float4 per thread, all of a thread's loads in flight together); the CTAs push
+// their sums of squares into one another's shared memory and meet at one
+// cluster barrier.
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(1024)
 reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int splits, int M, int N,
@@ -1057,30 +1058,50 @@ reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int sp
                                        TO* __restrict__ normed, long long normed_stride, float eps,
                                        float offset)
 {
-    pdl_enter();
+    pdl_trigger();
     __shared__ float scratch[33];
-    __shared__ float my_sum;
+    __shared__ float sums[8];                        // sums[r]: the sum of squares of CTA r's columns
     const int m = blockIdx.y;
-    const int parts = gridDim.x;                     // CTAs per row = cluster size
+    const int parts = gridDim.x;                     // CTAs per row = cluster size (<= 8)
     const int n4 = N >> 2;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;   // float4 index within the row
     const size_t total4 = ((size_t)M * N) >> 2;
+    if (j < n4) {
+        // while the product before this kernel still runs
+        const float4* part = reinterpret_cast<const float4*>(partial) + (size_t)m * n4 + j;
+        prefetch_l2(part);
+        prefetch_l2(part + (size_t)(splits - 1) * total4);
+        prefetch_l2(residual + (size_t)m * res_stride + 4 * j);
+        if (w) {
+            prefetch_l2(w + 4 * j);
+            prefetch_l2(normed + (size_t)m * normed_stride + 4 * j);
+        }
+    }
+    pdl_wait();
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wv[4] = { 0.f, 0.f, 0.f, 0.f };
     float s = 0.f;
     if (j < n4) {
+        // everything this thread reads is on its way at once: its column of up to 16 splits, the
+        // residual and the norm weights
         const float4* part = reinterpret_cast<const float4*>(partial) + (size_t)m * n4 + j;
-        for (int sp0 = 0; sp0 < splits; sp0 += 8) {
-            float4 q[8];
+        float4* res = reinterpret_cast<float4*>(residual + (size_t)m * res_stride) + j;
+        const float4 r = *res;
+        if (w) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            for (int u = 0; u < 4; ++u)
+                wv[u] = to_f32(w[4 * j + u]) + offset;
+        }
+        for (int sp0 = 0; sp0 < splits; sp0 += 16) {
+            float4 q[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
                 q[u] = sp0 + u < splits ? part[(size_t)(sp0 + u) * total4] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 acc.x += q[u].x; acc.y += q[u].y; acc.z += q[u].z; acc.w += q[u].w;
             }
         }
-        float4* res = reinterpret_cast<float4*>(residual + (size_t)m * res_stride) + j;
-        const float4 r = *res;
         acc.x = r.x + acc.x; acc.y = r.y + acc.y; acc.z = r.z + acc.z; acc.w = r.w + acc.w;
         *res = acc;
         s = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
@@ -1088,20 +1109,21 @@ reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int sp
     if (!w)
         return;
     s = block_sum(s, scratch);
-    if (threadIdx.x == 0)
-        my_sum = s;
+    // every CTA puts its sum into slot `rank` of every CTA of the cluster; after one cluster
+    // barrier each CTA adds the slots of its own copy, in rank order
+    if ((int)threadIdx.x < parts)
+        st_peer_shared_f32(smem_addr(&sums[cluster_cta_rank()]), threadIdx.x, s);
     cluster_sync();
     float total = 0.f;
     for (int r = 0; r < parts; ++r)
-        total += ld_peer_shared_f32(smem_addr(&my_sum), r);
-    cluster_sync();                                  // nobody leaves while its sum may still be read
+        total += sums[r];
     const float inv = rsqrtf(total / (float)N + eps);
     if (j < n4) {
         TO* dst = normed + (size_t)m * normed_stride + 4 * j;
-        dst[0] = from_f32<TO>((acc.x * inv) * (to_f32(w[4 * j]) + offset));
-        dst[1] = from_f32<TO>((acc.y * inv) * (to_f32(w[4 * j + 1]) + offset));
-        dst[2] = from_f32<TO>((acc.z * inv) * (to_f32(w[4 * j + 2]) + offset));
-        dst[3] = from_f32<TO>((acc.w * inv) * (to_f32(w[4 * j + 3]) + offset));
+        dst[0] = from_f32<TO>((acc.x * inv) * wv[0]);
+        dst[1] = from_f32<TO>((acc.y * inv) * wv[1]);
+        dst[2] = from_f32<TO>((acc.z * inv) * wv[2]);
+        dst[3] = from_f32<TO>((acc.w * inv) * wv[3]);
     }
 }
 
@@ -1166,9 +1188,10 @@ CHIBI_API int chibi_reduce_residual_rmsnorm(const float* partial, int splits, in
         const dim3 grid(parts, M);
         const int threads = N / 4 / parts;
         if (!w) {
-            launch_cluster_x(reduce_residual_rmsnorm_cluster_kernel<float, float>, grid, dim3(threads), 0, stream,
-                             parts, partial, splits, M, N, residual, res_stride, (const float*)nullptr,
-                             (float*)nullptr, (long long)0, eps, offset);
+            // no norm, nothing to exchange: the same grid without the cluster
+            launch(reduce_residual_rmsnorm_cluster_kernel<float, float>, grid, dim3(threads), 0, stream,
+                   partial, splits, M, N, residual, res_stride, (const float*)nullptr, (float*)nullptr,
+                   (long long)0, eps, offset);
             return launch_status();
         }
         CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(normed_type, TO, {

@@ -117,6 +117,14 @@ __device__ __forceinline__ float ld_peer_shared_f32(uint32_t own_smem_addr, uint
     return v;
 }
 
+// Writes a 32-bit value to the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void st_peer_shared_f32(uint32_t own_smem_addr, uint32_t rank, float v)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_smem_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 // ------------------------------------------------------------------ TMA
 // 2-d tile load: coordinates are (x = innermost element index, y = row).
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
