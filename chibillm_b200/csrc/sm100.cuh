@@ -193,6 +193,20 @@ __device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_des
                  : "memory");
 }
 
+// The same with the A operand in TMEM (lane = row; a 32-bit column holds two
+// consecutive bf16 of the row, the lower index in the low half).
+__device__ __forceinline__ void tcgen05_mma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                        uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+                 "}\n" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit: thread i of the warp gets columns
 // [col, col + 32) of lane (lane_base + i).
 __device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&r)[32])
@@ -232,6 +246,16 @@ __device__ __forceinline__ void tmem_store_32x32(uint32_t taddr, const uint32_t 
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
         "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
         "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_32x16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 

@@ -86,6 +86,7 @@ class CudaKernels:
         self.launches = 0           # kernels of this package launched so far
         self.use_tensor_cores = True
         self.tensor_core_calls = 0  # matrix products that ran on the tcgen05 kernel
+        self.tcgen05_attention_variant = 0   # 0: chosen by size; 1 / 2: query tiles per CTA (for tests)
         self._scratch_buf: Optional[torch.Tensor] = None
         self.scratch_generation = 0
         self.supports_graphs = True     # every op is a plain launch on the current stream
@@ -468,8 +469,8 @@ class CudaKernels:
             status = tc.chibi_attention_prefill_tc(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
-                float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len), _ptr(self.error),
-                self._stream())
+                float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len),
+                int(self.tcgen05_attention_variant), _ptr(self.error), self._stream())
             if status == 0:
                 self.launches += 1
                 mode &= 1

@@ -457,12 +457,14 @@ def test_attention_tcgen05_prompts(k, ref, nq, nkv, d, window, page):
     exp = torch.empty(T, nq * d, dtype=torch.bfloat16, device="cuda")
     ref.attention(q, kc, vc, exp, *args)
     outs = {}
-    for tc in (True, False):
+    for tc, variant in ((True, 1), (True, 2), (False, 0)):      # one and two query tiles per CTA; mma.sync
         k.use_tcgen05_attention = tc
+        k.tcgen05_attention_variant = variant
         out = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
         before = k.launches
         k.attention(q, kc, vc, out, *args)
         k.check_error_word()
-        close(out, exp, torch.bfloat16, f"prompt attention (tcgen05={tc})", rel=1.2e-2)
-        outs[tc] = out
+        close(out, exp, torch.bfloat16, f"prompt attention (tcgen05={tc}, variant {variant})", rel=1.2e-2)
+        outs[(tc, variant)] = out
     k.use_tcgen05_attention = True
+    k.tcgen05_attention_variant = 0
