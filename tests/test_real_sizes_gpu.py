@@ -1,4 +1,4 @@
-"""Layer sizes of real checkpoints (Qwen3-0.6B and a slice of Qwen3-8B: head size
+"""Layer sizes of real checkpoints (Qwen3-0.6B and slices of Qwen3-8B and Qwen3-14B: head size
 128, vocabulary 151,936, tied or untied output) with random weights and two
 layers: the bfloat16 engine against the 32-bit engine, whole prompts against
 portions and decoded tokens, and a long context whose decode steps are replayed
@@ -27,6 +27,9 @@ SHAPES = {
                  tie_word_embeddings=True),
     "8B": base(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, intermediate_size=12288,
                tie_word_embeddings=False),
+    # five query heads per kv head, widths that are no multiple of 1,024
+    "14B": base(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=17408,
+                tie_word_embeddings=False),
 }
 
 
