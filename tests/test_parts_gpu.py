@@ -339,3 +339,157 @@ def test_toy_architecture_with_a_state_of_its_own(tmp_path):
         assert runner.graph_replays == 0        # a part that gives no launch key is never captured
     finally:
         unregister_architecture("ToyHybridForCausalLM")
+
+
+# ------------------------------------------------------------------ a second toy: routing and another position encoding
+@dataclass(frozen=True)
+class ToyRoutedSpec:
+    kind: str
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    experts: int = 0
+
+
+def _register_routed_toy():
+    """A feed-forward that sends every token to one of its experts (router logits
+    and softmax in 32-bit, the chosen expert's output weighted by its
+    probability), and a position encoding that the kernels do not know: it
+    rotates neighbouring pairs (2i, 2i + 1) instead of split halves, so the
+    attention part has to call ``apply`` before the keys are cached."""
+    from chibillm_b200.config import (AttentionSpec, LayerSpec, ModelSpec, NormSpec, PositionSpec, RunStep,
+                                      register_architecture)
+    from chibillm_b200.parts import (FeedForward, PositionEncoding, TensorSpec, register_feed_forward,
+                                     register_position)
+
+    class PairRotation(PositionEncoding):
+        def __init__(self, spec, rt):
+            self.spec = spec
+            j = torch.arange(spec.rotary_dim // 2, dtype=torch.float32)
+            self.inv_freq = torch.pow(torch.tensor(float(spec.theta)), -2.0 * j / spec.rotary_dim).to(rt.device)
+
+        def fused_rotation(self):
+            return None
+
+        def apply(self, q, k, ctx):
+            angle = ctx.positions.float()[:, None] * self.inv_freq[None, :]        # [T, d/2]
+            c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            for t in (q, k):
+                if t is None:
+                    continue
+                T = t.shape[0]
+                x = t.float().reshape(T, -1, self.spec.head_dim // 2, 2)
+                x0, x1 = x[..., 0], x[..., 1]
+                y = torch.stack([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1)
+                t.copy_(y.reshape(T, -1).to(t.dtype))
+
+    class RoutedFeedForward(FeedForward):
+        def __init__(self, spec, names, rt):
+            self.spec, self.names, self.rt = spec, names, rt
+
+        def expected_tensors(self):
+            s = self.spec
+            out = [TensorSpec(self.names["router"], (s.experts, s.hidden_size))]
+            for e in range(s.experts):
+                out += [TensorSpec(self.names[f"up_{e}"], (s.intermediate_size, s.hidden_size)),
+                        TensorSpec(self.names[f"down_{e}"], (s.hidden_size, s.intermediate_size))]
+            return out
+
+        def bind(self, tensors):
+            self.router = tensors[self.names["router"]].float()
+            self.up = [tensors[self.names[f"up_{e}"]].float() for e in range(self.spec.experts)]
+            self.down = [tensors[self.names[f"down_{e}"]].float() for e in range(self.spec.experts)]
+
+        def forward(self, x, residual, ctx):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.t(), dim=-1)
+            chosen = prob.argmax(dim=-1)
+            for e in range(self.spec.experts):
+                rows = (chosen == e).nonzero().flatten()
+                if rows.numel():
+                    h = xf[rows] @ self.up[e].t()
+                    h = h / (1 + torch.exp(-h))
+                    residual[rows] += prob[rows, e, None] * (h @ self.down[e].t())
+
+    register_position("toy_pairs", PairRotation, replace=True)
+    register_feed_forward("toy_routed", RoutedFeedForward, replace=True)
+
+    def model_spec(obj):
+        H, E = obj["hidden_size"], obj["experts"]
+        norm = NormSpec("rmsnorm", H, obj["eps"], 0.0)
+        ff = ToyRoutedSpec("toy_routed", H, obj["intermediate_size"], E)
+        attn = AttentionSpec(kind="attention", hidden_size=H, num_heads=6, num_kv_heads=3, head_dim=16,
+                             scale=0.25, window=None, qk_norm=NormSpec("rmsnorm", 16, obj["eps"], 0.0),
+                             position=PositionSpec("toy_pairs", head_dim=16, rotary_dim=16, theta=obj["theta"]))
+        names = [("mixer_norm", "n1.weight"), ("feed_forward_norm", "n2.weight"), ("q_proj", "q.weight"),
+                 ("k_proj", "k.weight"), ("v_proj", "v.weight"), ("o_proj", "o.weight"), ("q_norm", "qn.weight"),
+                 ("k_norm", "kn.weight"), ("router", "router.weight")]
+        for e in range(E):
+            names += [(f"up_{e}", f"experts.{e}.up.weight"), (f"down_{e}", f"experts.{e}.down.weight")]
+        layers = tuple(LayerSpec("prenorm", attn, ff, norm, norm, f"layers.{i}.", tuple(names)) for i in range(2))
+        return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=obj["vocab_size"], hidden_size=H,
+                         max_positions=obj["max_positions"], layers=layers, run_order=(RunStep(0), RunStep(1)),
+                         final_norm=norm, embedding_name="embed.weight", final_norm_name="norm.weight",
+                         output_name="head.weight", tie_output_to_embedding=False)
+
+    register_architecture("ToyRoutedForCausalLM", lambda obj: obj, model_spec, replace=True)
+
+
+def _routed_toy_plain(obj, w, ids):
+    """Whole sequence, no cache, token by token where that is simplest."""
+    T, H, E, d = len(ids), obj["hidden_size"], obj["experts"], 16
+    eps, theta = obj["eps"], obj["theta"]
+    h = plain_qwen3.embedding(w["embed.weight"], ids)
+
+    def pairs(x, pos):                     # x: [heads, d]
+        out = x.clone()
+        for i in range(d // 2):
+            a = torch.tensor(float(pos), dtype=torch.float32) * torch.pow(torch.tensor(float(theta)),
+                                                                        torch.tensor(-2.0 * i / d))
+            c, s = torch.cos(a), torch.sin(a)
+            out[:, 2 * i] = x[:, 2 * i] * c - x[:, 2 * i + 1] * s
+            out[:, 2 * i + 1] = x[:, 2 * i + 1] * c + x[:, 2 * i] * s
+        return out
+
+    for layer in range(2):
+        p = f"layers.{layer}."
+        x = plain_qwen3.rms_norm(h, w[p + "n1.weight"], eps)
+        q = plain_qwen3.rms_norm((x @ w[p + "q.weight"].t()).view(T, 6, d), w[p + "qn.weight"], eps)
+        k = plain_qwen3.rms_norm((x @ w[p + "k.weight"].t()).view(T, 3, d), w[p + "kn.weight"], eps)
+        v = (x @ w[p + "v.weight"].t()).view(T, 3, d)
+        q = torch.stack([pairs(q[t], t) for t in range(T)])
+        k = torch.stack([pairs(k[t], t) for t in range(T)])
+        h = h + plain_qwen3.causal_attention(q, k, v, None).reshape(T, 6 * d) @ w[p + "o.weight"].t()
+        x = plain_qwen3.rms_norm(h, w[p + "n2.weight"], eps)
+        out = torch.zeros_like(h)
+        for t in range(T):
+            prob = torch.softmax(w[p + "router.weight"] @ x[t], dim=0)
+            e = int(prob.argmax())
+            u = w[p + f"experts.{e}.up.weight"] @ x[t]
+            out[t] = prob[e] * (w[p + f"experts.{e}.down.weight"] @ (u / (1 + torch.exp(-u))))
+        h = h + out
+    return plain_qwen3.rms_norm(h, w["norm.weight"], eps) @ w["head.weight"].t()
+
+
+def test_toy_architecture_with_routing_and_its_own_position_encoding(tmp_path):
+    from chibillm_b200.config import unregister_architecture
+    from chibillm_b200.engine.runner import ModelRunner
+    from chibillm_b200.weights import write_random_model
+    _register_routed_toy()
+    try:
+        obj = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "intermediate_size": 40, "experts": 3,
+               "vocab_size": 97, "eps": 1e-5, "theta": 5000.0, "max_positions": 96}
+        folder = write_random_model(obj, str(tmp_path / "routed"), seed=4, dtype=torch.float32)
+        runner = ModelRunner.from_folder(folder, dtype="float32", device=DEV, page_size=4, pool_tokens=192,
+                                         max_requests=3)
+        _, w = plain_qwen3.read_model_folder(folder)
+        # wide router weights, so that the experts really take turns
+        reqs = helpers.random_requests(97, [21, 9, 40, 14], seed=11)
+        ref = {rid: _routed_toy_plain(obj, w, ids) for rid, ids in reqs.items()}
+        for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, 1), "portions"),
+                            (helpers.trace_mixed(reqs, 128, seed=5, max_live=3, decode_tail=5), "mixed")):
+            got = helpers.run_trace(runner, trace)
+            helpers.assert_logits_close(got, ref, 2e-5, f"routed toy {what}")
+            runner.cache.check_invariants()
+        assert runner.graph_replays == 0
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
