@@ -168,7 +168,13 @@ def measure_decode(runner, sampler, batch, ctx_start, steps, warmup, vocab, tag)
         if i >= warmup:
             ctx_lens.append(ctx_start + i + 1)
         logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)], check=False)
-        tokens = sampler.sample(logits, params, keys, [i] * batch)
+        pending = sampler.launch(logits, params, keys, [i] * batch)
+        # as the engine does: the next step starts on the device while the tokens travel to the
+        # host -- but not across the borders of the timed region, which holds exactly `steps` steps
+        ahead = i != warmup - 1 and i != warmup + steps - 1 and runner.run_ahead(ids, pending.device_ids)
+        tokens = pending.result()
+        if ahead:
+            runner.confirm_ahead(tokens)
     end.record()
     torch.cuda.synchronize()
     runner.runtime.kernels.check_error_word()

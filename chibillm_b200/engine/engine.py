@@ -66,6 +66,7 @@ class InferenceEngine:
         self.scheduler = Scheduler(self.config, runner.cache, runner.spec.eos_token_id,
                                    on_admit=runner.admit, on_release=runner.end)
         self.sampler = Sampler(runner.runtime)
+        self.run_ahead = True          # launch the next decode step before this one's tokens are on the host
         self.pending: Deque[Sequence] = deque()
         self.metrics: Dict[Hashable, RequestMetrics] = {}
         self._keys: Dict[Hashable, int] = {}
@@ -130,13 +131,28 @@ class InferenceEngine:
                 seq = sched.sequences[item.seq_id]
                 toks = seq.tokens[item.first:item.first + item.count]
                 entries.append(StepEntry(item.seq_id, toks, [item.count - 1] if item.sample else []))
-            logits = self.runner.step(entries)
+            kernels = self.runner.runtime.kernels
+            deferred_check = hasattr(kernels, "error_word_async")
+            logits = self.runner.step(entries, check=not deferred_check)
+            if deferred_check:
+                kernels.error_word_async()        # read together with the tokens, below
             sampled: List[int] = []
             if batch.sample_count:
                 rows = [sched.sequences[i.seq_id] for i in batch.items if i.sample]
-                sampled = self.sampler.sample(
+                pending = self.sampler.launch(
                     logits, [s.params for s in rows], [self._keys[s.id] for s in rows],
                     [s.completion_len for s in rows])
+                # While the tokens travel to the host, the device already runs the step that
+                # follows if all of these requests go on (the usual case in steady decoding).
+                ahead = self.run_ahead and self._next_step_is_the_same(batch, rows) \
+                    and self.runner.run_ahead([s.id for s in rows], pending.device_ids)
+                sampled = pending.result()
+                if ahead:
+                    self.runner.confirm_ahead(sampled)
+            elif deferred_check:
+                torch.cuda.current_stream().synchronize()
+            if deferred_check:
+                kernels.check_error_copy()
             if len(sampled) != batch.sample_count:
                 raise SchedulerError("result_count_mismatch")
         except Exception:
@@ -155,6 +171,18 @@ class InferenceEngine:
             m.finish_reason = u.finish_reason
         self._admit_pending()
         return updates
+
+    def _next_step_is_the_same(self, batch, rows) -> bool:
+        """Whether the next step can be foretold: every item of this one is a single
+        decoded token, nobody waits to be admitted or to be prefilled, and no request
+        reaches its token limit with the token being chosen (an end-of-sequence
+        token cannot be foretold: then the step that ran ahead is dropped)."""
+        if self.pending or self.scheduler.waiting or len(rows) != len(batch.items):
+            return False
+        for item, seq in zip(batch.items, rows):
+            if item.count != 1 or seq.completion_len + 1 >= seq.params.max_new_tokens:
+                return False
+        return True
 
     def generate(self, prompts: Seq[Seq[int]], params=None) -> List[List[int]]:
         """Run the prompts to completion; returns the generated ids of each."""

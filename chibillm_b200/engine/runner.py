@@ -17,7 +17,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import torch
 
 from ..cache.manager import CacheError, CacheManager
-from ..cache.storage import CacheStorage, plan_cache
+from ..cache.storage import CacheStorage, FixedStateView, plan_cache
 from ..config.registry import load_config
 from ..parts.base import Runtime
 from ..weights.loader import load_weights
@@ -77,6 +77,11 @@ class ModelRunner:
         self._graphs_warm = set()
         self._graphs_epoch = None
         self.graph_replays = 0
+        # a decode step launched ahead of the tokens that decide whether it is wanted
+        self._ahead: Optional[dict] = None
+        self.steps_ahead_used = 0
+        self.steps_ahead_dropped = 0
+        self._has_state = any(isinstance(v, FixedStateView) for v in self.storage.views)
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -256,6 +261,65 @@ class ModelRunner:
         self.graph_replays += 1
         return logits
 
+    # ------------------------------------------------------------ running ahead
+    def run_ahead(self, request_ids: Sequence[Hashable], device_tokens: torch.Tensor) -> bool:
+        """Launch now the decode step that follows if every one of these requests
+        goes on with the token just chosen for it (``device_tokens[i]``, still on the
+        device), so that the device does not wait while the host reads the tokens
+        and decides.  The next ``step`` returns its logits if it asks for exactly
+        this (same requests in this order, one token each, the tokens given to
+        ``confirm_ahead``, logits of each); any other ``step`` drops it.  Only a
+        step that is replayed from a captured graph runs ahead, and only a model
+        whose requests hold nothing but paged keys and values (a fixed-size state
+        would be advanced by a step that may not be wanted).  Returns whether the
+        step was launched."""
+        if self._ahead is not None or not self.use_graphs or self._has_state:
+            return False
+        S = len(request_ids)
+        if S == 0 or S > self.cache.max_requests or device_tokens.numel() != S \
+                or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda:
+            return False
+        for rid in request_ids:
+            if not self.cache.has(rid) or self.cache.length(rid) + 1 > self.spec.max_positions:
+                return False
+        try:
+            for rid in request_ids:
+                self.cache.reserve(rid, self.cache.length(rid) + 1)
+        except Exception:
+            return False                      # no page left: the ordinary step will say so
+        entries = [StepEntry(rid, [0], [0]) for rid in request_ids]      # the tokens come from the device
+        ctx, update_views, fixed = self._build_context(entries, True)
+        key = self._graph_key(ctx) if fixed else None
+        entry = self._graphs.get(key) if key is not None and self._graph_epoch() == self._graphs_epoch else None
+        if entry is None:
+            # the table updates of this step have been taken from the manager: apply them now
+            k = self.runtime.kernels
+            for name, (view, cap) in update_views.items():
+                if cap > 0:
+                    k.apply_table_updates(self.storage.tables[name], view, cap)
+            return False
+        ctx.tokens.copy_(device_tokens)
+        graph, logits, launches = entry
+        graph.replay()
+        self.runtime.kernels.launches += launches
+        self.graph_replays += 1
+        self._ahead = {"ids": tuple(request_ids), "logits": logits, "ctx_lens": list(ctx.ctx_lens), "tokens": None}
+        return True
+
+    def confirm_ahead(self, tokens: Sequence[int]) -> None:
+        """The tokens that the step launched by ``run_ahead`` used, now that the host has them."""
+        if self._ahead is not None:
+            self._ahead["tokens"] = [int(t) for t in tokens]
+
+    @staticmethod
+    def _matches_ahead(ahead: dict, entries: Sequence[StepEntry]) -> bool:
+        if ahead["tokens"] is None or len(entries) != len(ahead["ids"]):
+            return False
+        for e, rid, tok in zip(entries, ahead["ids"], ahead["tokens"]):
+            if e.request_id != rid or len(e.tokens) != 1 or int(e.tokens[0]) != tok or list(e.want) != [0]:
+                return False
+        return True
+
     # ------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device in
@@ -268,6 +332,20 @@ class ModelRunner:
         wanted rows) travels in the packed metadata array."""
         if not entries:
             raise BatchError("a step needs at least one entry")
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            if self._matches_ahead(ahead, entries):
+                for e, new_len in zip(entries, ahead["ctx_lens"]):
+                    self.cache.commit(e.request_id, new_len)
+                self.steps_run += 1
+                self.steps_ahead_used += 1
+                if check and hasattr(self.runtime.kernels, "check_error_word"):
+                    self.runtime.kernels.check_error_word()
+                return ahead["logits"]
+            # Not wanted after all.  Nothing is undone: the step wrote keys and values one place
+            # past what its requests hold (a place that the step which does reach it writes
+            # again), and the pages it reserved stay reserved to their requests.
+            self.steps_ahead_dropped += 1
         if len(entries) > self.cache.max_requests:
             raise BatchError(f"{len(entries)} entries in one step; at most {self.cache.max_requests} "
                              f"requests are live at a time")

@@ -83,6 +83,7 @@ class CudaKernels:
             raise KernelError(f"device '{device}' is not a CUDA device; chibillm_b200 has no CPU path")
         self.lib = library.load("chibi_kernels")
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._error_host: Optional[torch.Tensor] = None
         self.launches = 0           # kernels of this package launched so far
         self.use_tensor_cores = True
         self.tensor_core_calls = 0  # matrix products that ran on the tcgen05 kernel
@@ -116,9 +117,22 @@ class CudaKernels:
     def _stream() -> int:
         return torch.cuda.current_stream().cuda_stream
 
+    def error_word_async(self) -> None:
+        """Starts the copy of the error word to the host; ``check_error_copy`` reads it
+        once the caller has waited for an event recorded after this call."""
+        if self._error_host is None:
+            self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._error_host.copy_(self.error, non_blocking=True)
+
+    def check_error_copy(self) -> None:
+        if self._error_host is not None:
+            self._raise_for(int(self._error_host[0]))
+
     def check_error_word(self) -> None:
         """Synchronises and raises if a kernel met an index outside its tables."""
-        code = int(self.error.item())
+        self._raise_for(int(self.error.item()))
+
+    def _raise_for(self, code: int) -> None:
         if code:
             self.error.zero_()
             what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",

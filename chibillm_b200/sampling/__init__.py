@@ -1,4 +1,4 @@
 """Sampling: greedy and temperature."""
-from .sampler import Sampler, SamplingParams, uniform_for
+from .sampler import PendingTokens, Sampler, SamplingParams, uniform_for
 
-__all__ = ["Sampler", "SamplingParams", "uniform_for"]
+__all__ = ["PendingTokens", "Sampler", "SamplingParams", "uniform_for"]

@@ -34,15 +34,38 @@ def uniform_for(seed: int, request_key: int, index: int) -> float:
     return (int.from_bytes(digest[:8], "little") >> 40) / float(1 << 24)
 
 
+class PendingTokens:
+    """Tokens that the device has chosen and is sending to the host.
+    ``device_ids`` (int32, one per row) can be used on the device at once;
+    ``result()`` waits for the copy and returns them as a list."""
+
+    def __init__(self, device_ids: torch.Tensor, host: Optional[torch.Tensor], event):
+        self.device_ids, self._host, self._event = device_ids, host, event
+        self._list: Optional[List[int]] = None
+
+    def result(self) -> List[int]:
+        if self._list is None:
+            if self._host is None:
+                self._list = self.device_ids.tolist()
+            else:
+                self._event.synchronize()
+                self._list = self._host[:self.device_ids.numel()].tolist()
+        return self._list
+
+
 class Sampler:
     def __init__(self, runtime):
         self.runtime = runtime
         self._out: Optional[torch.Tensor] = None
+        self._host = [None, None]        # pinned arrays, taken in turn
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               request_keys: Sequence[int], indices: Sequence[int]) -> List[int]:
-        """One token per row of ``logits``.  ``indices[r]`` is how many tokens
-        request r has generated before this one."""
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               request_keys: Sequence[int], indices: Sequence[int]) -> PendingTokens:
+        """One token per row of ``logits``, chosen on the device; the copy to
+        the host is started and an event marks its end, so that work queued
+        after this call does not hold the tokens back.  ``indices[r]`` is how
+        many tokens request r has generated before this one."""
         R = logits.shape[0]
         if not (len(params) == len(request_keys) == len(indices) == R):
             raise ValueError("one SamplingParams, key and index per row of logits")
@@ -57,4 +80,19 @@ class Sampler:
             unis = torch.tensor([uniform_for(p.seed, k, i) for p, k, i in zip(params, request_keys, indices)],
                                 dtype=torch.float32)
             self.runtime.kernels.sample(logits, temps.to(dev), unis.to(dev), out)
-        return out.tolist()
+        if dev.type != "cuda":
+            return PendingTokens(out, None, None)
+        self._turn ^= 1
+        host = self._host[self._turn]
+        if host is None or host.numel() < R:
+            host = torch.empty(max(R, 64), dtype=torch.int32, pin_memory=True)
+            self._host[self._turn] = host
+        host[:R].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(out, host, event)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               request_keys: Sequence[int], indices: Sequence[int]) -> List[int]:
+        """``launch`` and wait: the tokens as a list."""
+        return self.launch(logits, params, request_keys, indices).result()
