@@ -238,8 +238,9 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
-// Head jobs per warp: 1 for few tokens (as many warps as possible work side by
-// side), 4 for many tokens (their loads are all in flight together).
+// JPW head jobs per warp.  Every launch uses 1 (as many warps as possible side by
+// side); more per warp measured slower, and many tokens with 128-feature heads
+// take the per-token kernel below.
 template <int JPW, typename TX, typename TQ, typename TW, typename TC>
 __global__ void qk_norm_rope_append_vec4_kernel(
     const TX* __restrict__ qkv, long long qkv_stride, int splits, long long split_stride,
