@@ -26,7 +26,7 @@ def _generate(cfg, prompts, params, run_ahead, max_sequences=3):
     return out, runner.steps_ahead_used, runner.steps_ahead_dropped
 
 
-@pytest.mark.parametrize("name", ["D128", "B"])
+@pytest.mark.parametrize("name", ["D128", "B", "C"])
 def test_running_ahead_gives_the_same_tokens(name):
     from chibillm_b200.sampling import SamplingParams
     cfg = copy.deepcopy(tiny_configs.get(name))
