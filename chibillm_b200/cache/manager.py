@@ -20,13 +20,17 @@ reference has this only for its hybrid model
 (src/qwen/qwen3_5_model_state.cc:148-166); here every model has the slots, of
 size zero when no mixer declares state.
 
-Host bookkeeping only; the arrays live in :class:`CacheStorage`.
+Host bookkeeping only; the arrays live in :class:`CacheStorage`.  The bookkeeping
+itself is C++ (``csrc/runtime.cc``); the classes here hold a handle and turn its
+status codes into :class:`CacheError`.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+from . import native
 
 
 class CacheError(RuntimeError):
@@ -35,68 +39,53 @@ class CacheError(RuntimeError):
         self.code = code
 
 
+def _raise(status: int, what: str = "") -> None:
+    code = native.ERROR_CODES.get(status, f"status {status}")
+    message = native.error_message()
+    if code == "invariant":
+        raise AssertionError(message)
+    raise CacheError(code, f"{what}{message}" if what else message)
+
+
+def _ints(values: Sequence[int]):
+    return (ctypes.c_int * len(values))(*values)
+
+
 class PagePool:
     """A first-in first-out free list of page ids."""
 
     def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise CacheError("invalid_configuration", "a page pool needs at least one page")
+        self._lib = native.runtime()
+        self._handle = self._lib.chibi_pool_new(int(num_pages))
+        if not self._handle:
+            raise CacheError("invalid_configuration", native.error_message())
         self.num_pages = num_pages
-        self._free = deque(range(num_pages))
-        self._held = [False] * num_pages
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.chibi_pool_delete(self._handle)
+            self._handle = None
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return self._lib.chibi_pool_free_count(self._handle)
 
     @property
     def used_count(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.free_count
 
     def take(self, count: int) -> List[int]:
-        if count > len(self._free):
-            raise CacheError("capacity_exhausted", f"{count} pages wanted, {len(self._free)} free")
-        out = []
-        for _ in range(count):
-            p = self._free.popleft()
-            assert not self._held[p], "page handed out twice"
-            self._held[p] = True
-            out.append(p)
-        return out
+        out = (ctypes.c_int * max(count, 1))()
+        status = self._lib.chibi_pool_take(self._handle, int(count), out)
+        if status < 0:
+            _raise(status)
+        return list(out[:count])
 
     def give(self, pages: Sequence[int]) -> None:
         for p in pages:
-            if not (0 <= p < self.num_pages) or not self._held[p]:
-                raise CacheError("invalid_release", f"page {p} is not held")
-            self._held[p] = False
-            self._free.append(p)
-
-
-class SlotPool:
-    """State slots, lowest free index first."""
-
-    def __init__(self, num_slots: int):
-        self.num_slots = num_slots
-        self._free = list(range(num_slots - 1, -1, -1))
-        self._held = [False] * num_slots
-
-    @property
-    def free_count(self) -> int:
-        return len(self._free)
-
-    def take(self) -> int:
-        if not self._free:
-            raise CacheError("capacity_exhausted", "no state slot is free")
-        s = self._free.pop()
-        self._held[s] = True
-        return s
-
-    def give(self, slot: int) -> None:
-        if not (0 <= slot < self.num_slots) or not self._held[slot]:
-            raise CacheError("invalid_release", f"state slot {slot} is not held")
-        self._held[slot] = False
-        self._free.append(slot)
-        self._free.sort(reverse=True)
+            status = self._lib.chibi_pool_give(self._handle, int(p))
+            if status < 0:
+                _raise(status)
 
 
 @dataclass(frozen=True)
@@ -115,6 +104,8 @@ class GroupLayout:
 
 @dataclass
 class RequestCache:
+    """What the manager holds for one request, as of the call that returned it."""
+
     request_id: Hashable
     length: int = 0                       # tokens whose keys are stored (committed)
     reserved: int = 0                     # tokens that the tables have room for
@@ -138,129 +129,147 @@ def first_needed_block(length: int, window: Optional[int], page_size: int) -> in
     return first_pos // page_size
 
 
+class _SlotCounts:
+    """The state slots of a manager, as numbers (the pool itself is in the C++ manager)."""
+
+    def __init__(self, manager: "CacheManager"):
+        self._manager = manager
+        self.num_slots = manager.max_requests
+
+    @property
+    def free_count(self) -> int:
+        return self._manager._lib.chibi_cache_free_slots(self._manager._handle)
+
+
 class CacheManager:
     def __init__(self, groups: Sequence[GroupLayout], max_requests: int):
-        if max_requests <= 0:
-            raise CacheError("invalid_configuration", "max_requests must be positive")
+        self._lib = native.runtime()
         self.groups: Dict[str, GroupLayout] = {g.name: g for g in groups}
-        self.pools: Dict[str, PagePool] = {g.name: PagePool(g.num_pages) for g in groups}
-        self.slots = SlotPool(max_requests)
+        self._group_index = {g.name: i for i, g in enumerate(groups)}
+        self._handle = self._lib.chibi_cache_new(
+            len(groups), _ints([g.page_size for g in groups]), _ints([g.num_pages for g in groups]),
+            _ints([-1 if g.window is None else g.window for g in groups]), _ints([g.max_blocks for g in groups]),
+            int(max_requests))
+        if not self._handle:
+            raise CacheError("invalid_configuration", native.error_message())
         self.max_requests = max_requests
-        self.requests: Dict[Hashable, RequestCache] = {}
-        # per group: (table row, logical block, page or -1) changes since the last drain, in
-        # order; the row of a request is its state slot
-        self._updates: Dict[str, List[Tuple[int, int, int]]] = {g.name: [] for g in groups}
+        # request ids may be any hashable: the C++ side knows them by a running number
+        self._numbers: Dict[Hashable, int] = {}
+        self._next_number = 0
+        self._info = (ctypes.c_int * 3)()
+        self.slots = _SlotCounts(self)
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.chibi_cache_delete(self._handle)
+            self._handle = None
+
+    # ---- the C++ side's view
+    @property
+    def handle(self):
+        return self._handle
+
+    def number_of(self, request_id: Hashable) -> int:
+        try:
+            return self._numbers[request_id]
+        except KeyError:
+            raise CacheError("unknown_request", f"request {request_id!r} is not admitted") from None
+
+    def group_order(self) -> List[str]:
+        return list(self._group_index)
 
     def drain_updates(self, group: str) -> List[Tuple[int, int, int]]:
         """Block-table changes since the last call, for the mirror on the device:
         at most one per (row, block), the latest (they are applied in parallel)."""
-        last: Dict[Tuple[int, int], int] = {}
-        for row, index, page in self._updates[group]:
-            last[(row, index)] = page
-        self._updates[group] = []
-        return [(row, index, page) for (row, index), page in last.items()]
+        g = self._group_index[group]
+        n = self._lib.chibi_cache_pending_updates(self._handle, g)
+        out = (ctypes.c_int * max(3 * n, 1))()
+        count = self._lib.chibi_cache_drain(self._handle, g, out, n)
+        if count < 0:
+            _raise(count)
+        return [(out[3 * i], out[3 * i + 1], out[3 * i + 2]) for i in range(count)]
 
     # ---- queries
+    @property
+    def requests(self) -> Dict[Hashable, RequestCache]:
+        return {rid: self.get(rid) for rid in self._numbers}
+
     def has(self, request_id: Hashable) -> bool:
-        return request_id in self.requests
+        return request_id in self._numbers
 
     def get(self, request_id: Hashable) -> RequestCache:
-        try:
-            return self.requests[request_id]
-        except KeyError:
-            raise CacheError("unknown_request", f"request {request_id!r} is not admitted") from None
+        number = self.number_of(request_id)
+        status = self._lib.chibi_cache_info(self._handle, number, self._info)
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
+        rc = RequestCache(request_id, length=self._info[0], reserved=self._info[1], state_slot=self._info[2])
+        for name, g in self._group_index.items():
+            n = self._lib.chibi_cache_table(self._handle, number, g, None, 0)
+            buf = (ctypes.c_int * max(n, 1))()
+            self._lib.chibi_cache_table(self._handle, number, g, buf, n)
+            rc.tables[name] = list(buf[:n])
+        return rc
 
     def length(self, request_id: Hashable) -> int:
-        return self.get(request_id).length
+        status = self._lib.chibi_cache_info(self._handle, self.number_of(request_id), self._info)
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
+        return self._info[0]
+
+    def state_slot(self, request_id: Hashable) -> int:
+        status = self._lib.chibi_cache_info(self._handle, self.number_of(request_id), self._info)
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
+        return self._info[2]
 
     def free_pages(self, group: str) -> int:
-        return self.pools[group].free_count
+        return self._lib.chibi_cache_free_pages(self._handle, self._group_index[group])
 
     def worst_case_pages(self, group: str, tokens: int) -> int:
         """Most pages of this group that a request of ``tokens`` tokens holds at
         one time (all of them without a window)."""
-        g = self.groups[group]
-        return pages_for(tokens, g.page_size)
+        return pages_for(tokens, self.groups[group].page_size)
 
     # ---- life of a request
     def admit(self, request_id: Hashable) -> RequestCache:
-        if request_id in self.requests:
+        if request_id in self._numbers:
             raise CacheError("duplicate_request", f"request {request_id!r} is already admitted")
-        slot = self.slots.take()
-        rc = RequestCache(request_id, state_slot=slot, tables={name: [] for name in self.groups})
-        self.requests[request_id] = rc
-        return rc
+        number = self._next_number
+        slot = self._lib.chibi_cache_admit(self._handle, number)
+        if slot < 0:
+            _raise(slot)
+        self._next_number += 1
+        self._numbers[request_id] = number
+        return RequestCache(request_id, state_slot=slot, tables={name: [] for name in self.groups})
 
     def reserve(self, request_id: Hashable, tokens: int) -> None:
         """Make room for the request to hold ``tokens`` tokens, in every group,
         or change nothing."""
         if tokens <= 0:
             raise CacheError("invalid_reservation", "a reservation needs at least one token")
-        rc = self.get(request_id)
-        if tokens <= rc.reserved:
-            return
-        wanted = {}
-        for name, g in self.groups.items():
-            need = pages_for(tokens, g.page_size) - len(rc.tables[name])
-            if need > self.pools[name].free_count:
-                raise CacheError("capacity_exhausted",
-                                 f"group '{name}': {need} pages wanted for request {request_id!r}, "
-                                 f"{self.pools[name].free_count} free")
-            wanted[name] = need
-        for name, need in wanted.items():
-            if need > 0:
-                table = rc.tables[name]
-                limit = self.groups[name].max_blocks
-                if limit and len(table) + need > limit:
-                    raise CacheError("invalid_reservation",
-                                     f"group '{name}': {len(table) + need} blocks exceed the table's {limit}")
-                for page in self.pools[name].take(need):
-                    self._updates[name].append((rc.state_slot, len(table), page))
-                    table.append(page)
-        rc.reserved = max(rc.reserved, tokens)
+        status = self._lib.chibi_cache_reserve(self._handle, self.number_of(request_id), int(tokens))
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
 
     def commit(self, request_id: Hashable, new_length: int) -> None:
         """The request now holds ``new_length`` tokens; pages that its windows
         have passed go back to their pools."""
-        rc = self.get(request_id)
-        if new_length < rc.length or new_length > rc.reserved:
-            raise CacheError("invalid_commit",
-                             f"request {request_id!r}: length {rc.length} -> {new_length}, reserved {rc.reserved}")
-        rc.length = new_length
-        for name, g in self.groups.items():
-            if g.window is None:
-                continue
-            table = rc.tables[name]
-            dead = min(first_needed_block(new_length, g.window, g.page_size), len(table))
-            gone = [p for p in table[:dead] if p >= 0]
-            if gone:
-                self.pools[name].give(gone)
-                for i in range(dead):
-                    if table[i] >= 0:
-                        self._updates[name].append((rc.state_slot, i, -1))
-                    table[i] = -1
+        status = self._lib.chibi_cache_commit(self._handle, self.number_of(request_id), int(new_length))
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
 
     def release(self, request_id: Hashable) -> None:
-        rc = self.requests.pop(request_id, None)
-        if rc is None:
+        number = self._numbers.pop(request_id, None)
+        if number is None:
             return
-        for name, table in rc.tables.items():
-            self.pools[name].give([p for p in table if p >= 0])
-        self.slots.give(rc.state_slot)
+        status = self._lib.chibi_cache_release(self._handle, number)
+        if status < 0:
+            _raise(status, f"request {request_id!r}: ")
 
     # ---- checks (used by tests and by debug runs)
     def check_invariants(self) -> None:
-        for name, pool in self.pools.items():
-            held = [p for rc in self.requests.values() for p in rc.tables[name] if p >= 0]
-            if len(held) != len(set(held)):
-                raise AssertionError(f"group '{name}': a page is held twice")
-            free = list(pool._free)
-            if len(free) != len(set(free)) or set(free) & set(held):
-                raise AssertionError(f"group '{name}': free list and tables overlap")
-            if len(free) + len(held) != pool.num_pages:
-                raise AssertionError(f"group '{name}': {pool.num_pages - len(free) - len(held)} pages lost")
-        slots = [rc.state_slot for rc in self.requests.values()]
-        if len(slots) != len(set(slots)):
-            raise AssertionError("a state slot is held twice")
-        if len(slots) + self.slots.free_count != self.slots.num_slots:
-            raise AssertionError("a state slot is lost")
+        status = self._lib.chibi_cache_check(self._handle)
+        if status < 0:
+            _raise(status)
+        if self._lib.chibi_cache_count(self._handle) != len(self._numbers):
+            raise AssertionError("the two sides disagree on the number of requests")

@@ -157,6 +157,53 @@ def ensure_library(name: str, defines: Sequence[str] = (), verbose: bool = True)
     return target
 
 
+# ------------------------------------------------------------------ the host-side runtime
+HOST_SOURCES = ["runtime.cc"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-static-libstdc++", "-static-libgcc"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler was found (looked at CXX, g++, c++, clang++); the host-side runtime "
+                     "of chibillm_b200 (cache manager, scheduler) cannot be compiled")
+
+
+def runtime_library(verbose: bool = True) -> str:
+    """The cache manager, the scheduler and the batch packing: plain C++, no CUDA."""
+    h = hashlib.sha256()
+    for name in HOST_SOURCES:
+        with open(os.path.join(CSRC, name), "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    target = os.path.join(library_dir(), f"libchibi_runtime_{h.hexdigest()[:12]}.so")
+    if os.path.isfile(target):
+        return target
+    cxx = find_cxx()
+    started = time.time()
+    fd, tmp = tempfile.mkstemp(suffix=".so", dir=os.path.dirname(target))
+    os.close(fd)
+    try:
+        _run([cxx] + HOST_FLAGS + [os.path.join(CSRC, s) for s in HOST_SOURCES] + ["-o", tmp])
+        os.chmod(tmp, 0o755)
+        os.replace(tmp, target)
+    finally:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+    if verbose:
+        _say(f"{os.path.basename(target)} (host runtime, {cxx}) ready in {time.time() - started:.1f} s")
+    for f in os.listdir(os.path.dirname(target)):
+        full = os.path.join(os.path.dirname(target), f)
+        if f.startswith("libchibi_runtime_") and f.endswith(".so") and full != target:
+            try:
+                os.remove(full)
+            except OSError:
+                pass
+    return target
+
+
 def attention_library(head_dim: int, verbose: bool = True) -> str:
     return ensure_library("chibi_attention_mma", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
 
@@ -166,7 +213,7 @@ def attention_tc_library(head_dim: int, verbose: bool = True) -> str:
 
 
 def build_all(verbose: bool = True) -> List[str]:
-    out = [ensure_library("chibi_kernels", verbose=verbose)]
+    out = [runtime_library(verbose), ensure_library("chibi_kernels", verbose=verbose)]
     with ThreadPoolExecutor(max_workers=4) as pool:
         out += list(pool.map(lambda d: attention_library(d, verbose), PREBUILT_HEAD_DIMS))
         out += list(pool.map(lambda d: attention_tc_library(d, verbose), TCGEN05_ATTENTION_HEAD_DIMS))

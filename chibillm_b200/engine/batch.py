@@ -6,12 +6,13 @@ chunks and decode tokens in separate batches.  Here one batch holds any mix:
 every entry is (request, its next tokens, the places whose logits are wanted);
 a decode token is an entry of one token.  Metadata is per sequence
 (``q_start``, ``ctx_len``, one block-table row per group) plus per token
-(``positions``, ``seq_of_token``).
+(``positions``, ``seq_of_token``).  The flattening itself, with its checks, is
+``chibi_pack_step`` of the C++ runtime (``csrc/runtime.cc``).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Sequence, Tuple
 
 import torch
 
@@ -90,47 +91,3 @@ class StepContext:
     @property
     def decode_only(self) -> bool:
         return self.max_q_len == 1
-
-
-def flatten_entries(entries: Sequence[StepEntry], lengths: Dict[Hashable, int], vocab_size: int,
-                    max_positions: int):
-    """Host-side flattening and checks (the checks of src/model_batch.cc:52-85,
-    148-203 that apply here): no request twice, at least one token each, ids
-    inside the vocabulary, positions below the model's limit, wanted places
-    inside the entry."""
-    seen = set()
-    tokens: List[int] = []
-    positions: List[int] = []
-    seq_of_token: List[int] = []
-    q_start = [0]
-    ctx_lens: List[int] = []
-    q_lens: List[int] = []
-    logit_rows: List[int] = []
-    for s, e in enumerate(entries):
-        if e.request_id in seen:
-            raise BatchError(f"request {e.request_id!r} appears twice in one step")
-        seen.add(e.request_id)
-        n = len(e.tokens)
-        if n == 0:
-            raise BatchError(f"request {e.request_id!r} brings no tokens")
-        start = lengths[e.request_id]
-        if start + n > max_positions:
-            raise BatchError(f"request {e.request_id!r} would reach position {start + n - 1}; "
-                             f"the model's limit is {max_positions - 1}")
-        for i, tok in enumerate(e.tokens):
-            tok = int(tok)
-            if not (0 <= tok < vocab_size):
-                raise BatchError(f"request {e.request_id!r}: token id {tok} is outside the vocabulary "
-                                 f"of {vocab_size}")
-            tokens.append(tok)
-            positions.append(start + i)
-            seq_of_token.append(s)
-        for w in e.want:
-            w = int(w)
-            if not (0 <= w < n):
-                raise BatchError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
-            logit_rows.append(q_start[-1] + w)
-        q_start.append(q_start[-1] + n)
-        q_lens.append(n)
-        ctx_lens.append(start + n)
-    return tokens, positions, seq_of_token, q_start, q_lens, ctx_lens, logit_rows

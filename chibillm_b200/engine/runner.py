@@ -12,16 +12,18 @@ pages that former steps wrote.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
+from ..cache import native
 from ..cache.manager import CacheError, CacheManager
 from ..cache.storage import CacheStorage, FixedStateView, plan_cache
 from ..config.registry import load_config
 from ..parts.base import Runtime
 from ..weights.loader import load_weights
-from .batch import BatchError, StepContext, StepEntry, Workspace, flatten_entries
+from .batch import BatchError, StepContext, StepEntry, Workspace
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -146,47 +148,53 @@ class ModelRunner:
         return self._meta_host, self._meta_dev
 
     def _build_context(self, entries: Sequence[StepEntry], fixed_update_capacity: bool):
-        """Flatten the entries, send the packed metadata to the device and bring
-        the device's block tables up to date.  With ``fixed_update_capacity`` the
-        layout of the packed array depends only on the numbers of tokens,
-        sequences and wanted rows (what a captured graph needs); returns None if
-        the table updates of this step do not fit that layout."""
-        lengths = {e.request_id: self.cache.length(e.request_id) for e in entries}
-        (tokens, positions, seq_of_token, q_start, q_lens, ctx_lens, logit_rows) = flatten_entries(
-            entries, lengths, self.spec.vocab_size, self.spec.max_positions)
-        T, S, R = len(tokens), len(entries), len(logit_rows)
-        slots = [self.cache.get(e.request_id).state_slot for e in entries]
-        updates = {g.name: self.cache.drain_updates(g.name) for g in self.plan.groups}
-        if fixed_update_capacity and any(len(u) > 2 * S for u in updates.values()):
-            fixed_update_capacity = False
-        caps = {name: (2 * S if fixed_update_capacity else len(u)) for name, u in updates.items()}
-        # layout of the packed array, every segment on a 16-byte boundary
-        segments = [("tokens", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1),
-                    ("ctx_len", S), ("state_slots", S), ("logit_rows", R)]
-        segments += [("updates:" + name, 1 + 3 * cap) for name, cap in caps.items()]
-        offsets, cursor = {}, 0
-        for name, n in segments:
-            offsets[name] = cursor
-            cursor += _align4(max(n, 1))
-        host, dev = self._meta_buffers(cursor)
-        flat = [0] * cursor
-
-        def put(name, values):
-            o = offsets[name]
-            flat[o:o + len(values)] = values
-
-        put("tokens", tokens)
-        put("positions", positions)
-        put("seq_of_token", seq_of_token)
-        put("q_start", q_start)
-        put("ctx_len", ctx_lens)
-        put("state_slots", slots)
-        put("logit_rows", logit_rows)
-        for name, ups in updates.items():
-            put("updates:" + name, [len(ups)] + [v for triple in ups for v in triple])
-        if self._meta_copied is not None:
-            self._meta_copied.synchronize()     # the pinned array may still be read by the last copy
-        host[:cursor] = torch.tensor(flat, dtype=torch.int32)
+        """Make room for the entries' tokens, flatten them, send the packed
+        metadata to the device and hand back what brings the device's block tables
+        up to date.  The checks, the reservations and the packing are one call into
+        the C++ runtime, which writes straight into the pinned array.  With
+        ``fixed_update_capacity`` the layout of the packed array depends only on the
+        numbers of tokens, sequences and wanted rows (what a captured graph needs);
+        the third value returned says whether the table updates of this step fitted
+        that layout."""
+        cache = self.cache
+        S = len(entries)
+        groups = cache.group_order()
+        G = len(groups)
+        q_lens = [len(e.tokens) for e in entries]
+        want_lens = [len(e.want) for e in entries]
+        T, R = sum(q_lens), sum(want_lens)
+        ids = (ctypes.c_longlong * S)(*[cache.number_of(e.request_id) for e in entries])
+        n_tokens = (ctypes.c_int * S)(*q_lens)
+        n_want = (ctypes.c_int * S)(*want_lens)
+        try:
+            tokens = (ctypes.c_int * max(T, 1))(*[int(t) for e in entries for t in e.tokens])
+            want = (ctypes.c_int * max(R, 1))(*[int(w) for e in entries for w in e.want])
+        except (OverflowError, TypeError) as exc:
+            raise BatchError(f"token ids and wanted places must be integers that fit 32 bits: {exc}") from None
+        info = (ctypes.c_int * (13 + 2 * G))()
+        words = 3 * _align4(max(T, 1)) + _align4(S + 1) + 2 * _align4(S) + _align4(max(R, 1)) \
+            + G * _align4(1 + 6 * S) + 64
+        while True:
+            host, dev = self._meta_buffers(words)
+            if self._meta_copied is not None:
+                self._meta_copied.synchronize()     # the pinned array may still be read by the last copy
+            status = native.runtime().chibi_pack_step(
+                cache.handle, S, ids, n_tokens, tokens, n_want, want, self.spec.vocab_size,
+                self.spec.max_positions, 1 if fixed_update_capacity else 0, host.data_ptr(), host.numel(),
+                info, len(info))
+            if status == 0:
+                break
+            code = native.ERROR_CODES.get(status)
+            if code == "buffer_too_small" and words < (1 << 28):
+                words *= 4                          # many table updates at once: a larger array
+                continue
+            message = native.error_message()
+            if code in ("batch", "unknown_request"):
+                raise BatchError(message)
+            raise CacheError(code or f"status {status}", message)
+        cursor, max_ctx, fixed = info[3], info[4], bool(info[5])
+        offsets = dict(zip(("tokens", "positions", "seq_of_token", "q_start", "ctx_len", "state_slots",
+                            "logit_rows"), info[6:13]))
         dev[:cursor].copy_(host[:cursor], non_blocking=True)
         if dev.is_cuda:
             if self._meta_copied is None:
@@ -198,16 +206,20 @@ class ModelRunner:
             o = offsets[name]
             return dev[o:o + n]
 
+        ctx_lens = host[offsets["ctx_len"]:offsets["ctx_len"] + S].tolist()
+        slots = host[offsets["state_slots"]:offsets["state_slots"] + S].tolist()
         ctx = StepContext(
             num_tokens=T, num_seqs=S, tokens=view("tokens", T), positions=view("positions", T),
             seq_of_token=view("seq_of_token", T), q_start=view("q_start", S + 1),
             ctx_len=view("ctx_len", S), state_slots=view("state_slots", S),
             logit_rows=view("logit_rows", R), tables=self.storage.tables, workspace=self.workspace,
             request_ids=[e.request_id for e in entries], q_lens=q_lens, ctx_lens=ctx_lens,
-            slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens),
-            max_ctx_len=max(ctx_lens))
-        update_views = {name: (view("updates:" + name, 1 + 3 * cap), cap) for name, cap in caps.items()}
-        return ctx, update_views, fixed_update_capacity
+            slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max_ctx)
+        update_views = {}
+        for g, name in enumerate(groups):
+            o, cap = info[13 + g], info[13 + G + g]
+            update_views[name] = (dev[o:o + 1 + 3 * cap], cap)
+        return ctx, update_views, fixed
 
     def _run_model(self, ctx: StepContext, update_views) -> Optional[torch.Tensor]:
         k = self.runtime.kernels
@@ -352,8 +364,6 @@ class ModelRunner:
         for e in entries:
             if not self.cache.has(e.request_id):
                 self.admit(e.request_id)
-        for e in entries:
-            self.cache.reserve(e.request_id, self.cache.length(e.request_id) + len(e.tokens))
         decode_only = all(len(e.tokens) == 1 for e in entries)
         ctx, update_views, fixed = self._build_context(entries, decode_only and self.use_graphs)
         key = self._graph_key(ctx) if fixed else None

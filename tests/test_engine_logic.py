@@ -108,3 +108,28 @@ def test_generation_through_entry_point_on_cpu(tmp_path):
         assert got == expected, f"budget {budget}"
         llm.runner.cache.check_invariants()
         assert not llm.runner.cache.requests
+
+
+def test_a_step_refuses_what_it_cannot_run(tmp_path):
+    """The checks of the batch packing (in the C++ runtime): a request twice, no
+    tokens, an id outside the vocabulary, a position past the model's limit, a
+    wanted place outside the entry; and a refused step changes no length."""
+    from chibillm_b200.engine.batch import BatchError, StepEntry
+    folder = helpers.make_model_dir(tmp_path, "A", seed=3)
+    cfg = tiny_configs.get("A")
+    runner = cpu_runner(folder, 4, 256)
+    runner.step([StepEntry("a", [1, 2, 3], [2])])
+    for entries, what in (
+            ([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])], "twice"),
+            ([StepEntry("a", [], [])], "no tokens"),
+            ([StepEntry("a", [cfg["vocab_size"]], [0])], "vocabulary"),
+            ([StepEntry("a", [-1], [0])], "vocabulary"),
+            ([StepEntry("a", [1, 2], [2])], "wanted place"),
+            ([StepEntry("a", [1] * cfg["max_position_embeddings"], [0])], "limit")):
+        with pytest.raises(BatchError) as e:
+            runner.step(entries)
+        assert what in str(e.value), (what, str(e.value))
+        assert runner.length("a") == 3
+    logits = runner.step([StepEntry("a", [4], [0])])
+    assert logits.shape == (1, cfg["vocab_size"]) and runner.length("a") == 4
+    runner.cache.check_invariants()
