@@ -36,6 +36,22 @@ _SIGNATURES = {
     "chibi_cache_pending_updates": ([c_void_p, c_int], c_int),
     "chibi_cache_drain": ([c_void_p, c_int, IP, c_int], c_int),
     "chibi_cache_check": ([c_void_p], c_int),
+    "chibi_sched_new": ([c_void_p, c_int, c_int, c_int, c_int], c_void_p),
+    "chibi_sched_delete": ([c_void_p], None),
+    "chibi_sched_fits_cache": ([c_void_p, c_int, c_int], c_int),
+    "chibi_sched_admission": ([c_void_p, c_int, c_int], c_int),
+    "chibi_sched_add": ([c_void_p, c_longlong, IP, c_int, c_int, c_int], c_int),
+    "chibi_sched_has_work": ([c_void_p], c_int),
+    "chibi_sched_active": ([c_void_p], c_int),
+    "chibi_sched_schedule": ([c_void_p, LP, c_int, IP], c_int),
+    "chibi_sched_complete": ([c_void_p, c_int, IP, c_int, LP, c_int], c_int),
+    "chibi_sched_abort": ([c_void_p, c_int], c_int),
+    "chibi_sched_cancel": ([c_void_p, c_longlong], c_int),
+    "chibi_sched_remove": ([c_void_p, c_longlong], c_int),
+    "chibi_sched_info": ([c_void_p, c_longlong, IP], c_int),
+    "chibi_sched_tokens": ([c_void_p, c_longlong, c_int, c_int, IP], c_int),
+    "chibi_sched_queue": ([c_void_p, c_int, LP, c_int], c_int),
+    "chibi_sched_check": ([c_void_p], c_int),
     "chibi_pack_step": ([c_void_p, c_int, LP, IP, IP, IP, IP, c_int, c_int, c_int, c_void_p, c_int, IP, c_int],
                         c_int),
 }

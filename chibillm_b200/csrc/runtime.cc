@@ -567,3 +567,410 @@ RT_API int chibi_pack_step(void* cache, int num_entries, const long long* ids, c
     }
     return 0;
 }
+
+// ------------------------------------------------------------------ scheduler
+// Admits requests, cuts prompts into portions under a token budget, decodes,
+// finishes.  Kept from the reference (src/scheduler.cc, src/seq.cc): a sequence is
+// waiting (prompt not fully processed), running (one token per step) or finished;
+// after the last portion of the prompt the sampled token is appended unprocessed, and
+// every decode step processes it and appends the next (src/seq.cc:138-160,
+// src/scheduler.cc:393-398); admission is three-way (src/scheduler.cc:162-235); the page
+// budget is the worst case of every live request, so pages cannot run out in the middle
+// of a request (src/scheduler.cc:13-22); a portion is min(what is left, quantum, what
+// the step's budget has left), the quantum being prefill_chunk_tokens while requests
+// compete and the whole budget otherwise (src/scheduler.cc:259-275); a prompt that was
+// not finished goes to the back of the waiting queue (src/scheduler.cc:376-383); stop:
+// EOS first, then length (src/seq.cc:287-303).  Changed: every step takes one token of
+// every running sequence first and fills what is left of the budget with prompt
+// portions, in one mixed batch.
+//
+// The scheduler reserves pages itself (it shares the cache manager) but neither admits
+// requests to the cache nor releases them: its caller does, when told.
+namespace {
+
+enum : int {
+    SC_BATCH_IN_FLIGHT = -20,
+    SC_DUPLICATE_SEQUENCE = -21,
+    SC_INVALID_SEQUENCE_STATE = -22,
+    SC_NO_RUNNABLE_SEQUENCES = -23,
+    SC_CACHE_CAPACITY_EXHAUSTED = -24,
+    SC_BLOCK_MANAGER_FAILURE = -25,
+    SC_NO_BATCH_IN_FLIGHT = -26,
+    SC_BATCH_ID_MISMATCH = -27,
+    SC_RESULT_COUNT_MISMATCH = -28,
+    SC_UNKNOWN_SEQUENCE = -29,
+    SC_SEQUENCE_NOT_FINISHED = -30,
+    SC_INVALID_CONFIGURATION = -31,
+};
+
+enum : int { ST_WAITING = 0, ST_RUNNING = 1, ST_FINISHED = 2 };
+enum : int { FR_NONE = 0, FR_EOS = 1, FR_LEN_LIMIT = 2, FR_CANCELLED = 3 };
+enum : int { AD_ADMITTED = 0, AD_DEFERRED = 1, AD_TOO_LARGE = 2 };
+
+struct Seq {
+    std::vector<int> tokens;
+    int prompt_len = 0, processed = 0, scheduled = 0, status = ST_WAITING, reason = FR_NONE;
+    int max_new_tokens = 0;
+    bool ignore_eos = false;
+    int schedulable() const { return static_cast<int>(tokens.size()) - processed - scheduled; }
+    int completion_len() const { return static_cast<int>(tokens.size()) - prompt_len; }
+};
+
+struct Item {
+    long long id;
+    int first, count, sample;
+};
+
+class Scheduler {
+public:
+    Scheduler(CacheManager* cache, int max_sequences, int max_batch_tokens, int prefill_chunk_tokens, int eos)
+        : cache_(cache), max_sequences_(max_sequences), max_batch_tokens_(max_batch_tokens),
+          prefill_chunk_tokens_(prefill_chunk_tokens), eos_(eos)
+    {
+    }
+    bool active() const { return active_; }
+    int active_id() const { return active_id_; }
+    const std::vector<Item>& active_items() const { return items_; }
+    const std::deque<long long>& queue(int which) const { return which ? running_ : waiting_; }
+    Seq* find(long long id)
+    {
+        auto it = seqs_.find(id);
+        return it == seqs_.end() ? nullptr : &it->second;
+    }
+    static int budget_tokens(int prompt_len, int max_new_tokens) { return prompt_len + max_new_tokens - 1; }
+    bool fits_cache(int prompt_len, int max_new_tokens) const
+    {
+        for (int g = 0; g < cache_->num_groups(); ++g)
+            if (pages_for(budget_tokens(prompt_len, max_new_tokens), cache_->group(g).page_size)
+                > cache_->group(g).num_pages)
+                return false;
+        return true;
+    }
+    int admission(int prompt_len, int max_new_tokens) const
+    {
+        if (active_)
+            return fail(SC_BATCH_IN_FLIGHT, "a batch is in flight");
+        if (!fits_cache(prompt_len, max_new_tokens))
+            return AD_TOO_LARGE;
+        if (static_cast<int>(waiting_.size() + running_.size()) >= max_sequences_)
+            return AD_DEFERRED;
+        for (int g = 0; g < cache_->num_groups(); ++g) {
+            const int page_size = cache_->group(g).page_size;
+            int available = cache_->group(g).num_pages;
+            for (const auto* q : { &waiting_, &running_ })
+                for (long long id : *q) {
+                    const Seq& s = seqs_.at(id);
+                    available -= pages_for(budget_tokens(s.prompt_len, s.max_new_tokens), page_size);
+                }
+            if (pages_for(budget_tokens(prompt_len, max_new_tokens), page_size) > available)
+                return AD_DEFERRED;
+        }
+        return AD_ADMITTED;
+    }
+    int add(long long id, const int* prompt, int prompt_len, int max_new_tokens, bool ignore_eos)
+    {
+        if (active_)
+            return fail(SC_BATCH_IN_FLIGHT, "a batch is in flight");
+        if (seqs_.count(id))
+            return fail(SC_DUPLICATE_SEQUENCE, "the sequence is already known");
+        if (prompt_len <= 0 || max_new_tokens <= 0)
+            return fail(SC_INVALID_SEQUENCE_STATE, "a sequence needs a prompt and a positive token limit");
+        Seq s;
+        s.tokens.assign(prompt, prompt + prompt_len);
+        s.prompt_len = prompt_len;
+        s.max_new_tokens = max_new_tokens;
+        s.ignore_eos = ignore_eos;
+        seqs_.emplace(id, std::move(s));
+        waiting_.push_back(id);
+        return 0;
+    }
+    bool has_work() const { return !waiting_.empty() || !running_.empty(); }
+    int schedule()
+    {
+        if (active_)
+            return fail(SC_BATCH_IN_FLIGHT, "a batch is in flight");
+        if (!has_work())
+            return fail(SC_NO_RUNNABLE_SEQUENCES, "nothing to run");
+        items_.clear();
+        int used = 0;
+        auto full = [&] { return static_cast<int>(items_.size()) >= max_sequences_ || used >= max_batch_tokens_; };
+        auto take = [&](long long id, Seq& s, int count) -> int {
+            const int st = cache_->reserve(id, s.processed + count);
+            if (st < 0)
+                return fail(st == RT_CAPACITY_EXHAUSTED ? SC_CACHE_CAPACITY_EXHAUSTED : SC_BLOCK_MANAGER_FAILURE,
+                            g_error);
+            items_.push_back({ id, s.processed, count, count == s.schedulable() ? 1 : 0 });
+            s.scheduled = count;
+            used += count;
+            return 0;
+        };
+        int status = 0;
+        for (long long id : running_) {
+            if (full())
+                break;
+            Seq& s = seqs_.at(id);
+            if (s.schedulable() != 1) {
+                status = fail(SC_INVALID_SEQUENCE_STATE, "a running sequence has " + str(s.schedulable())
+                                                             + " tokens to run");
+                break;
+            }
+            if ((status = take(id, s, 1)) < 0)
+                break;
+        }
+        if (status == 0) {
+            const bool contended = waiting_.size() > 1 || !running_.empty();
+            const int quantum = contended ? prefill_chunk_tokens_ : max_batch_tokens_;
+            for (long long id : waiting_) {
+                if (full())
+                    break;
+                Seq& s = seqs_.at(id);
+                const int available = s.schedulable();
+                if (available <= 0) {
+                    status = fail(SC_INVALID_SEQUENCE_STATE, "a waiting sequence has nothing to run");
+                    break;
+                }
+                const int count = std::min({ available, quantum, max_batch_tokens_ - used });
+                if ((status = take(id, s, count)) < 0)
+                    break;
+            }
+        }
+        if (status == 0 && items_.empty())
+            status = fail(SC_NO_RUNNABLE_SEQUENCES, "nothing to run");
+        if (status < 0) {
+            const std::string keep = g_error;
+            rollback();
+            g_error = keep;
+            return status;
+        }
+        active_ = true;
+        active_id_ = next_batch_++;
+        return static_cast<int>(items_.size());
+    }
+    // updates: (id, token, finish reason) per sampling item, in the order of the items
+    int complete(int batch_id, const int* sampled, int n_sampled, std::vector<long long>* updates)
+    {
+        if (!active_)
+            return fail(SC_NO_BATCH_IN_FLIGHT, "no batch is in flight");
+        if (batch_id != active_id_)
+            return fail(SC_BATCH_ID_MISMATCH, "another batch is in flight");
+        int samples = 0;
+        for (const Item& it : items_)
+            samples += it.sample;
+        if (n_sampled != samples)
+            return fail(SC_RESULT_COUNT_MISMATCH, str(n_sampled) + " samples for " + str(samples) + " sampling items");
+        int k = 0;
+        for (const Item& it : items_) {
+            Seq& s = seqs_.at(it.id);
+            s.processed += s.scheduled;
+            s.scheduled = 0;
+            const bool was_waiting = s.status == ST_WAITING;
+            std::deque<long long>& q = was_waiting ? waiting_ : running_;
+            q.erase(std::find(q.begin(), q.end(), it.id));
+            if (!it.sample) {
+                waiting_.push_back(it.id);
+                continue;
+            }
+            if (was_waiting)
+                s.status = ST_RUNNING;
+            s.tokens.push_back(sampled[k++]);
+            int reason = FR_NONE;
+            if (!s.ignore_eos && eos_ >= 0 && s.tokens.back() == eos_)
+                reason = FR_EOS;
+            else if (s.completion_len() >= s.max_new_tokens)
+                reason = FR_LEN_LIMIT;
+            if (reason != FR_NONE) {
+                s.status = ST_FINISHED;
+                s.reason = reason;
+            } else {
+                running_.push_back(it.id);
+            }
+            updates->push_back(it.id);
+            updates->push_back(s.tokens.back());
+            updates->push_back(reason);
+        }
+        active_ = false;
+        items_.clear();
+        return static_cast<int>(updates->size() / 3);
+    }
+    int abort(int batch_id)
+    {
+        if (!active_)
+            return fail(SC_NO_BATCH_IN_FLIGHT, "no batch is in flight");
+        if (batch_id != active_id_)
+            return fail(SC_BATCH_ID_MISMATCH, "another batch is in flight");
+        rollback();
+        return 0;
+    }
+    // 1: the sequence was live and is now finished (its caller releases its cache); 0: it had finished
+    int cancel(long long id)
+    {
+        if (active_)
+            return fail(SC_BATCH_IN_FLIGHT, "a batch is in flight");
+        Seq* s = find(id);
+        if (!s)
+            return fail(SC_UNKNOWN_SEQUENCE, "no such sequence");
+        if (s->status == ST_FINISHED)
+            return 0;
+        for (auto* q : { &waiting_, &running_ }) {
+            auto it = std::find(q->begin(), q->end(), id);
+            if (it != q->end())
+                q->erase(it);
+        }
+        s->status = ST_FINISHED;
+        s->reason = FR_CANCELLED;
+        s->scheduled = 0;
+        return 1;
+    }
+    int remove(long long id)
+    {
+        Seq* s = find(id);
+        if (!s)
+            return fail(SC_UNKNOWN_SEQUENCE, "no such sequence");
+        if (s->status != ST_FINISHED)
+            return fail(SC_SEQUENCE_NOT_FINISHED, "the sequence has not finished");
+        seqs_.erase(id);
+        return 0;
+    }
+    int check() const
+    {
+        std::unordered_set<long long> live;
+        for (const auto* q : { &waiting_, &running_ })
+            for (long long id : *q)
+                if (!live.insert(id).second)
+                    return fail(RT_INVARIANT, "a sequence is queued twice");
+        for (const auto& kv : seqs_) {
+            const Seq& s = kv.second;
+            if (s.processed < 0 || s.scheduled < 0 || s.processed + s.scheduled > static_cast<int>(s.tokens.size()))
+                return fail(RT_INVARIANT, "a sequence's counters are out of order");
+            const bool in_waiting = std::find(waiting_.begin(), waiting_.end(), kv.first) != waiting_.end();
+            const bool in_running = std::find(running_.begin(), running_.end(), kv.first) != running_.end();
+            if (s.status == ST_WAITING && !in_waiting)
+                return fail(RT_INVARIANT, "a waiting sequence is not in the waiting queue");
+            if (s.status == ST_RUNNING && (!in_running || s.schedulable() + s.scheduled != 1))
+                return fail(RT_INVARIANT, "a running sequence is not in the running queue with one token to run");
+            if (s.status == ST_FINISHED && (in_waiting || in_running))
+                return fail(RT_INVARIANT, "a finished sequence is still queued");
+        }
+        return 0;
+    }
+
+private:
+    void rollback()
+    {
+        for (const Item& it : items_)
+            seqs_.at(it.id).scheduled = 0;
+        items_.clear();
+        active_ = false;
+    }
+    CacheManager* cache_;
+    int max_sequences_, max_batch_tokens_, prefill_chunk_tokens_, eos_;
+    std::unordered_map<long long, Seq> seqs_;
+    std::deque<long long> waiting_, running_;
+    bool active_ = false;
+    int active_id_ = -1, next_batch_ = 0;
+    std::vector<Item> items_;
+};
+
+} // namespace
+
+// eos < 0: the model has no end-of-sequence token
+RT_API void* chibi_sched_new(void* cache, int max_sequences, int max_batch_tokens, int prefill_chunk_tokens, int eos)
+{
+    if (!cache || max_sequences <= 0 || max_batch_tokens <= 0 || prefill_chunk_tokens <= 0) {
+        fail(SC_INVALID_CONFIGURATION, "max_sequences, max_batch_tokens and prefill_chunk_tokens must be positive");
+        return nullptr;
+    }
+    return new Scheduler(static_cast<CacheManager*>(cache), max_sequences, max_batch_tokens, prefill_chunk_tokens, eos);
+}
+RT_API void chibi_sched_delete(void* s) { delete static_cast<Scheduler*>(s); }
+RT_API int chibi_sched_fits_cache(void* s, int prompt_len, int max_new_tokens)
+{
+    return static_cast<Scheduler*>(s)->fits_cache(prompt_len, max_new_tokens) ? 1 : 0;
+}
+// 0 admitted, 1 deferred, 2 too large
+RT_API int chibi_sched_admission(void* s, int prompt_len, int max_new_tokens)
+{
+    return static_cast<Scheduler*>(s)->admission(prompt_len, max_new_tokens);
+}
+RT_API int chibi_sched_add(void* s, long long id, const int* prompt, int prompt_len, int max_new_tokens,
+                           int ignore_eos)
+{
+    return static_cast<Scheduler*>(s)->add(id, prompt, prompt_len, max_new_tokens, ignore_eos != 0);
+}
+RT_API int chibi_sched_has_work(void* s) { return static_cast<Scheduler*>(s)->has_work() ? 1 : 0; }
+RT_API int chibi_sched_active(void* s) { return static_cast<Scheduler*>(s)->active() ? 1 : 0; }
+// items: (id, first, count, sample) per item; returns their number
+RT_API int chibi_sched_schedule(void* s, long long* items, int capacity_items, int* batch_id)
+{
+    Scheduler* sc = static_cast<Scheduler*>(s);
+    const int n = sc->schedule();
+    if (n < 0)
+        return n;
+    if (n > capacity_items) {
+        sc->abort(sc->active_id());
+        return fail(RT_BUFFER_TOO_SMALL, "more items than the caller has room for");
+    }
+    const std::vector<Item>& its = sc->active_items();
+    for (int i = 0; i < n; ++i) {
+        items[4 * i] = its[i].id;
+        items[4 * i + 1] = its[i].first;
+        items[4 * i + 2] = its[i].count;
+        items[4 * i + 3] = its[i].sample;
+    }
+    *batch_id = sc->active_id();
+    return n;
+}
+// updates: (id, token, finish reason: 0 none, 1 eos, 2 len_limit) per sampling item
+RT_API int chibi_sched_complete(void* s, int batch_id, const int* sampled, int n_sampled, long long* updates,
+                                int capacity_updates)
+{
+    std::vector<long long> out;
+    const int n = static_cast<Scheduler*>(s)->complete(batch_id, sampled, n_sampled, &out);
+    if (n < 0)
+        return n;
+    if (n > capacity_updates)
+        return fail(RT_BUFFER_TOO_SMALL, "more updates than the caller has room for");
+    std::copy(out.begin(), out.end(), updates);
+    return n;
+}
+RT_API int chibi_sched_abort(void* s, int batch_id) { return static_cast<Scheduler*>(s)->abort(batch_id); }
+RT_API int chibi_sched_cancel(void* s, long long id) { return static_cast<Scheduler*>(s)->cancel(id); }
+RT_API int chibi_sched_remove(void* s, long long id) { return static_cast<Scheduler*>(s)->remove(id); }
+// out: processed, scheduled, status (0 waiting, 1 running, 2 finished), finish reason, tokens, prompt tokens
+RT_API int chibi_sched_info(void* s, long long id, int* out)
+{
+    const Seq* q = static_cast<Scheduler*>(s)->find(id);
+    if (!q)
+        return fail(SC_UNKNOWN_SEQUENCE, "no such sequence");
+    out[0] = q->processed;
+    out[1] = q->scheduled;
+    out[2] = q->status;
+    out[3] = q->reason;
+    out[4] = static_cast<int>(q->tokens.size());
+    out[5] = q->prompt_len;
+    return 0;
+}
+// tokens [first, first + count) of a sequence
+RT_API int chibi_sched_tokens(void* s, long long id, int first, int count, int* out)
+{
+    const Seq* q = static_cast<Scheduler*>(s)->find(id);
+    if (!q)
+        return fail(SC_UNKNOWN_SEQUENCE, "no such sequence");
+    if (first < 0 || count < 0 || first + count > static_cast<int>(q->tokens.size()))
+        return fail(SC_INVALID_SEQUENCE_STATE, "tokens outside the sequence");
+    std::copy(q->tokens.begin() + first, q->tokens.begin() + first + count, out);
+    return count;
+}
+// which: 0 waiting, 1 running; returns the queue's length (which may exceed `capacity`)
+RT_API int chibi_sched_queue(void* s, int which, long long* out, int capacity)
+{
+    const std::deque<long long>& q = static_cast<Scheduler*>(s)->queue(which);
+    int i = 0;
+    for (long long id : q) {
+        if (i < capacity)
+            out[i] = id;
+        ++i;
+    }
+    return i;
+}
+RT_API int chibi_sched_check(void* s) { return static_cast<Scheduler*>(s)->check(); }

@@ -129,7 +129,7 @@ class InferenceEngine:
             entries = []
             for item in batch.items:
                 seq = sched.sequences[item.seq_id]
-                toks = seq.tokens[item.first:item.first + item.count]
+                toks = seq.slice(item.first, item.count)
                 entries.append(StepEntry(item.seq_id, toks, [item.count - 1] if item.sample else []))
             kernels = self.runner.runtime.kernels
             deferred_check = hasattr(kernels, "error_word_async")

@@ -27,24 +27,44 @@ Changed: the reference runs prefill batches and decode rounds in turns
 (src/scheduler.cc:250-258,415-423).  Here every step takes one token of every
 running sequence first and fills what is left of the budget with prompt
 portions, in one mixed batch.
+
+The queues, the counters and the decisions are C++ (``csrc/runtime.cc``); the
+classes here hold a handle, keep the sampling parameters and the request ids (any
+hashable), and admit to and release from the cache when the C++ side says so.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
-from ..cache.manager import CacheError, CacheManager, pages_for
+from ..cache import native
+from ..cache.manager import CacheError, CacheManager
 from ..sampling.sampler import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 ADMITTED, DEFERRED, TOO_LARGE = "admitted", "deferred", "too_large"
+
+_STATUS = (WAITING, RUNNING, FINISHED)
+_REASONS = (None, "eos", "len_limit", "cancelled")
+_ADMISSION = (ADMITTED, DEFERRED, TOO_LARGE)
+_ERRORS = {-20: "batch_in_flight", -21: "duplicate_sequence_id", -22: "invalid_sequence_state",
+           -23: "no_runnable_sequences", -24: "cache_capacity_exhausted", -25: "block_manager_failure",
+           -26: "no_batch_in_flight", -27: "batch_id_mismatch", -28: "result_count_mismatch",
+           -29: "unknown_sequence", -30: "sequence_not_finished", -31: "invalid_configuration"}
 
 
 class SchedulerError(RuntimeError):
     def __init__(self, code: str, message: str = ""):
         super().__init__(f"{code}: {message}" if message else code)
         self.code = code
+
+
+def _raise(status: int) -> None:
+    message = native.error_message()
+    if native.ERROR_CODES.get(status) == "invariant":
+        raise AssertionError(message)
+    raise SchedulerError(_ERRORS.get(status, native.ERROR_CODES.get(status, f"status {status}")), message)
 
 
 @dataclass
@@ -63,7 +83,9 @@ class SchedulerConfig:
 
 class Sequence:
     """Token list with the counters processed <= processed + scheduled <= tokens
-    (src/seq.cc:305-323)."""
+    (src/seq.cc:305-323).  Until a scheduler takes it, and again once it has been
+    removed from one, the object holds its own values; in between they are read
+    from the scheduler."""
 
     def __init__(self, seq_id: Hashable, prompt: Sequence[int], params: SamplingParams):
         if len(prompt) == 0:
@@ -71,38 +93,76 @@ class Sequence:
         if params.max_new_tokens <= 0:
             raise SchedulerError("seq.invalid_max_new_tokens")
         self.id = seq_id
-        self.tokens: List[int] = [int(t) for t in prompt]
-        self.prompt_len = len(self.tokens)
+        self.prompt_len = len(prompt)
         self.params = params
-        self.processed = 0
-        self.scheduled = 0
-        self.status = WAITING
-        self.finish_reason: Optional[str] = None
+        self._owner: Optional["Scheduler"] = None
+        self._number = -1
+        self._tokens: List[int] = [int(t) for t in prompt]
+        self._state = (0, 0, WAITING, None)         # processed, scheduled, status, finish reason
+
+    # ---- values that the scheduler owns while it has the sequence
+    def _info(self):
+        return self._owner._info(self._number) if self._owner is not None else None
+
+    @property
+    def tokens(self) -> List[int]:
+        if self._owner is None:
+            return self._tokens
+        return self._owner._tokens(self._number, 0, self._info()[4])
+
+    def slice(self, first: int, count: int) -> List[int]:
+        """tokens[first : first + count] without fetching the rest."""
+        if self._owner is None:
+            return self._tokens[first:first + count]
+        return self._owner._tokens(self._number, first, count)
+
+    @property
+    def processed(self) -> int:
+        info = self._info()
+        return info[0] if info else self._state[0]
+
+    @property
+    def scheduled(self) -> int:
+        info = self._info()
+        return info[1] if info else self._state[1]
+
+    @property
+    def status(self) -> str:
+        info = self._info()
+        return _STATUS[info[2]] if info else self._state[2]
+
+    @property
+    def finish_reason(self) -> Optional[str]:
+        info = self._info()
+        return _REASONS[info[3]] if info else self._state[3]
+
+    @property
+    def length(self) -> int:
+        info = self._info()
+        return info[4] if info else len(self._tokens)
 
     @property
     def completion_len(self) -> int:
-        return len(self.tokens) - self.prompt_len
+        return self.length - self.prompt_len
 
     @property
     def completion(self) -> List[int]:
-        return self.tokens[self.prompt_len:]
+        return self.slice(self.prompt_len, self.completion_len)
 
     @property
     def schedulable(self) -> int:
-        return len(self.tokens) - self.processed - self.scheduled
+        return self.length - self.processed - self.scheduled
 
     @property
     def is_finished(self) -> bool:
         return self.status == FINISHED
 
-    def evaluate_stop(self, eos: Optional[int]) -> Optional[str]:
-        if self.completion_len == 0:
-            return None
-        if not self.params.ignore_eos and eos is not None and self.tokens[-1] == eos:
-            return "eos"
-        if self.completion_len >= self.params.max_new_tokens:
-            return "len_limit"
-        return None
+    def _detach(self) -> None:
+        """Take the values over from the scheduler that is about to forget the sequence."""
+        info = self._info()
+        self._tokens = self._owner._tokens(self._number, 0, info[4])
+        self._state = (info[0], info[1], _STATUS[info[2]], _REASONS[info[3]])
+        self._owner = None
 
 
 @dataclass
@@ -142,51 +202,87 @@ class Scheduler:
         self.cache = cache
         self.eos_token = eos_token
         self.sequences: Dict[Hashable, Sequence] = {}
-        self.waiting: Deque[Hashable] = deque()
-        self.running: Deque[Hashable] = deque()
         self.active: Optional[ScheduledBatch] = None
-        self._next_batch = 0
         self._on_admit = on_admit or cache.admit
         self._on_release = on_release or cache.release
+        self._lib = native.runtime()
+        self._handle = self._lib.chibi_sched_new(cache.handle, config.max_sequences, config.max_batch_tokens,
+                                                 config.prefill_chunk_tokens,
+                                                 -1 if eos_token is None else int(eos_token))
+        if not self._handle:
+            raise SchedulerError("invalid_configuration", native.error_message())
+        self._ids: Dict[int, Hashable] = {}        # the C++ side's number -> request id
+        self._info_buf = (ctypes.c_int * 6)()
+        self._items_buf = (ctypes.c_longlong * (4 * config.max_sequences))()
+        self._updates_buf = (ctypes.c_longlong * (3 * config.max_sequences))()
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.chibi_sched_delete(self._handle)
+            self._handle = None
+
+    # ---- what sequences read
+    def _info(self, number: int):
+        status = self._lib.chibi_sched_info(self._handle, number, self._info_buf)
+        if status < 0:
+            _raise(status)
+        return tuple(self._info_buf)
+
+    def _tokens(self, number: int, first: int, count: int) -> List[int]:
+        out = (ctypes.c_int * max(count, 1))()
+        status = self._lib.chibi_sched_tokens(self._handle, number, first, count, out)
+        if status < 0:
+            _raise(status)
+        return list(out[:count])
+
+    def _queue(self, which: int) -> List[Hashable]:
+        n = self._lib.chibi_sched_queue(self._handle, which, None, 0)
+        out = (ctypes.c_longlong * max(n, 1))()
+        self._lib.chibi_sched_queue(self._handle, which, out, n)
+        return [self._ids[out[i]] for i in range(n)]
+
+    @property
+    def waiting(self) -> List[Hashable]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Hashable]:
+        return self._queue(1)
 
     # ---- budget
-    def _budget_tokens(self, seq: Sequence) -> int:
-        return seq.prompt_len + seq.params.max_new_tokens - 1
-
-    def _budget_pages(self, seq: Sequence) -> Dict[str, int]:
-        return {name: self.cache.worst_case_pages(name, self._budget_tokens(seq)) for name in self.cache.groups}
-
     def fits_cache(self, seq: Sequence) -> bool:
-        need = self._budget_pages(seq)
-        return all(need[name] <= g.num_pages for name, g in self.cache.groups.items())
+        return bool(self._lib.chibi_sched_fits_cache(self._handle, seq.prompt_len, seq.params.max_new_tokens))
 
     # ---- admission
     def try_add(self, seq: Sequence) -> str:
-        if self.active is not None:
-            raise SchedulerError("batch_in_flight")
         if seq.id in self.sequences:
+            if self.active is not None:
+                raise SchedulerError("batch_in_flight")
             raise SchedulerError("duplicate_sequence_id", repr(seq.id))
-        if seq.status != WAITING or seq.processed or seq.scheduled or len(seq.tokens) != seq.prompt_len:
+        if seq._owner is not None or seq.status != WAITING or seq.processed or seq.scheduled \
+                or seq.length != seq.prompt_len:
             raise SchedulerError("invalid_sequence_state", repr(seq.id))
-        if not self.fits_cache(seq):
-            return TOO_LARGE
-        if len(self.waiting) + len(self.running) >= self.config.max_sequences:
-            return DEFERRED
-        need = self._budget_pages(seq)
-        for name, g in self.cache.groups.items():
-            available = g.num_pages
-            for sid in list(self.waiting) + list(self.running):
-                available -= self._budget_pages(self.sequences[sid])[name]
-            if need[name] > available:
-                return DEFERRED
+        decision = self._lib.chibi_sched_admission(self._handle, seq.prompt_len, seq.params.max_new_tokens)
+        if decision < 0:
+            _raise(decision)
+        if decision != 0:
+            return _ADMISSION[decision]
         try:
             self._on_admit(seq.id)
             self.cache.reserve(seq.id, 1)
         except CacheError as e:
             self._on_release(seq.id)
             raise SchedulerError("block_manager_failure", str(e)) from None
+        number = self.cache.number_of(seq.id)
+        prompt = (ctypes.c_int * seq.prompt_len)(*seq._tokens)
+        status = self._lib.chibi_sched_add(self._handle, number, prompt, seq.prompt_len,
+                                           seq.params.max_new_tokens, 1 if seq.params.ignore_eos else 0)
+        if status < 0:
+            self._on_release(seq.id)
+            _raise(status)
+        seq._owner, seq._number = self, number
+        self._ids[number] = seq.id
         self.sequences[seq.id] = seq
-        self.waiting.append(seq.id)
         return ADMITTED
 
     def add(self, seq: Sequence) -> None:
@@ -198,123 +294,55 @@ class Scheduler:
 
     # ---- one step
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.chibi_sched_has_work(self._handle))
 
     def schedule(self) -> ScheduledBatch:
-        if self.active is not None:
-            raise SchedulerError("batch_in_flight")
-        if not self.has_work():
-            raise SchedulerError("no_runnable_sequences")
-        cfg = self.config
-        batch = ScheduledBatch(self._next_batch)
-        used = 0
-        try:
-            for sid in self.running:
-                if len(batch.items) >= cfg.max_sequences or used >= cfg.max_batch_tokens:
-                    break
-                seq = self.sequences[sid]
-                if seq.schedulable != 1:
-                    raise SchedulerError("invalid_sequence_state", f"running sequence {sid!r} has "
-                                         f"{seq.schedulable} tokens to run")
-                self._reserve(seq, 1)
-                batch.items.append(ScheduledItem(sid, seq.processed, 1, True))
-                seq.scheduled = 1
-                used += 1
-            contended = len(self.waiting) > 1 or bool(self.running)
-            quantum = cfg.prefill_chunk_tokens if contended else cfg.max_batch_tokens
-            for sid in self.waiting:
-                if len(batch.items) >= cfg.max_sequences or used >= cfg.max_batch_tokens:
-                    break
-                seq = self.sequences[sid]
-                available = seq.schedulable
-                if available <= 0:
-                    raise SchedulerError("invalid_sequence_state", f"waiting sequence {sid!r} has nothing to run")
-                count = min(available, quantum, cfg.max_batch_tokens - used)
-                self._reserve(seq, count)
-                batch.items.append(ScheduledItem(sid, seq.processed, count, count == available))
-                seq.scheduled = count
-                used += count
-        except SchedulerError:
-            self._rollback(batch)
-            raise
-        if not batch.items:
-            raise SchedulerError("no_runnable_sequences")
+        batch_id = ctypes.c_int()
+        n = self._lib.chibi_sched_schedule(self._handle, self._items_buf, self.config.max_sequences,
+                                           ctypes.byref(batch_id))
+        if n < 0:
+            _raise(n)
+        b = self._items_buf
+        batch = ScheduledBatch(batch_id.value, [
+            ScheduledItem(self._ids[b[4 * i]], b[4 * i + 1], b[4 * i + 2], bool(b[4 * i + 3])) for i in range(n)])
         self.active = batch
-        self._next_batch += 1
         return batch
 
-    def _reserve(self, seq: Sequence, count: int) -> None:
-        try:
-            self.cache.reserve(seq.id, seq.processed + count)
-        except CacheError as e:
-            if e.code == "capacity_exhausted":
-                raise SchedulerError("cache_capacity_exhausted", str(e)) from None
-            raise SchedulerError("block_manager_failure", str(e)) from None
-
-    def _rollback(self, batch: ScheduledBatch) -> None:
-        for item in batch.items:
-            self.sequences[item.seq_id].scheduled = 0
-
     def complete(self, batch_id: int, sampled: Sequence[int]) -> List[SequenceUpdate]:
-        if self.active is None:
-            raise SchedulerError("no_batch_in_flight")
-        batch = self.active
-        if batch_id != batch.batch_id:
-            raise SchedulerError("batch_id_mismatch")
-        if len(sampled) != batch.sample_count:
-            raise SchedulerError("result_count_mismatch",
-                                 f"{len(sampled)} samples for {batch.sample_count} sampling items")
+        values = (ctypes.c_int * max(len(sampled), 1))(*[int(t) for t in sampled])
+        n = self._lib.chibi_sched_complete(self._handle, int(batch_id), values, len(sampled), self._updates_buf,
+                                           self.config.max_sequences)
+        if n < 0:
+            _raise(n)
         updates: List[SequenceUpdate] = []
-        k = 0
-        for item in batch.items:
-            seq = self.sequences[item.seq_id]
-            seq.processed += seq.scheduled
-            seq.scheduled = 0
-            was_waiting = seq.status == WAITING
-            (self.waiting if was_waiting else self.running).remove(item.seq_id)
-            if not item.sample:
-                self.waiting.append(item.seq_id)
-                continue
-            if was_waiting:
-                seq.status = RUNNING
-            seq.tokens.append(int(sampled[k]))
-            k += 1
-            reason = seq.evaluate_stop(self.eos_token)
+        for i in range(n):
+            seq_id = self._ids[self._updates_buf[3 * i]]
+            reason = _REASONS[self._updates_buf[3 * i + 2]]
             if reason is not None:
-                seq.status = FINISHED
-                seq.finish_reason = reason
-                self._on_release(item.seq_id)
-            else:
-                self.running.append(item.seq_id)
-            updates.append(SequenceUpdate(item.seq_id, seq.tokens[-1], reason))
+                self._on_release(seq_id)
+            updates.append(SequenceUpdate(seq_id, int(self._updates_buf[3 * i + 1]), reason))
         self.active = None
         return updates
 
     def abort(self, batch_id: int) -> None:
         """Undo the token reservations of the batch in flight; pages stay, so a
         retry schedules the same batch (src/scheduler.cc:431-452)."""
-        if self.active is None:
-            raise SchedulerError("no_batch_in_flight")
-        if batch_id != self.active.batch_id:
-            raise SchedulerError("batch_id_mismatch")
-        self._rollback(self.active)
+        status = self._lib.chibi_sched_abort(self._handle, int(batch_id))
+        if status < 0:
+            _raise(status)
         self.active = None
 
     def cancel(self, seq_id: Hashable) -> None:
-        if self.active is not None:
-            raise SchedulerError("batch_in_flight")
         seq = self.sequences.get(seq_id)
         if seq is None:
+            if self.active is not None:
+                raise SchedulerError("batch_in_flight")
             raise SchedulerError("unknown_sequence", repr(seq_id))
-        if seq.is_finished:
-            return
-        for q in (self.waiting, self.running):
-            if seq_id in q:
-                q.remove(seq_id)
-        seq.status = FINISHED
-        seq.finish_reason = "cancelled"
-        seq.scheduled = 0
-        self._on_release(seq_id)
+        status = self._lib.chibi_sched_cancel(self._handle, seq._number)
+        if status < 0:
+            _raise(status)
+        if status == 1:
+            self._on_release(seq_id)
 
     def remove(self, seq_id: Hashable) -> Sequence:
         seq = self.sequences.get(seq_id)
@@ -322,16 +350,15 @@ class Scheduler:
             raise SchedulerError("unknown_sequence", repr(seq_id))
         if not seq.is_finished:
             raise SchedulerError("sequence_not_finished", repr(seq_id))
+        seq_number = seq._number
+        seq._detach()
+        status = self._lib.chibi_sched_remove(self._handle, seq_number)
+        if status < 0:
+            _raise(status)
+        self._ids.pop(seq_number, None)
         return self.sequences.pop(seq_id)
 
     def check_invariants(self) -> None:
-        live = list(self.waiting) + list(self.running)
-        assert len(live) == len(set(live)), "a sequence is queued twice"
-        for sid, seq in self.sequences.items():
-            assert 0 <= seq.processed <= seq.processed + seq.scheduled <= len(seq.tokens)
-            if seq.status == WAITING:
-                assert sid in self.waiting
-            elif seq.status == RUNNING:
-                assert sid in self.running and seq.schedulable + seq.scheduled == 1
-            else:
-                assert sid not in live
+        status = self._lib.chibi_sched_check(self._handle)
+        if status < 0:
+            _raise(status)
