@@ -163,7 +163,8 @@ HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-
 
 
 def find_cxx() -> str:
-    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++", "/usr/bin/g++", "/opt/gcc/bin/g++",
+                 "/usr/local/bin/g++"):
         path = shutil.which(cand) if cand else None
         if path:
             return path
