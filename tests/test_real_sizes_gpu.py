@@ -98,3 +98,48 @@ def test_long_context_decode():
         del runner
         torch.cuda.empty_cache()
     helpers.assert_logits_close(outs["bfloat16"], outs["float32"], helpers.TOL["bfloat16"], "long context decode")
+
+
+def test_long_prompt_takes_the_many_row_kernels():
+    """A prompt of 1,600 tokens at the 8B layer sizes (one layer), whole and in two
+    portions of which the second continues the first: the prompt attention with two
+    query tiles per CTA, the per-token norm + rotation kernel and the persistent
+    matrix product, against the 32-bit engine; then generation with and without
+    steps that run ahead gives the same tokens."""
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = dict(SHAPES["8B"], num_hidden_layers=1)
+    ids = helpers.random_requests(cfg["vocab_size"], [1600], seed=12)["r0"]
+    want = [0, 511, 1100, 1599]
+    outs = {}
+    for dtype, cuts in (("float32", [1600]), ("bfloat16", [1600]), ("bfloat16", [900, 700])):
+        runner = ModelRunner.from_random(cfg, seed=8, dtype=dtype, page_size=16, pool_tokens=2048, max_requests=2)
+        rows, fed = {}, 0
+        for n in cuts:
+            places = [w - fed for w in want if fed <= w < fed + n]
+            logits = runner.step([StepEntry("a", ids[fed:fed + n], places)])
+            for k, w in enumerate(places):
+                rows[fed + w] = logits[k].float().cpu().clone()
+            fed += n
+        outs[(dtype, len(cuts))] = {"a": torch.stack([rows[w] for w in want])}
+        del runner
+        torch.cuda.empty_cache()
+    ref = outs[("float32", 1)]
+    helpers.assert_logits_close(outs[("bfloat16", 1)], ref, helpers.TOL["bfloat16"], "long prompt, whole")
+    helpers.assert_logits_close(outs[("bfloat16", 2)], ref, helpers.TOL["bfloat16"], "long prompt, two portions")
+    helpers.assert_logits_close(outs[("bfloat16", 2)], outs[("bfloat16", 1)], helpers.TOL_SAME_DTYPE["bfloat16"],
+                                "long prompt, portions vs whole")
+
+    import chibillm_b200
+    from chibillm_b200.sampling import SamplingParams
+    tokens = {}
+    for ahead in (False, True):
+        llm = chibillm_b200.LLM(None, random_config=cfg, dtype="bfloat16", context_length=2048,
+                                kv_cache_tokens=4096, max_sequences=2)
+        llm.engine.run_ahead = ahead
+        tokens[ahead] = llm.engine.generate([ids[:1300], ids[300:900]],
+                                            [SamplingParams(max_new_tokens=24, ignore_eos=True)] * 2)
+        assert (llm.runner.steps_ahead_used > 0) == ahead
+        del llm
+        torch.cuda.empty_cache()
+    assert tokens[True] == tokens[False]
