@@ -238,6 +238,54 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
+// A row copied with a change of type, four features per thread and step (n a
+// multiple of 4, rows 16-byte aligned); a thread's loads all go out before its
+// stores.  Used by the embedding (row = table[token]) and the row gather.
+template <typename TX, typename TO>
+__device__ __forceinline__ void copy_row_vec4(const TX* __restrict__ src, TO* __restrict__ dst, int n, bool ok)
+{
+    const int n4 = n >> 2;
+    for (int j0 = threadIdx.x; j0 < n4; j0 += 4 * blockDim.x) {
+        float v[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * blockDim.x;
+            if (ok && j < n4)
+                Vec4<TX>::load(src + 4 * j, v[u]);
+            else
+                v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * blockDim.x;
+            if (j < n4)
+                Vec4<TO>::store(dst + 4 * j, v[u]);
+        }
+    }
+}
+
+template <typename TW, typename TO>
+__global__ void embed_vec4_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                  TO* __restrict__ out, int hidden, int vocab, int* __restrict__ error)
+{
+    pdl_enter();
+    const int id = tokens[blockIdx.x];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0 && error)
+        atomicExch(error, 1);
+    copy_row_vec4(table + (size_t)(ok ? id : 0) * hidden, out + (size_t)blockIdx.x * hidden, hidden, ok);
+}
+
+template <typename TX, typename TO>
+__global__ void gather_rows_vec4_kernel(const TX* __restrict__ x, const int* __restrict__ rows,
+                                        TO* __restrict__ out, int n, long long x_rows)
+{
+    pdl_enter();
+    const int r = rows[blockIdx.x];
+    const bool ok = r >= 0 && r < x_rows;
+    copy_row_vec4(x + (size_t)(ok ? r : 0) * n, out + (size_t)blockIdx.x * n, n, ok);
+}
+
 // JPW head jobs per warp.  Every launch uses 1 (as many warps as possible side by
 // side); more per warp measured slower, and many tokens with 128-feature heads
 // take the per-token kernel below.
@@ -593,9 +641,15 @@ CHIBI_API int chibi_embed(const int* tokens, const void* table, int table_type, 
     if (rows <= 0)
         return CHIBI_OK;
     const int block = hidden >= 1024 ? 256 : 128;
+    const bool vec = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     CHIBI_DISPATCH_TYPE(table_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        launch_ordered(embed_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream, 
-            tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
+        if (vec)
+            launch_ordered(embed_vec4_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream,
+                           tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
+        else
+            launch_ordered(embed_kernel<TW, TO>, dim3((unsigned)rows), dim3(block), 0, stream,
+                           tokens, (const TW*)table, (TO*)out, hidden, vocab, error);
     }));
     return launch_status();
 }
@@ -740,9 +794,15 @@ CHIBI_API int chibi_gather_rows(const void* x, int x_type, const int* rows, void
 {
     if (count <= 0)
         return CHIBI_OK;
+    const bool vec = n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
-        launch(gather_rows_kernel<TX, TO>, dim3((unsigned)count), dim3(256), 0, stream, 
-            (const TX*)x, rows, (TO*)out, n, x_rows);
+        if (vec)
+            launch(gather_rows_vec4_kernel<TX, TO>, dim3((unsigned)count), dim3(256), 0, stream,
+                   (const TX*)x, rows, (TO*)out, n, x_rows);
+        else
+            launch(gather_rows_kernel<TX, TO>, dim3((unsigned)count), dim3(256), 0, stream,
+                   (const TX*)x, rows, (TO*)out, n, x_rows);
     }));
     return launch_status();
 }
