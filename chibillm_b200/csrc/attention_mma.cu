@@ -49,6 +49,19 @@ struct AttnParams {
     int splits;                    // decode: key ranges per sequence
     float* scratch_o;              // decode: [S, nq, splits, D]
     float* scratch_ml;             // decode: [S, nq, splits, 2]
+    // decode, optional: q (and the newest key and value) are not in `q` and the caches yet but
+    // still the partial sums of the q | k | v product: the kernel adds them up, applies the per-head
+    // norm and the rotation itself and appends the new key and value (head size 128 only)
+    __nv_bfloat16* k_cache_out;    // the caches again, to write to
+    __nv_bfloat16* v_cache_out;
+    const float* partial;          // [partial_splits][tokens][partial_width] or null
+    int partial_splits;
+    long long partial_split_stride, partial_width;
+    const __nv_bfloat16* q_norm_w; // [D] or null
+    const __nv_bfloat16* k_norm_w;
+    const float* inv_freq;         // [D / 2]
+    float norm_eps, norm_offset;
+    int append;                    // write the new key and value (0: the layer reads another layer's cache)
     int skip_single;               // prefill: leave one-token sequences to the decode kernel
     int* error;
 };
@@ -279,6 +292,85 @@ constexpr size_t DEC_SMEM_PIPE = (size_t)(DEC_Q_ELEMS + DEC_WARPS * DEC_STAGES *
 constexpr size_t DEC_SMEM_MERGE = (size_t)DEC_WARPS * (16 * (D + 1) + 32) * 4;
 constexpr size_t DEC_SMEM = DEC_SMEM_PIPE > DEC_SMEM_MERGE ? DEC_SMEM_PIPE : DEC_SMEM_MERGE;
 
+// q of one (sequence, kv head) from the partial sums of the q | k | v product, for head
+// size 128 and 128 threads (thread j owns feature j of every head): sum over the splits in
+// split order, RMSNorm per head (if a weight is given), split-half rotation with the
+// token's cosines and sines `cs` ([0, 64) cosines, [64, 128) sines), bfloat16 into the
+// q tile.  With `with_kv` the same for the new key, and the new value as it is, written
+// to the cache slot at `cache_base`.  xs: [8][128] floats, red: [4][8] floats.
+__device__ __forceinline__ void build_q_from_partial(const AttnParams& p, int t, int kv_head, int head0, int rows,
+                                                     bool with_kv, long long cache_base,
+                                                     __nv_bfloat16* q_tile, const float* cs, float (*xs)[128],
+                                                     float (*red)[8])
+{
+    const int j = threadIdx.x, warp = j >> 5, lane = j & 31;
+    const int heads = rows + (with_kv ? 2 : 0);              // at most 8
+    long long col[8];
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+        int head = head0 + h;                                 // a query head
+        if (h == rows)
+            head = p.nq + kv_head;                            // the key head
+        else if (h == rows + 1)
+            head = p.nq + p.nkv + kv_head;                    // the value head
+        col[h] = (long long)t * p.partial_width + (long long)head * 128 + j;
+    }
+    float acc[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+    for (int s0 = 0; s0 < p.partial_splits; s0 += 8) {        // 64 loads in flight
+        float q[8][8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                q[h][u] = (h < heads && s0 + u < p.partial_splits)
+                    ? p.partial[(long long)(s0 + u) * p.partial_split_stride + col[h]] : 0.f;
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                acc[h] += q[h][u];
+    }
+    // per-head sums of squares (the value head is not normalised)
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+        const float ss = warp_sum(acc[h] * acc[h]);
+        if (lane == 0)
+            red[warp][h] = ss;
+    }
+    __syncthreads();
+    const float wq = p.q_norm_w ? __bfloat162float(p.q_norm_w[j]) + p.norm_offset : 1.f;
+    const float wk = p.k_norm_w ? __bfloat162float(p.k_norm_w[j]) + p.norm_offset : 1.f;
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+        const bool is_q = h < rows, is_k = with_kv && h == rows;
+        if ((is_q && p.q_norm_w) || (is_k && p.k_norm_w)) {
+            const float total = (red[0][h] + red[1][h]) + (red[2][h] + red[3][h]);
+            const float inv = rsqrtf(total / 128.f + p.norm_eps);
+            acc[h] = (acc[h] * inv) * (is_q ? wq : wk);
+        }
+        xs[h][j] = acc[h];
+    }
+    __syncthreads();
+    const float c = cs[j & 63], sn = cs[64 + (j & 63)];
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+        if (h < rows || (with_kv && h == rows)) {
+            const float partner = xs[h][j ^ 64];
+            const float out = j < 64 ? acc[h] * c - partner * sn : acc[h] * c + partner * sn;
+            if (h < rows)
+                q_tile[h * DPAD + j] = __float2bfloat16_rn(out);
+            else
+                p.k_cache_out[cache_base + j] = __float2bfloat16_rn(out);
+        } else if (with_kv && h == rows + 1) {
+            p.v_cache_out[cache_base + j] = __float2bfloat16_rn(acc[h]);
+        }
+    }
+    for (int r = rows; r < 16; ++r)                           // rows past the group are zero
+        q_tile[r * DPAD + j] = __float2bfloat16_rn(0.f);
+    if (with_kv)
+        __threadfence();                                      // the copies of the last tile read them back
+}
+
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p)
 {
     pdl_trigger();
@@ -318,6 +410,18 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     auto key0_of = [&](int i) { return first + (my_first_tile + i * DEC_WARPS) * DEC_TILE; };
     int page_ahead = my_tiles > 0 ? lookup_tile_page(table, p.page_size, key0_of(0), key_end, lane) : -1;
     bool waited = false;
+    [[maybe_unused]] const bool fused = D == 128 && p.partial != nullptr;
+    __shared__ float rope_cs[128];
+    __shared__ float head_x[8][128];
+    __shared__ float head_ss[DEC_WARPS][8];
+    if constexpr (D == 128) {
+        if (fused && threadIdx.x < 64) {                     // the token's cosines and sines, before the wait
+            float sn, cn;
+            sincosf((float)pos * p.inv_freq[threadIdx.x], &sn, &cn);
+            rope_cs[threadIdx.x] = cn;
+            rope_cs[64 + threadIdx.x] = sn;
+        }
+    }
     auto issue = [&](int i) {
         if (i < my_tiles) {
             if (!waited && key0_of(i) + DEC_TILE > pos) {        // the tile with the newest key
@@ -333,23 +437,55 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         }
         cp_async_commit();
     };
+    // The first stages of the pipeline; a stage that needs the newest key waits until that key
+    // is there (written by the kernel before this one, or, fused, by this CTA below).
+    int resume = DEC_STAGES - 1;
 #pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; ++i)
-        issue(i);
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+        if (fused && resume == DEC_STAGES - 1 && i < my_tiles && key0_of(i) + DEC_TILE > pos)
+            resume = i;
+        if (i < resume)
+            issue(i);
+    }
     if (!waited) {
         pdl_wait();
         waited = true;
     }
-
-    // query rows -> shared memory (rows past the group are zero)
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += blockDim.x) {
-        const int row = c / CHUNKS, col = c - row * CHUNKS;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < rows)
-            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nq + head0 + row) * D + col * 8);
-        *reinterpret_cast<uint4*>(q_tile + row * DPAD + col * 8) = v;
+    bool q_built = false;
+    if constexpr (D == 128) {
+        if (fused) {
+            const int last_tile = tiles_total - 1;               // holds the newest key
+            const bool with_kv = p.append && tile_begin <= last_tile && last_tile < tile_end;
+            long long cache_base = 0;
+            bool write_kv = with_kv;
+            if (with_kv) {
+                const int page = table[pos / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    if (threadIdx.x == 0 && p.error)
+                        atomicExch(p.error, 2);
+                    write_kv = false;
+                } else {
+                    cache_base = (((long long)page * p.nkv + kv_head) * p.page_size + pos % p.page_size) * D;
+                }
+            }
+            __syncthreads();                                     // the cosines and sines are there
+            build_q_from_partial(p, t, kv_head, head0, rows, write_kv, cache_base, q_tile, rope_cs, head_x, head_ss);
+            q_built = true;
+        }
+    }
+    if (!q_built) {
+        // query rows -> shared memory (rows past the group are zero)
+        for (int c = threadIdx.x; c < 16 * CHUNKS; c += blockDim.x) {
+            const int row = c / CHUNKS, col = c - row * CHUNKS;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < rows)
+                v = *reinterpret_cast<const uint4*>(p.q + ((size_t)t * p.nq + head0 + row) * D + col * 8);
+            *reinterpret_cast<uint4*>(q_tile + row * DPAD + col * 8) = v;
+        }
     }
     __syncthreads();
+    for (int i = resume; i < DEC_STAGES - 1; ++i)
+        issue(i);
     uint32_t qf[KSTEPS][4];
     if constexpr (Q_IN_REGS)
         load_q_frags(qf, q_tile, lane);
@@ -678,4 +814,84 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
         return launch_status();
     }
     return CHIBI_OK;
+}
+
+// The decode kernel on the partial sums of the q | k | v product (32-bit,
+// [partial_splits][tokens][partial_width]): every sequence brings one token; the kernel
+// adds the partial sums of its heads, applies the per-head RMSNorm (weights bfloat16 or
+// null) and the rotation, and the CTA whose key range holds the newest position writes
+// the new key and value to the caches (append != 0) before it reads them back.  Takes
+// head size 128 with at most 6 query heads per kv head and a rotation of the whole head;
+// returns CHIBI_ERR_UNSUPPORTED otherwise.
+CHIBI_API int chibi_attention_decode_fused(const float* partial, int partial_splits, long long partial_width,
+                                           long long tokens, void* k_cache, void* v_cache, void* out,
+                                           const int* block_table, int table_stride, const int* seq_rows,
+                                           const int* q_start, const int* ctx_len, int seqs, int nq, int nkv,
+                                           int page_size, int num_pages, float scale, int window, int splits,
+                                           float* scratch, long long scratch_floats, const void* q_norm_w,
+                                           const void* k_norm_w, const float* inv_freq, float eps, float offset,
+                                           int append, int* error, cudaStream_t stream)
+{
+    if (seqs <= 0)
+        return CHIBI_OK;
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1 || !partial || partial_splits < 1
+        || !inv_freq)
+        return CHIBI_ERR_ARGUMENT;
+    if (D != 128 || nq / nkv > 6 || partial_width < (long long)(append ? nq + 2 * nkv : nq) * D)
+        return CHIBI_ERR_UNSUPPORTED;
+    AttnParams p {};
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.k_cache_out = static_cast<__nv_bfloat16*>(k_cache);
+    p.v_cache_out = static_cast<__nv_bfloat16*>(v_cache);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.seq_rows = seq_rows;
+    p.q_start = q_start;
+    p.ctx_len = ctx_len;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.group = nq / nkv;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.splits = splits;
+    p.error = error;
+    p.skip_single = 1;
+    p.partial = partial;
+    p.partial_splits = partial_splits;
+    p.partial_split_stride = tokens * partial_width;
+    p.partial_width = partial_width;
+    p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w);
+    p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
+    p.inv_freq = inv_freq;
+    p.norm_eps = eps;
+    p.norm_offset = offset;
+    p.append = append;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)DEC_SMEM);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    if (splits > 1) {
+        const long long need = chibi_attention_mma_scratch_floats(seqs, nq, splits);
+        if (!scratch || scratch_floats < need)
+            return CHIBI_ERR_ARGUMENT;
+        p.scratch_o = scratch;
+        p.scratch_ml = scratch + (size_t)seqs * nq * splits * D;
+    }
+    launch(attn_decode_kernel, dim3(splits, nkv, seqs), dim3(DEC_WARPS * 32), DEC_SMEM, stream, p);
+    int st = launch_status();
+    if (st != CHIBI_OK)
+        return st;
+    if (splits > 1) {
+        launch(attn_decode_merge_kernel, dim3(dim3(nq, seqs)), dim3(D), 0, stream, p);
+        st = launch_status();
+    }
+    return st;
 }

@@ -45,6 +45,8 @@ _SIGNATURES = {
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
         "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, L, P, P],
+        "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P, L, P, P, P,
+                                         F, F, I, P, P],
     },
 }
 

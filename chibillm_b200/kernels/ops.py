@@ -505,6 +505,49 @@ class CudaKernels:
         self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
         _check(status, "attention (tensor cores)")
 
+    def attention_decode_from_partial(self, pending: PendingSum, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                      out: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
+                                      ctx_len: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                                      scale: float, window: Optional[int], max_ctx_len: int,
+                                      q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                                      inv_freq: torch.Tensor, rotary_dim: int, eps: float, norm_offset: float,
+                                      append: bool, seq_rows: Optional[torch.Tensor] = None) -> bool:
+        """Decode attention straight from the pending q | k | v product of a step in
+        which every sequence brings one token: the attention kernel adds the partial
+        sums, applies the per-head norm and the rotation and appends the new key and
+        value itself.  False if the kernel does not take these sizes (the caller then
+        runs ``qk_norm_rope_append_partial`` and ``attention``)."""
+        if not (self.use_tensor_cores and d == 128 and rotary_dim == d and nq // nkv <= 6
+                and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16):
+            return False
+        for w in (q_norm_w, k_norm_w):
+            if w is not None and w.dtype != torch.bfloat16:
+                return False
+        _need_cuda(k_cache, v_cache, out, block_table, q_start, ctx_len, seq_rows, q_norm_w, k_norm_w, inv_freq)
+        seqs = ctx_len.numel()
+        width = (nq + 2 * nkv) * d if append else nq * d
+        if pending.M != seqs or pending.N != width or out.shape != (seqs, nq * d) or not out.is_contiguous() \
+                or tuple(k_cache.shape[1:]) != (nkv, page_size, d) or not k_cache.is_contiguous() \
+                or not v_cache.is_contiguous():
+            raise KernelError("attention_decode_from_partial: shapes")
+        lib = self._attention_libs.get(d)
+        if lib is None:
+            lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
+            self._attention_libs[d] = lib
+        splits = self.decode_attention_splits(seqs, nq, nkv, max_ctx_len)
+        scratch = self._scratch(seqs * nq * splits * (d + 2)) if splits > 1 else None
+        status = lib.chibi_attention_decode_fused(
+            _ptr(pending.partial), pending.splits, width, seqs, _ptr(k_cache), _ptr(v_cache), _ptr(out),
+            _ptr(block_table), block_table.stride(0), _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv,
+            page_size, k_cache.shape[0], float(scale), int(window or 0), splits, _ptr(scratch),
+            scratch.numel() if scratch is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+            float(eps), float(norm_offset), 1 if append else 0, _ptr(self.error), self._stream())
+        if status == -2:
+            return False
+        _check(status, "attention (decode, from the partial sums)")
+        self.launches += 2 if splits > 1 else 1
+        return True
+
     def apply_table_updates(self, table: torch.Tensor, updates: torch.Tensor, capacity: int) -> None:
         """table[row][index] = page for the (row, index, page) triples that follow
         the count in ``updates`` (int32: [count, row, index, page, ...])."""

@@ -94,6 +94,15 @@ class PagedAttention(Mixer):
         norm = s.qk_norm
         q_norm_w = self.q_norm if norm is not None else None
         k_norm_w = self.k_norm if norm is not None else None
+        att = ctx.workspace.get("attn.out", (T, qw), rt.dtype)
+        from_partial = getattr(k, "attention_decode_from_partial", None)
+        if pending is not None and ctx.max_q_len == 1 and from_partial is not None and fused[0] is not None:
+            # every sequence brings one token: the attention kernel finishes the product itself
+            if from_partial(pending, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len, nq, nkv, d,
+                            cache.page_size, s.scale, s.window, ctx.max_ctx_len, q_norm_w, k_norm_w, fused[0],
+                            fused[1], norm.eps if norm is not None else 0.0,
+                            norm.weight_offset if norm is not None else 0.0, writes, ctx.seq_rows):
+                return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
         if fused is None:
             # An encoding the kernels do not know: normalise head by head in
             # place, let the encoding transform q and k, then only copy and append.
@@ -114,7 +123,6 @@ class PagedAttention(Mixer):
             norm.weight_offset if norm is not None else 0.0,
             ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size,
             ctx.seq_rows)
-        att = ctx.workspace.get("attn.out", (T, qw), rt.dtype)
         k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
                     s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows)

@@ -468,3 +468,45 @@ def test_attention_tcgen05_prompts(k, ref, nq, nkv, d, window, page):
         outs[(tc, variant)] = out
     k.use_tcgen05_attention = True
     k.tcgen05_attention_variant = 0
+
+
+@pytest.mark.parametrize("nq,nkv,window,append", [(32, 8, None, True), (8, 2, 100, True), (6, 1, None, True),
+                                                  (8, 2, None, False)])
+def test_decode_attention_from_partial_sums(k, nq, nkv, window, append):
+    """Decode attention that finishes the q | k | v product itself (sum of the
+    partial sums, per-head norm, rotation, append of the new key and value) against
+    the two kernels it replaces, on sequences that end at and next to page edges."""
+    d, page, K = 128, 16, 1024
+    seq_ctx = [1, 16, 17, 129, 300, 640, 33, 48]
+    S = len(seq_ctx)
+    pages = sum((c + page - 1) // page for c in seq_ctx) + 2
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, [1] * S, page, pages, seed=80)
+    x = rnd(S, K, dtype=torch.bfloat16, seed=81)
+    width = (nq + 2 * nkv) * d if append else nq * d
+    w = rnd(width, K, dtype=torch.bfloat16, seed=82, scale=0.05)
+    qn = (1 + 0.1 * rnd(d, seed=83)).to(torch.bfloat16)
+    kn = (1 + 0.1 * rnd(d, seed=84)).to(torch.bfloat16)
+    inv_freq = torch.pow(torch.tensor(1e6), -2 * torch.arange(d // 2, dtype=torch.float32) / d).cuda()
+    kc0 = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=85)
+    vc0 = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=86)
+    scale = 1.0 / math.sqrt(d)
+
+    kc, vc = kc0.clone(), vc0.clone()
+    pending = k.linear_partial(x, w)
+    assert pending is not None and pending.splits > 1
+    q = torch.empty(S, nq * d, dtype=torch.bfloat16, device="cuda")
+    k.qk_norm_rope_append_partial(pending, q, kc if append else None, vc if append else None, qn, kn, inv_freq, d,
+                                  1e-6, 0.0, positions, seq_of_token, table if append else None, nq, nkv, d, page)
+    exp = torch.empty(S, nq * d, dtype=torch.bfloat16, device="cuda")
+    k.attention(q, kc, vc, exp, table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, scale, window,
+                1, max(seq_ctx), 1)
+
+    kc2, vc2 = kc0.clone(), vc0.clone()
+    pending = k.linear_partial(x, w)
+    got = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert k.attention_decode_from_partial(pending, kc2, vc2, got, table, q_start, ctx_len, nq, nkv, d, page, scale,
+                                           window, max(seq_ctx), qn, kn, inv_freq, d, 1e-6, 0.0, append)
+    k.check_error_word()
+    close(got, exp, torch.bfloat16, "decode attention from the partial sums", rel=8e-3)
+    close(kc2, kc, torch.bfloat16, "key cache", rel=8e-3)
+    assert torch.equal(vc2, vc), "value cache"
