@@ -37,7 +37,14 @@ QWEN3_8B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
     "tie_word_embeddings": False, "use_sliding_window": False, "sliding_window": None,
 }
-FULL_LAYERS = 36
+# Other shapes of the same architecture (--shape); the default run and its record are the 8B shape.
+SHAPES = {
+    "qwen3-8b": {},
+    "qwen3-0.6b": {"num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16,
+                   "num_key_value_heads": 8, "intermediate_size": 3072, "tie_word_embeddings": True},
+    "qwen3-14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40,
+                  "num_key_value_heads": 8, "intermediate_size": 17408},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -245,7 +252,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+    ap.add_argument("--layers", type=int, default=None,
                     help="run only the first layers (each at full size); the JSON names both numbers")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=2048, help="tokens held when decoding starts")
@@ -254,6 +261,8 @@ def main() -> int:
     ap.add_argument("--point-steps", type=int, default=32)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),
+                    help="layer sizes (random weights); the contract's record is the default")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -272,7 +281,9 @@ def main() -> int:
     from chibillm_b200.sampling import Sampler
 
     cfg = dict(QWEN3_8B)
-    layers = min(args.layers, FULL_LAYERS)
+    cfg.update(SHAPES[args.shape])
+    full_layers = cfg["num_hidden_layers"]
+    layers = full_layers if args.layers is None else max(1, min(args.layers, full_layers))
     cfg["num_hidden_layers"] = layers
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
@@ -314,10 +325,11 @@ def main() -> int:
     if not args.skip_e2e:
         e2e = measure_e2e(llm, args.batch, args.prompt, args.steps, args.warmup, vocab)
 
+    shape_name = "Qwen3-" + args.shape.split("-")[1].upper()
     step_bytes = decode_step_bytes(cfg, layers, [main_run["mean_ctx"]] * args.batch)
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random bf16 weights, KV bf16 paged, block 16)",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name} shape, random bf16 weights, KV bf16 paged, block 16)",
         "value": round(main_run["tok_s"], 2),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -331,8 +343,8 @@ def main() -> int:
         "data": "synthetic",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape, random weights", "global_batch": args.batch, "seq_len": args.context,
-            "parallelism": "single GPU", "layers": layers, "layers_full": FULL_LAYERS,
+            "model": f"{shape_name} shape, random weights", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "single GPU", "layers": layers, "layers_full": full_layers,
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": vocab, "kv_block": 16,

@@ -45,6 +45,15 @@ struct GemmParams {
     int swiglu;            // the rows of w come in blocks of 64 gate rows then 64 up rows; out[M, N / 2] =
                            // silu(gate) * up
     int* error;
+    // Many rows (the persistent kernel): the last sk_tiles output tiles do not fill a round of all
+    // CTAs, so the other CTAs help with them.  CTA i < sk_tiles takes the first sk_head K blocks of
+    // tile i (these CTAs walk K together, as a round of whole tiles does, and share what they load);
+    // the rest of those tiles' K blocks, end to end, is dealt out in runs of sk_per to the next
+    // sk_helpers CTAs.  A helper writes the sums of each piece to a slot of sk_scratch and counts
+    // itself in; the tile's first CTA adds those slots to its own sums, in K order, and writes the tile.
+    int sk_tiles, sk_head, sk_helpers, sk_per, sk_slots_per_helper;
+    float* sk_scratch;     // [helpers][slots per helper][128 x BN]
+    int* sk_counters;      // [sk_tiles][4], zero between launches
 };
 
 template <int BN>
@@ -539,6 +548,182 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
     }
 }
 
+// The pieces of work of one CTA of the persistent kernel, in the order in which its three roles
+// take them: whole tiles (tile t, t + CTAs, ...), then either the head of one shared tile or a
+// helper's run over the tails of shared tiles (see GemmParams).
+struct WorkWalk {
+    int t, step, whole_tiles, kb, head, own_tile, tail, pos, end, slot;
+    __device__ WorkWalk(const GemmParams& p, int tiles_total)
+    {
+        whole_tiles = tiles_total - p.sk_tiles;
+        kb = p.k_blocks_total;
+        t = blockIdx.x;
+        step = gridDim.x;
+        head = p.sk_head;
+        tail = kb - head;
+        own_tile = (int)blockIdx.x < p.sk_tiles ? whole_tiles + (int)blockIdx.x : -1;
+        const int helper = (int)blockIdx.x - p.sk_tiles;
+        pos = end = 0;
+        slot = 0;
+        if (helper >= 0 && helper < p.sk_helpers) {
+            const int all = p.sk_tiles * tail;
+            const long long b = (long long)helper * p.sk_per;
+            pos = b < all ? (int)b : all;
+            end = b + p.sk_per < all ? (int)(b + p.sk_per) : all;
+            slot = helper * p.sk_slots_per_helper;
+        }
+    }
+    // kind: 0 a whole tile, 1 the head of a shared tile (collect the rest), 2 a helper's piece (-> slot)
+    __device__ bool next(int& tile, int& k0, int& k1, int& kind, int& piece_slot)
+    {
+        piece_slot = 0;
+        if (t < whole_tiles) {
+            tile = t;
+            k0 = 0;
+            k1 = kb;
+            kind = 0;
+            t += step;
+            return true;
+        }
+        if (own_tile >= 0) {
+            tile = own_tile;
+            k0 = 0;
+            k1 = head;
+            kind = head < kb ? 1 : 0;
+            own_tile = -1;
+            return true;
+        }
+        if (pos < end) {
+            const int ti = pos / tail;
+            k0 = head + (pos - ti * tail);
+            k1 = k0 + (end - pos) < kb ? k0 + (end - pos) : kb;
+            tile = whole_tiles + ti;
+            kind = 2;
+            piece_slot = slot++;
+            pos += k1 - k0;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ int load_acquire(const int* p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// A CTA that has K blocks from the middle of a tile: its sums go to its slot and the warp counts
+// itself in for its quarter of the rows.  A slot is [quarter][half of the columns][column / 4][row][4],
+// so that what one warp of the collecting CTA needs is one run of 16 KB per half.
+constexpr int SK_HALF_FLOATS = 32 * 32 * 4;         // 128 columns of 32 rows
+template <int BN>
+__device__ __forceinline__ void contribute_partial_tile(const GemmParams& p, uint32_t taddr, int quarter, int lane,
+                                                        int shared_tile, int piece_slot)
+{
+    static_assert(BN == 256, "the slot layout is written for tiles of 256 columns");
+    float4* slot = reinterpret_cast<float4*>(p.sk_scratch + (size_t)piece_slot * (TILE_A * BN)
+                                             + (size_t)quarter * 2 * SK_HALF_FLOATS) + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_load_32x32(taddr + c0, r);
+        tmem_load_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            slot[(c0 / 4 + j) * 32] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0)
+        atomicAdd(p.sk_counters + shared_tile * 4 + quarter, 1);
+}
+
+// The CTA with a tile's first K blocks: waits (with a limit) until the helpers that share the
+// tile's other K blocks have left their sums, adds them to its own in TMEM in K order, and clears
+// the counter for the next launch.  The sums come through shared memory by bulk copies, 16 KB at a
+// time into three buffers (`buffers`: 48 KB of this warp's own, free because this is the CTA's last
+// piece of work).
+template <int BN>
+__device__ __forceinline__ void collect_partial_tiles(const GemmParams& p, uint32_t taddr, int quarter, int lane,
+                                                      int shared_tile, uint8_t* buffers, uint64_t* bars)
+{
+    static_assert(BN == 256, "the slot layout is written for tiles of 256 columns");
+    // the tile's tail is [shared_tile * tail, + tail) of the helpers' range; helper j's piece of it is
+    // the (shared_tile - first tile of j)-th slot of j
+    const int tail = p.k_blocks_total - p.sk_head;
+    const int helper0 = (shared_tile * tail) / p.sk_per;
+    const int others = ((shared_tile + 1) * tail - 1) / p.sk_per - helper0 + 1;
+    const auto slot_of = [&](int c) {
+        const int j = helper0 + c;
+        return j * p.sk_slots_per_helper + shared_tile - (j * p.sk_per) / tail;
+    };
+    int* counter = p.sk_counters + shared_tile * 4 + quarter;
+    int ok = 1;
+    if (lane == 0 && load_acquire(counter) < others) {
+        const long long start = clock64();
+        while (load_acquire(counter) < others) {
+            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                if (p.error)
+                    atomicExch(p.error, 15);
+                ok = 0;
+                break;
+            }
+            __nanosleep(40);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    if (!ok)
+        return;
+    if (lane == 0)
+        *counter = 0;
+    const float* mine = p.sk_scratch + (size_t)quarter * 2 * SK_HALF_FLOATS;
+    const int items = 2 * others;               // (CTA, half of the columns), in that order
+    constexpr uint32_t BYTES = SK_HALF_FLOATS * 4;
+    const auto fetch = [&](int n) {             // item n -> buffer n % 3 (lane 0 only)
+        mbar_arrive_expect_tx(&bars[n % 3], BYTES);
+        bulk_load(buffers + (n % 3) * BYTES, mine + (size_t)slot_of(n >> 1) * (TILE_A * BN) + (n & 1) * SK_HALF_FLOATS,
+                  BYTES, &bars[n % 3]);
+    };
+    if (lane == 0) {
+        fetch(0);
+        fetch(1);
+    }
+#pragma unroll 1
+    for (int i = 0; i < items; ++i) {
+        if (i + 2 < items) {
+            __syncwarp();                        // every lane has read what item i - 1 left in that buffer
+            if (lane == 0) {
+                fence_proxy_async();
+                fetch(i + 2);
+            }
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars[i % 3], (i / 3) & 1, p.error, 16)))
+            return;                              // (the whole warp: what follows is warp-wide)
+        const float4* src = reinterpret_cast<const float4*>(buffers + (i % 3) * BYTES) + lane;
+        const uint32_t col0 = (i & 1) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+            uint32_t r[32];
+            tmem_load_32x32(taddr + col0 + c0, r);
+            tmem_load_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 q = src[(c0 / 4 + j) * 32];
+                r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + q.x);
+                r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + q.y);
+                r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + q.z);
+                r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + q.w);
+            }
+            tmem_store_32x32(taddr + col0 + c0, r);
+        }
+        tmem_store_wait();
+    }
+}
+
 // x is the A operand (many rows).  One CTA per SM walks over the output tiles
 // (tile t -> row block t % tiles_m, column block t / tiles_m, so that CTAs working
 // at the same time share a block of w).  Two accumulators in TMEM: while the four
@@ -558,10 +743,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;     // [2]
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;     // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    uint64_t* collect_bar = tmem_empty_bar + 2;       // [4][3]: the bulk copies of a shared-out tile's other sums
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(collect_bar + 12);
     uint8_t* stage_base = reinterpret_cast<uint8_t*>(tmem_slot + 4);      // 16-byte aligned
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb_count = p.k_blocks_total;
     constexpr uint32_t TMEM_COLS = 2 * BN;
 
     if (threadIdx.x == 0) {
@@ -573,6 +758,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             mbar_init(&tmem_full_bar[b], 1);
             mbar_init(&tmem_empty_bar[b], 128);       // every epilogue thread arrives
         }
+        for (int b = 0; b < 12; ++b)
+            mbar_init(&collect_bar[b], 1);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -590,9 +777,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             tma_prefetch_descriptor(&map_b);
             uint32_t it = 0;
             bool waited = false;
-            for (int t = blockIdx.x; t < tiles_total; t += gridDim.x) {
+            WorkWalk walk(p, tiles_total);
+            int t, k0, k1, kind, piece_slot;
+            while (walk.next(t, k0, k1, kind, piece_slot)) {
                 const int tile_a = t % tiles_m, tile_b = t / tiles_m;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                for (int kb = k0; kb < k1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (round > 0)
@@ -613,13 +802,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
             constexpr uint32_t idesc = make_idesc_bf16_f32(TILE_A, BN);
             uint32_t it = 0, lt = 0;
-            for (int t = blockIdx.x; t < tiles_total; t += gridDim.x, ++lt) {
+            WorkWalk walk(p, tiles_total);
+            int t, k0, k1, kind, piece_slot;
+            for (; walk.next(t, k0, k1, kind, piece_slot); ++lt) {
                 const uint32_t buf = lt & 1, use = lt >> 1;
                 if (use > 0)
                     mbar_wait(&tmem_empty_bar[buf], (use - 1) & 1, p.error, 14);
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                for (int kb = k0; kb < k1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     mbar_wait(&full_bar[s], round & 1, p.error, 12);
@@ -630,7 +821,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                     for (int k = 0; k < TILE_K / UMMA_K; ++k) {
                         const uint64_t a_desc = make_kmajor_sw128_desc(a_addr + k * UMMA_K * 2);
                         const uint64_t b_desc = make_kmajor_sw128_desc(b_addr + k * UMMA_K * 2);
-                        tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tcgen05_mma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > k0 || k > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(&empty_bar[s]);
                 }
@@ -641,14 +832,27 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         const int quarter = warp & 3;
         pdl_wait();
         uint32_t lt = 0;
-        for (int t = blockIdx.x; t < tiles_total; t += gridDim.x, ++lt) {
+        WorkWalk walk(p, tiles_total);
+        int t, k0, k1, kind, piece_slot;
+        for (; walk.next(t, k0, k1, kind, piece_slot); ++lt) {
             const int tile_a = t % tiles_m, tile_b = t / tiles_m;
             const uint32_t buf = lt & 1, use = lt >> 1;
             mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 13);
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
-                                    stage_base + quarter * EPILOGUE_STAGE_BYTES);
+            const int shared_tile = t - walk.whole_tiles;
+            if (kind == 2) {
+                contribute_partial_tile<BN>(p, taddr, quarter, lane, shared_tile, piece_slot);
+            } else {
+                if (kind == 1) {
+                    // (this is the CTA's last piece of work and its products are done: the stages are free)
+                    static_assert(STAGES >= 4 && S::STAGE_BYTES >= 3 * SK_HALF_FLOATS * 4, "a stage per epilogue warp");
+                    collect_partial_tiles<BN>(p, taddr, quarter, lane, shared_tile, smem + quarter * S::STAGE_BYTES,
+                                              collect_bar + 3 * quarter);
+                }
+                epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
+                                        stage_base + quarter * EPILOGUE_STAGE_BYTES);
+            }
             tcgen05_fence_before();
             mbar_arrive(&tmem_empty_bar[buf]);
         }
@@ -684,6 +888,10 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 }
 
 // ------------------------------------------------------------------ host side
+constexpr int STREAM_K_COUNTERS = 4096;
+__device__ int stream_k_counters[STREAM_K_COUNTERS];      // zero when loaded; every use leaves them zero
+static struct { float* scratch; long long floats; int fill_divisor; } stream_k = { nullptr, 0, 4 };
+
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
                        cudaStream_t stream, int cluster_z = 1)
@@ -714,7 +922,7 @@ template <int BN, int STAGES>
 static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
                                   int tiles_m, int tiles_n, cudaStream_t stream)
 {
-    constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16
+    constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4 + 12) * 8 + 16
         + 4 * EPILOGUE_STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -728,8 +936,42 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
     int device = 0, sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess)
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const int ctas = tiles < sms ? tiles : sms;
-    launch(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(GEMM_THREADS), smem, stream, ma, mb, p,
+    int ctas = tiles < sms ? tiles : sms;
+    GemmParams q = p;
+    // A last round that would leave most SMs idle is shared out by K blocks instead.  Measured at
+    // 2,048 rows: a round that fills a quarter of the SMs or less gains (5120 x 17408: 333 -> 274 us;
+    // 7168 x 5120: 120 -> 116), a fuller one does not (under the power cap the busy SMs of a partly
+    // filled round run faster, and adding up the partial sums costs 15 to 20 us: 4096 x 4096 with
+    // 108 tiles left, 56 -> 63 us).
+    const int rest = tiles % sms, kb = p.k_blocks_total;
+    int* counters = nullptr;
+    if (stream_k.scratch && rest > 0 && rest * stream_k.fill_divisor <= sms && kb >= 16 && rest * 4 <= STREAM_K_COUNTERS
+        && cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), stream_k_counters) == cudaSuccess) {
+        // CTAs to a tile: what the idle SMs allow, at most eight (the first CTA adds the others' sums
+        // one after the other); head and helpers' runs of about the same length
+        const double share = (double)sms / rest < 8.0 ? (double)sms / rest : 8.0;
+        int head = (int)((kb + share - 1e-9) / share);
+        if (head < 1)
+            head = 1;
+        const int tail = kb - head;
+        int helpers = sms - rest < rest * 7 ? sms - rest : rest * 7;
+        if (tail > 0 && helpers > 0) {
+            const int per = (rest * tail + helpers - 1) / helpers;
+            helpers = (rest * tail + per - 1) / per;
+            const int slots_per = (per + tail - 1) / tail + 1;
+            if ((long long)helpers * slots_per * TILE_A * BN <= stream_k.floats) {
+                ctas = sms;
+                q.sk_tiles = rest;
+                q.sk_head = head;
+                q.sk_helpers = helpers;
+                q.sk_per = per;
+                q.sk_slots_per_helper = slots_per;
+                q.sk_scratch = stream_k.scratch;
+                q.sk_counters = counters;
+            }
+        }
+    }
+    launch(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(GEMM_THREADS), smem, stream, ma, mb, q,
            tiles_m, tiles);
     return launch_status();
 }
@@ -881,6 +1123,17 @@ CHIBI_API int chibi_gemm_bf16(const void* x, const void* w, void* out, int out_t
 {
     return gemm_bf16_impl(x, w, out, out_type, residual, M, N, K, x_stride, w_stride, out_stride,
                           res_stride, scratch, scratch_floats, error, stream, true);
+}
+
+// Scratch for the many-row kernel's shared-out last round: up to 2 * multiProcessorCount slots of
+// 128 * 256 floats, 16-byte aligned, used by one stream at a time.  Without it (null) every tile is computed whole.
+CHIBI_API int chibi_gemm_set_stream_scratch(float* scratch, long long floats)
+{
+    if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15))
+        return CHIBI_ERR_ARGUMENT;
+    stream_k.scratch = scratch;
+    stream_k.floats = scratch ? floats : 0;
+    return CHIBI_OK;
 }
 
 // How many CTAs share one tile's K range in chibi_gemm_bf16_fused (1 for M > 64).

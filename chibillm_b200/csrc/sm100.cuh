@@ -136,6 +136,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
                  : "memory");
 }
 
+// Untiled bulk copy global -> shared memory of this CTA: both addresses 16-byte aligned, bytes a
+// multiple of 16; completes on the mbarrier with `bytes` transaction bytes.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -29,6 +29,7 @@ _SIGNATURES = {
         "chibi_gemm_bf16_splits": [I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_gemm_bf16_cluster_size": [I, I, I],
+        "chibi_gemm_set_stream_scratch": [P, L],
         "chibi_gemm_bf16_fused": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P],
         "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, P, P],
         "chibi_reduce_residual_rmsnorm": [P, I, I, I, P, L, P, I, P, I, L, F, F, P],

@@ -7,7 +7,7 @@ nothing once its workspace exists) and launch on torch's current stream.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -70,6 +70,9 @@ class PendingSum:
         self.kernels.reduce_residual_rmsnorm(self, residual, None, 0.0, 0.0, None)
 
 
+_STREAM_SCRATCH: Dict[torch.device, torch.Tensor] = {}
+
+
 class CudaKernels:
     """The one set of operations of the product path."""
 
@@ -104,6 +107,22 @@ class CudaKernels:
         self.use_clusters = False
         self.fuse_split_products = True
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # the many-row product shares its last, partly filled round of tiles out by K blocks and
+        # needs room for one tile of partial sums per SM
+        # (one per process, never freed: the library keeps the pointer)
+        if self.device not in _STREAM_SCRATCH:
+            _STREAM_SCRATCH.clear()
+            _STREAM_SCRATCH[self.device] = torch.empty(2 * self.sm_count * 128 * 256, dtype=torch.float32,
+                                                       device=self.device)
+            scratch = _STREAM_SCRATCH[self.device]
+            _check(self.lib.chibi_gemm_set_stream_scratch(_ptr(scratch), scratch.numel()), "stream scratch")
+
+    def share_out_last_round(self, enabled: bool) -> None:
+        """Whether the many-row product deals the K blocks of a thinly filled last round
+        of tiles out to all SMs (the default) or computes every tile whole."""
+        scratch = _STREAM_SCRATCH[self.device] if enabled else None
+        _check(self.lib.chibi_gemm_set_stream_scratch(_ptr(scratch), scratch.numel() if enabled else 0),
+               "stream scratch")
 
     def _scratch(self, floats: int) -> torch.Tensor:
         """32-bit scratch for kernels that split a reduction over several CTAs."""

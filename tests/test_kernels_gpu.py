@@ -323,6 +323,40 @@ def _linear_tensor_cores(k, ref, M, N, K):
     close(out, exp, torch.float32, "tensor-core linear on views", rel=2e-5)
 
 
+@pytest.mark.parametrize("M,N,K", [(1300, 4096, 1024), (2000, 5120, 5160), (300, 1000, 1000), (257, 512, 8192)])
+def test_linear_shares_out_a_thin_last_round(k, ref, M, N, K):
+    """Many rows whose tiles leave a last round that fills a quarter of the SMs or
+    less: the K blocks of those tiles are dealt out to all SMs and the partial
+    sums added by the tile's first CTA.  Same result as whole tiles up to the
+    order of 32-bit sums, launch after launch (the counters are left at zero)."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=36)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=37, scale=0.05)
+    exp = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ref.linear(x, w, exp)
+    whole = torch.empty_like(exp)
+    k.share_out_last_round(False)
+    try:
+        k.linear(x, w, whole)
+    finally:
+        k.share_out_last_round(True)
+    close(whole, exp, torch.float32, "whole tiles", rel=2e-5)
+    for launch in range(3):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        k.linear(x, w, out)
+        close(out, exp, torch.float32, f"last round shared out, launch {launch}", rel=2e-5)
+    res = rnd(M, N, seed=38)
+    exp_res = torch.empty_like(res)
+    ref.linear(x, w, exp_res, residual=res)
+    k.linear(x, w, res, residual=res)
+    close(res, exp_res, torch.float32, "shared out + residual in place", rel=2e-5)
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    exp16 = torch.empty_like(out16)
+    k.linear(x, w, out16)
+    ref.linear(x, w, exp16)
+    close(out16, exp16, torch.bfloat16, "shared out -> bfloat16", rel=8e-3)
+    k.check_error_word()
+
+
 def test_linear_falls_back_when_unaligned(k, ref):
     x = rnd(5, 100, dtype=torch.bfloat16, seed=34)      # K = 100 is no multiple of 8
     w = rnd(40, 100, dtype=torch.bfloat16, seed=35)
