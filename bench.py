@@ -14,6 +14,10 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 64.  Token ids are uniform random; the caches that decoding starts from are
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
+
+``--shape`` runs the same at the Qwen3-0.6B or Qwen3-14B layer sizes, and
+``--mixed-requests N`` replaces the record by a serving run: N requests with
+prompts of 16 to 2,048 tokens and 256 new tokens each through ``LLM.generate``.
 """
 from __future__ import annotations
 
@@ -246,6 +250,36 @@ def measure_e2e(llm, batch, prompt_len, steps, warmup, vocab):
     return {"tok_s": produced / dt, "h2d": h2d, "d2h": batch * 4 + 4}
 
 
+def measure_mixed(cfg, layers, full_layers, requests, shape):
+    """Requests of mixed lengths through ``LLM.generate``: prompts of 16 to 2,048 uniform random
+    tokens, 256 greedy tokens each (the end-of-sequence token ignored), all submitted at once, so
+    that prompt portions run beside decoding requests.  Wall-clock time of the second of two runs."""
+    import random
+    import torch
+    import chibillm_b200
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(16, 2048))] for _ in range(requests)]
+    new_tokens = 256
+    llm = chibillm_b200.LLM(None, dtype="bfloat16", device="cuda:0", context_length=8192,
+                            kv_cache_tokens=requests * (2048 + new_tokens + 64), max_sequences=requests,
+                            max_batch_tokens=2048, prefill_chunk_tokens=2048, random_config=cfg, random_seed=0)
+    seconds = None
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, max_tokens=new_tokens, ignore_eos=True)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+    generated = sum(len(o) for o in outs)
+    prompt_tokens = sum(len(p) for p in prompts)
+    return {"metric": f"generated tok/s, {requests} requests of mixed prompt lengths (Qwen3-{shape.split('-')[1].upper()} "
+                      "shape, random bf16 weights)", "value": round(generated / seconds, 1), "unit": "tokens/s",
+            "n_gpus": 1, "seconds": round(seconds, 3), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+            "total_tok_s": round((prompt_tokens + generated) / seconds, 1), "layers": layers,
+            "layers_full": full_layers, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "steps_from_graphs": llm.runner.graph_replays, "steps_launched_ahead": llm.runner.steps_ahead_used}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -261,6 +295,9 @@ def main() -> int:
     ap.add_argument("--point-steps", type=int, default=32)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--mixed-requests", type=int, default=0,
+                    help="instead of the record: this many requests with prompts of 16 to 2,048 random tokens "
+                         "and 256 new tokens each through the Python entry point; prints its own JSON line")
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),
                     help="layer sizes (random weights); the contract's record is the default")
     args = ap.parse_args()
@@ -287,6 +324,9 @@ def main() -> int:
     cfg["num_hidden_layers"] = layers
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
+    if args.mixed_requests > 0:
+        print(json.dumps(measure_mixed(cfg, layers, full_layers, args.mixed_requests, args.shape)))
+        return 0
     big = 64 if not args.skip_points else args.batch
     per_request = args.prompt + args.warmup + max(args.steps, args.point_steps) + 64
     pool = ((max(big, args.batch) * per_request + 63) // 64) * 64
