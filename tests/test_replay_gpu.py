@@ -23,9 +23,14 @@ CASES = {
     "A": ("A", 4, [5, 47, 100, 128]),
     "B": ("B", 16, [1, 40, 130, 250]),
     "C": ("C", 8, [3, 70, 200, 333]),
+    # head sizes 64 and 128: the tensor-core attention kernels, and at 128 the decode attention that
+    # finishes the q|k|v product itself (a window of 200 on the second layer)
+    "D64": ("D64", 16, [2, 90, 260, 400]),
+    "D128": ("D128", 16, [4, 65, 300, 520]),
 }
 MIXED_LENGTHS = {"A": [50, 100, 30, 128, 64, 90, 17], "B": [1, 200, 33, 250, 64, 129, 7],
-                 "C": [300, 20, 150, 65, 333, 2, 180]}
+                 "C": [300, 20, 150, 65, 333, 2, 180], "D64": [400, 31, 129, 64, 350, 3, 222],
+                 "D128": [17, 520, 66, 250, 2, 480, 128]}
 
 
 @pytest.fixture(scope="module")
