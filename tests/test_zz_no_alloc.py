@@ -80,7 +80,7 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(lib):
 
 
 def test_a_product_beyond_the_built_in_scratch_is_refused(lib):
-    M, N, K = 64, 4096, 12288
+    M, N, K = 32, 4096, 12288
     splits = lib.chibi_gemm_bf16_splits(M, N, K)
     assert splits * M * N > NOALLOC_SCRATCH_FLOATS
     x, w, _ = _inputs(M, N, K, 5)
