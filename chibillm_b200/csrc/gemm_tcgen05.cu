@@ -890,7 +890,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 // ------------------------------------------------------------------ host side
 constexpr int STREAM_K_COUNTERS = 4096;
 __device__ int stream_k_counters[STREAM_K_COUNTERS];      // zero when loaded; every use leaves them zero
-static struct { float* scratch; long long floats; int fill_divisor; } stream_k = { nullptr, 0, 4 };
+static struct { float* scratch; long long floats; int fill_divisor; int* counters; } stream_k = { nullptr, 0, 4, nullptr };
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
@@ -944,9 +944,8 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
     // filled round run faster, and adding up the partial sums costs 15 to 20 us: 4096 x 4096 with
     // 108 tiles left, 56 -> 63 us).
     const int rest = tiles % sms, kb = p.k_blocks_total;
-    int* counters = nullptr;
-    if (stream_k.scratch && rest > 0 && rest * stream_k.fill_divisor <= sms && kb >= 16 && rest * 4 <= STREAM_K_COUNTERS
-        && cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), stream_k_counters) == cudaSuccess) {
+    if (stream_k.scratch && stream_k.counters && rest > 0 && rest * stream_k.fill_divisor <= sms && kb >= 16
+        && rest * 4 <= STREAM_K_COUNTERS) {
         // CTAs to a tile: what the idle SMs allow, at most eight (the first CTA adds the others' sums
         // one after the other); head and helpers' runs of about the same length
         const double share = (double)sms / rest < 8.0 ? (double)sms / rest : 8.0;
@@ -967,7 +966,7 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
                 q.sk_per = per;
                 q.sk_slots_per_helper = slots_per;
                 q.sk_scratch = stream_k.scratch;
-                q.sk_counters = counters;
+                q.sk_counters = stream_k.counters;
             }
         }
     }
@@ -1152,6 +1151,14 @@ CHIBI_API int chibi_gemm_set_stream_scratch(float* scratch, long long floats)
 {
     if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15))
         return CHIBI_ERR_ARGUMENT;
+    if (scratch && !stream_k.counters) {
+        // looked up here, once, and not at a launch (which may be part of a stream capture)
+        void* counters = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&counters, stream_k_counters);
+        if (e != cudaSuccess)
+            return (int)e;
+        stream_k.counters = static_cast<int*>(counters);
+    }
     stream_k.scratch = scratch;
     stream_k.floats = scratch ? floats : 0;
     return CHIBI_OK;

@@ -143,3 +143,33 @@ def test_long_prompt_takes_the_many_row_kernels():
         del llm
         torch.cuda.empty_cache()
     assert tokens[True] == tokens[False]
+
+
+def test_many_sequences_decode_through_the_many_row_product():
+    """80 sequences decode in step: more than 64 rows, so the products of the replayed decode
+    graph are the many-row kernel, whose few tiles at this width are shared out by K blocks
+    (partial sums through scratch and counters that every launch must leave at zero).  The
+    bfloat16 engine against the 32-bit engine, step after step."""
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = base(hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, intermediate_size=2048,
+               vocab_size=4096, tie_word_embeddings=True)
+    n, steps = 80, 6
+    reqs = helpers.random_requests(cfg["vocab_size"], [3 + (i * 7) % 20 for i in range(n)], seed=9)
+    follow = helpers.random_requests(cfg["vocab_size"], [steps] * n, seed=10)
+
+    def run(dtype):
+        runner = ModelRunner.from_random(cfg, seed=6, dtype=dtype, page_size=16, pool_tokens=64 * n, max_requests=n)
+        rows = [runner.step([StepEntry(rid, ids, [len(ids) - 1]) for rid, ids in reqs.items()]).float().cpu().clone()]
+        for s in range(steps):
+            rows.append(runner.step([StepEntry(rid, [follow[rid][s]], [0]) for rid in reqs]).float().cpu().clone())
+        runner.runtime.kernels.check_error_word()
+        return torch.stack(rows), runner.graph_replays
+
+    exact, _ = run("float32")
+    got, replays = run("bfloat16")
+    assert replays >= steps - 2, "the decode steps were not replayed from a graph"
+    scale = float(exact.abs().max())
+    worst = float((got - exact).abs().max())
+    assert worst <= helpers.TOL["bfloat16"] * scale, f"bfloat16 against 32-bit: {worst} of {scale}"
+    assert (got.argmax(-1) == exact.argmax(-1)).float().mean() > 0.9
