@@ -818,6 +818,44 @@ CHIBI_API int chibi_cast(const void* x, int x_type, void* out, int out_type, lon
     return launch_status();
 }
 
+// x[m, :] *= rsqrt(sum of ssq[m][0 .. parts) / norm_n + eps): the factor of an RMSNorm that a
+// matrix product left out of its norm output, for a reader that cannot apply it itself.
+namespace chibi {
+__global__ void scale_rows_kernel(__nv_bfloat16* x, long long stride, int n, const float* __restrict__ ssq,
+                                  int parts, float eps, int norm_n)
+{
+    pdl_enter();
+    const long long m = blockIdx.x;
+    float ss = 0.f;
+    for (int j = 0; j < parts; ++j)
+        ss += ssq[m * parts + j];
+    const float inv = rsqrtf(ss / (float)norm_n + eps);
+    __nv_bfloat16* row = x + m * stride;
+    for (int j = threadIdx.x * 8; j < n; j += blockDim.x * 8) {
+        uint4 q = *reinterpret_cast<const uint4*>(row + j);
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            h[e] = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+        }
+        *reinterpret_cast<uint4*>(row + j) = q;
+    }
+}
+} // namespace chibi
+
+CHIBI_API int chibi_scale_rows(void* x, long long rows, int n, long long stride, const float* ssq, int parts,
+                               float eps, int norm_n, cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    if (n % 8 != 0 || stride % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || parts < 1 || norm_n < 1)
+        return CHIBI_ERR_UNSUPPORTED;
+    launch(chibi::scale_rows_kernel, dim3((unsigned)rows), dim3(256), 0, stream, static_cast<__nv_bfloat16*>(x),
+           stride, n, ssq, parts, eps, norm_n);
+    return launch_status();
+}
+
 CHIBI_API int chibi_add_into(float* acc, const void* x, int x_type, long long total,
                              cudaStream_t stream)
 {

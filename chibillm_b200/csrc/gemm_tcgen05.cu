@@ -54,6 +54,23 @@ struct GemmParams {
     int sk_tiles, sk_head, sk_helpers, sk_per, sk_slots_per_helper;
     float* sk_scratch;     // [helpers][slots per helper][128 x BN]
     int* sk_counters;      // [sk_tiles][4], zero between launches
+    // Many rows, RMSNorm folded into the products around it.  The per-row factor of the norm commutes
+    // with a product: RMSNorm(h) W^T = inv[m] * ((h * w_norm) W^T).  The product that completes the
+    // residual (out = residual + x W^T, 32-bit) also writes normed_out = bf16(out * (norm_w + offset))
+    // and, per row and column tile, the sum of the squares of out (ssq_out[m][tile]); the product that
+    // reads normed_out multiplies its sums by inv[m] = rsqrt(sum of row_ssq[m][0 .. parts) / n + eps)
+    // before what follows (conversion to bfloat16, SwiGLU).
+    const void* norm_w;    // [N], null: no norm output
+    int norm_w_type;
+    float norm_offset;
+    __nv_bfloat16* normed_out;
+    long long normed_stride;
+    float* ssq_out;        // [M][ssq_out_parts]
+    int ssq_out_parts;
+    const float* row_ssq;  // [M][row_ssq_parts], null: no factor
+    int row_ssq_parts;
+    float row_eps;
+    int row_n;
 };
 
 template <int BN>
@@ -399,6 +416,14 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
     const int m = m0 + lane;
     const int sub = lane >> 3, unit = lane & 7;      // the write-out: rows 4 * i + sub, 16-byte unit `unit`
     const bool inside = (tile_b + 1) * BN <= p.N && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    // the factor of the norm that was left out of x (this thread's row; 1 without one)
+    float inv = 1.f;
+    if (p.row_ssq && m < p.M) {
+        float ss = 0.f;
+        for (int j = 0; j < p.row_ssq_parts; ++j)
+            ss += __ldg(p.row_ssq + (size_t)m * p.row_ssq_parts + j);
+        inv = rsqrtf(ss / (float)p.row_n + p.row_eps);
+    }
     // every branch below is taken by whole warps: tcgen05.ld is a warp-wide instruction
     if (p.swiglu && inside && p.out_stride % 8 == 0) {
         // the BN columns are rows of w, which come as [64 gate | 64 up] blocks
@@ -417,8 +442,9 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
                         v[q] = __floats2bfloat162_rn(
-                            silu_mul(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q])),
-                            silu_mul(__uint_as_float(g[8 * j + 2 * q + 1]), __uint_as_float(u[8 * j + 2 * q + 1])));
+                            silu_mul(inv * __uint_as_float(g[8 * j + 2 * q]), inv * __uint_as_float(u[8 * j + 2 * q])),
+                            silu_mul(inv * __uint_as_float(g[8 * j + 2 * q + 1]),
+                                     inv * __uint_as_float(u[8 * j + 2 * q + 1])));
                     *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
                 }
             }
@@ -467,11 +493,13 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         const float* res = p.residual;
         const int n_tile = tile_b * BN;
         float4 q[8], qn[8];
+        float ssq[8];                   // with a norm output: squares of this lane's columns of rows 4 i + sub
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int r = m0 + 4 * i + sub;
             q[i] = (res && r < p.M) ? *reinterpret_cast<const float4*>(res + (size_t)r * p.res_stride + n_tile + unit * 4)
                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+            ssq[i] = 0.f;
         }
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -489,19 +517,52 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
             for (int j = 0; j < 8; ++j)
                 *stage_unit(stage, lane, j) = make_uint4(r32[4 * j], r32[4 * j + 1], r32[4 * j + 2], r32[4 * j + 3]);
             __syncwarp();
+            float w4[4] = { 0.f, 0.f, 0.f, 0.f };
+            if (p.norm_w) {
+                const int col = n_tile + c0 + unit * 4;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    w4[e] = (p.norm_w_type == CHIBI_F32 ? static_cast<const float*>(p.norm_w)[col + e]
+                                                        : __bfloat162float(static_cast<const __nv_bfloat16*>(p.norm_w)[col + e]))
+                        + p.norm_offset;
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int r = 4 * i + sub;
                 const uint4 v = *stage_unit(stage, r, unit);
-                if (m0 + r < p.M)
-                    *reinterpret_cast<float4*>(out + (size_t)(m0 + r) * p.out_stride + n_tile + c0 + unit * 4) =
-                        make_float4(q[i].x + __uint_as_float(v.x), q[i].y + __uint_as_float(v.y),
-                                    q[i].z + __uint_as_float(v.z), q[i].w + __uint_as_float(v.w));
+                const float4 h = make_float4(q[i].x + __uint_as_float(v.x), q[i].y + __uint_as_float(v.y),
+                                             q[i].z + __uint_as_float(v.z), q[i].w + __uint_as_float(v.w));
+                if (m0 + r < p.M) {
+                    *reinterpret_cast<float4*>(out + (size_t)(m0 + r) * p.out_stride + n_tile + c0 + unit * 4) = h;
+                    if (p.norm_w) {
+                        ssq[i] = fmaf(h.x, h.x, fmaf(h.y, h.y, fmaf(h.z, h.z, fmaf(h.w, h.w, ssq[i]))));
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(h.x * w4[0], h.y * w4[1]);
+                        const __nv_bfloat162 hi = __floats2bfloat162_rn(h.z * w4[2], h.w * w4[3]);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(p.normed_out + (size_t)(m0 + r) * p.normed_stride + n_tile + c0 + unit * 4) =
+                            packed;
+                    }
+                }
             }
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 q[i] = qn[i];
+        }
+        if (p.norm_w) {
+            // a row's eight lanes (the units) add up, always in the same order
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float s = ssq[i];
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                const int r = m0 + 4 * i + sub;
+                if (unit == 0 && r < p.M)
+                    p.ssq_out[(size_t)r * p.ssq_out_parts + tile_b] = s;
+            }
         }
         return;
     }
@@ -519,8 +580,8 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
                     __nv_bfloat162 v[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
-                        v[q] = __floats2bfloat162_rn(__uint_as_float(r32[8 * j + 2 * q]),
-                                                     __uint_as_float(r32[8 * j + 2 * q + 1]));
+                        v[q] = __floats2bfloat162_rn(inv * __uint_as_float(r32[8 * j + 2 * q]),
+                                                     inv * __uint_as_float(r32[8 * j + 2 * q + 1]));
                     *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
                 }
             }
@@ -1252,6 +1313,92 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     if (bn == 128)
         return launch_gemm<128, 4>(ma, mb, p, grid, stream);
     return launch_gemm<64, 4>(ma, mb, p, grid, stream);
+}
+
+// Many rows with an RMSNorm folded into the products around it (see GemmParams).  `scale`
+// (may be null) describes the factor that x lacks; `norm` (may be null) asks for the norm output of
+// the completed residual.  epilogue 1: SwiGLU as in chibi_gemm_bf16_fused.  Only the kernel for more
+// than 64 rows with whole 256-column tiles does this: CHIBI_ERR_UNSUPPORTED otherwise, and the caller
+// applies the norm or the factor with kernels of their own.
+struct ChibiRowScale {
+    const float* ssq;      // [M][parts] sums of squares
+    int parts;
+    float eps;
+    int n;                 // width of the normalised rows
+};
+struct ChibiNormOut {
+    const void* w;         // [N] norm weight
+    int w_type;
+    float offset;
+    void* out;             // [M][N] bfloat16: (residual + x W^T) * (w + offset), without the row's factor
+    long long out_stride;
+    float* ssq;            // [M][parts], parts = chibi_gemm_bf16_norm_parts(N)
+    long long ssq_floats;
+};
+
+CHIBI_API int chibi_gemm_bf16_norm_parts(int N) { return N > 0 && N % 256 == 0 ? N / 256 : 0; }
+
+CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int out_type, const float* residual,
+                                   int M, int N, int K, long long x_stride, long long w_stride, long long out_stride,
+                                   long long res_stride, int epilogue, const ChibiRowScale* scale,
+                                   const ChibiNormOut* norm, int* error, cudaStream_t stream)
+{
+    if (M <= 64 || N <= 0 || N % 256 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
+        || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
+        || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
+        return CHIBI_ERR_UNSUPPORTED;
+    GemmParams p {};
+    p.K = K;
+    p.M = M;
+    p.N = N;
+    p.out = out;
+    p.out_type = out_type;
+    p.out_stride = out_stride;
+    p.residual = residual;
+    p.res_stride = res_stride;
+    p.error = error;
+    p.swiglu = epilogue == 1 ? 1 : 0;
+    p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
+    p.k_blocks_per_split = p.k_blocks_total;
+    p.swap = 0;
+    p.rows_a = M;
+    p.rows_b = N;
+    if (p.swiglu) {
+        if (out_type != CHIBI_BF16 || residual || out_stride % 8 != 0 || norm)
+            return CHIBI_ERR_UNSUPPORTED;
+    } else if (norm) {
+        // the path that adds the residual in 32-bit, whole tiles only
+        if (out_type != CHIBI_F32 || !residual || out_stride % 4 != 0 || res_stride % 4 != 0 || scale)
+            return CHIBI_ERR_UNSUPPORTED;
+    } else if (out_type != CHIBI_BF16 || residual || out_stride % 8 != 0) {
+        return CHIBI_ERR_UNSUPPORTED;      // a factor is applied where the sums become bfloat16
+    }
+    if (scale) {
+        if (!scale->ssq || scale->parts < 1 || scale->n < 1)
+            return CHIBI_ERR_ARGUMENT;
+        p.row_ssq = scale->ssq;
+        p.row_ssq_parts = scale->parts;
+        p.row_eps = scale->eps;
+        p.row_n = scale->n;
+    }
+    if (norm) {
+        const int parts = N / 256;
+        if (!norm->w || !norm->out || !norm->ssq || norm->ssq_floats < (long long)M * parts
+            || (norm->w_type != CHIBI_F32 && norm->w_type != CHIBI_BF16) || norm->out_stride % 4 != 0
+            || (reinterpret_cast<uintptr_t>(norm->out) & 7))
+            return CHIBI_ERR_ARGUMENT;
+        p.norm_w = norm->w;
+        p.norm_w_type = norm->w_type;
+        p.norm_offset = norm->offset;
+        p.normed_out = static_cast<__nv_bfloat16*>(norm->out);
+        p.normed_stride = norm->out_stride;
+        p.ssq_out = norm->ssq;
+        p.ssq_out_parts = parts;
+    }
+    CUtensorMap ma, mb;
+    if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, 256, &mb))
+        return CHIBI_ERR_UNSUPPORTED;
+    return launch_gemm_persistent<256, 4>(ma, mb, p, (M + TILE_A - 1) / TILE_A, N / 256, stream);
 }
 
 // The first half only, for shapes that chibi_gemm_bf16_splits splits (> 1): the

@@ -30,6 +30,9 @@ _SIGNATURES = {
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_gemm_bf16_cluster_size": [I, I, I],
         "chibi_gemm_set_stream_scratch": [P, L],
+        "chibi_gemm_bf16_norm_parts": [I],
+        "chibi_gemm_bf16_rows": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P, P, P],
+        "chibi_scale_rows": [P, L, I, L, P, I, F, I, P],
         "chibi_gemm_bf16_fused": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P],
         "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, P, P],
         "chibi_reduce_residual_rmsnorm": [P, I, I, I, P, L, P, I, P, I, L, F, F, P],
@@ -50,6 +53,17 @@ _SIGNATURES = {
                                          F, F, I, P, P],
     },
 }
+
+
+class RowScale(ctypes.Structure):
+    """ChibiRowScale of gemm_tcgen05.cu: the factor of an RMSNorm that x lacks."""
+    _fields_ = [("ssq", c_void_p), ("parts", c_int), ("eps", c_float), ("n", c_int)]
+
+
+class NormOut(ctypes.Structure):
+    """ChibiNormOut of gemm_tcgen05.cu: the norm output that a product writes beside the residual."""
+    _fields_ = [("w", c_void_p), ("w_type", c_int), ("offset", c_float), ("out", c_void_p),
+                ("out_stride", c_longlong), ("ssq", c_void_p), ("ssq_floats", c_longlong)]
 
 
 class KernelLibraryError(RuntimeError):

@@ -7,6 +7,7 @@ nothing once its workspace exists) and launch on torch's current stream.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Optional
 
 import torch
@@ -70,6 +71,54 @@ class PendingSum:
         self.kernels.reduce_residual_rmsnorm(self, residual, None, 0.0, 0.0, None)
 
 
+class ScaledRows:
+    """A norm's output without the factor of each row: ``tensor`` holds
+    x * (w + offset) in bfloat16 and ``ssq`` [rows, parts] sums of squares of x, so
+    that RMSNorm(x)[m] = tensor[m] * rsqrt(sum(ssq[m]) / n + eps).  The factor
+    commutes with a matrix product, and ``linear`` / ``linear_swiglu`` apply it to
+    their sums; ``materialise`` applies it in place for any other reader."""
+
+    def __init__(self, kernels, tensor: torch.Tensor, ssq: torch.Tensor, parts: int, eps: float, n: int):
+        self.kernels, self.tensor, self.ssq, self.parts, self.eps, self.n = kernels, tensor, ssq, parts, eps, n
+
+    @property
+    def shape(self):
+        return self.tensor.shape
+
+    @property
+    def dtype(self):
+        return self.tensor.dtype
+
+    def materialise(self) -> torch.Tensor:
+        self.kernels.scale_rows(self)
+        return self.tensor
+
+
+class DeferredProduct:
+    """residual += x @ w^T of many rows, not launched yet: the norm that follows
+    may have the product write the norm's output as well (``finish_with_norm``);
+    anybody else adds it (``add_into``)."""
+
+    def __init__(self, kernels, x: torch.Tensor, w: torch.Tensor):
+        self.kernels, self.x, self.w = kernels, x, w
+
+    def add_into(self, residual: torch.Tensor) -> None:
+        self.kernels.linear(self.x, self.w, residual, residual=residual)
+
+    def finish_with_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, offset: float,
+                         out: torch.Tensor, scaled_ok: bool):
+        """Adds the product into ``residual`` and normalises: returns ``out`` (the
+        norm's output) or, if the reader takes them, ScaledRows over ``out``."""
+        k = self.kernels
+        if scaled_ok:
+            scaled = k.linear_residual_norm(self.x, self.w, residual, weight, eps, offset, out)
+            if scaled is not None:
+                return scaled
+        self.add_into(residual)
+        k.rmsnorm(residual, weight, eps, offset, out)
+        return out
+
+
 _STREAM_SCRATCH: Dict[torch.device, torch.Tensor] = {}
 
 
@@ -99,6 +148,11 @@ class CudaKernels:
         self.use_tcgen05_attention = True
         self._partial_bufs = [None, None]
         self._partial_turn = 0
+        self._ssq_bufs = [None, None]
+        self._ssq_turn = 0
+        # Many rows: the product that completes the residual also writes the following RMSNorm's
+        # output, up to the factor of each row, which the next product applies to its sums.
+        self.fold_norms = True
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
         # global scratch to a second kernel that also does what follows the product (the default), or
         # the CTAs form a cluster and add up through distributed shared memory (use_clusters; measured
@@ -123,6 +177,79 @@ class CudaKernels:
         scratch = _STREAM_SCRATCH[self.device] if enabled else None
         _check(self.lib.chibi_gemm_set_stream_scratch(_ptr(scratch), scratch.numel() if enabled else 0),
                "stream scratch")
+
+    def scale_rows(self, rows: ScaledRows) -> None:
+        """rows.tensor *= the factor of each row, in place."""
+        t = rows.tensor
+        _rows_contiguous(t, "scale_rows")
+        self.launches += 1
+        _check(self.lib.chibi_scale_rows(_ptr(t), t.shape[0], t.shape[1], t.stride(0), _ptr(rows.ssq), rows.parts,
+                                         float(rows.eps), rows.n, self._stream()), "scale_rows")
+
+    def linear_residual_norm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
+                             weight: torch.Tensor, eps: float, offset: float,
+                             out: torch.Tensor) -> Optional[ScaledRows]:
+        """residual += x @ w^T and, from the same kernel, the RMSNorm of the new
+        residual without the rows' factor (see ScaledRows).  None if the kernel for
+        many rows does not take these shapes; nothing has run then."""
+        M, K = x.shape
+        N = w.shape[0]
+        parts = self.lib.chibi_gemm_bf16_norm_parts(N)
+        if not (self.use_tensor_cores and self.fold_norms and M > 64 and parts > 0 and x.dtype == torch.bfloat16
+                and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and residual.dtype == torch.float32
+                and residual.shape == (M, N) and out.shape == (M, N) and weight.shape == (N,)
+                and weight.is_contiguous() and weight.dtype in (torch.bfloat16, torch.float32)):
+            return None
+        _need_cuda(x, w, residual, weight, out)
+        for t, what in ((x, "x"), (w, "w"), (residual, "residual"), (out, "out")):
+            _rows_contiguous(t, f"linear_residual_norm: {what}")
+        ssq = self._ssq_buffer(M * parts)
+        norm = library.NormOut(_ptr(weight), _code(weight), float(offset), _ptr(out), out.stride(0), _ptr(ssq),
+                               ssq.numel())
+        status = self.lib.chibi_gemm_bf16_rows(
+            _ptr(x), _ptr(w), _ptr(residual), F32, _ptr(residual), M, N, K, x.stride(0), w.stride(0),
+            residual.stride(0), residual.stride(0), 0, None, ctypes.byref(norm), _ptr(self.error), self._stream())
+        if status == -2:
+            return None
+        _check(status, "linear (+ residual, + norm output)")
+        self.launches += 1
+        self.tensor_core_calls += 1
+        return ScaledRows(self, out, ssq, parts, eps, N)
+
+    def _ssq_buffer(self, floats: int) -> torch.Tensor:
+        """Two buffers in turn: the sums of squares of one norm are read while the
+        product that follows the next norm already writes its own."""
+        self._ssq_turn ^= 1
+        buf = self._ssq_bufs[self._ssq_turn]
+        if buf is None or buf.numel() < floats:
+            buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=self.device)
+            self._ssq_bufs[self._ssq_turn] = buf
+            self.scratch_generation += 1
+        return buf
+
+    def _linear_of_scaled(self, x: ScaledRows, w: torch.Tensor, out: torch.Tensor, swiglu: bool) -> bool:
+        """out = (the factor of each row) * (x.tensor @ w^T), with SwiGLU if asked,
+        from the kernel for many rows; False if it does not take the shapes."""
+        t = x.tensor
+        M, K = t.shape
+        N = w.shape[0]
+        if not (self.use_tensor_cores and M > 64 and N % 256 == 0 and w.dtype == torch.bfloat16
+                and out.dtype == torch.bfloat16 and w.shape[1] == K
+                and out.shape == (M, N // 2 if swiglu else N)):
+            return False
+        _need_cuda(t, w, out)
+        for u, what in ((t, "x"), (w, "w"), (out, "out")):
+            _rows_contiguous(u, f"linear: {what}")
+        scale = library.RowScale(_ptr(x.ssq), x.parts, float(x.eps), x.n)
+        status = self.lib.chibi_gemm_bf16_rows(
+            _ptr(t), _ptr(w), _ptr(out), BF16, None, M, N, K, t.stride(0), w.stride(0), out.stride(0), 0,
+            1 if swiglu else 0, ctypes.byref(scale), None, _ptr(self.error), self._stream())
+        if status == -2:
+            return False
+        _check(status, "linear (rows with a factor)")
+        self.launches += 1
+        self.tensor_core_calls += 1
+        return True
 
     def _scratch(self, floats: int) -> torch.Tensor:
         """32-bit scratch for kernels that split a reduction over several CTAs."""
@@ -207,6 +334,8 @@ class CudaKernels:
         """Start x @ w^T with the K range split over CTAs and leave the partial
         sums for a fused consumer; None if this product is not one that is split
         (then use ``linear``)."""
+        if isinstance(x, ScaledRows):
+            return None                  # many rows: such a product is not split
         if not (self.use_tensor_cores and self.fuse_split_products and x.is_cuda
                 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             return None
@@ -244,6 +373,10 @@ class CudaKernels:
         """out[M, I] = silu(x @ gate^T) * (x @ up^T) in one kernel, with the weights
         as ``interleave_gate_up`` arranges them.  False if the kernel refuses the
         shapes (the caller then takes the two-kernel way)."""
+        if isinstance(x, ScaledRows):
+            if self._linear_of_scaled(x, w_interleaved, out, swiglu=True):
+                return True
+            x = x.materialise()
         _need_cuda(x, w_interleaved, out)
         _rows_contiguous(x, "linear_swiglu: x")
         _rows_contiguous(w_interleaved, "linear_swiglu: w")
@@ -343,10 +476,17 @@ class CudaKernels:
         """out[M, N] = x[M, K] @ w[N, K]^T (+ residual, 32-bit, may alias out).
         With ``defer`` (only together with a residual that aliases out) a split
         product is left pending -- the caller adds it later -- and is returned."""
+        if isinstance(x, ScaledRows):
+            if residual is None and self._linear_of_scaled(x, w, out, swiglu=False):
+                return None
+            x = x.materialise()
         if defer and residual is not None and residual is out:
             pending = self.linear_partial(x, w)
             if pending is not None:
                 return pending
+            if self.use_tensor_cores and self.fold_norms and x.shape[0] > 64 and x.dtype == torch.bfloat16 \
+                    and w.dtype == torch.bfloat16 and residual.dtype == torch.float32:
+                return DeferredProduct(self, x, w)
         _need_cuda(x, w, out, residual)
         _rows_contiguous(x, "linear: x")
         _rows_contiguous(w, "linear: w")

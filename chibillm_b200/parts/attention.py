@@ -57,6 +57,8 @@ class PagedAttention(Mixer):
             self.k_norm = tensors[self.names["k_norm"]].to(self.q_norm.dtype).contiguous()
 
     # ---- cache
+    accepts_scaled_rows = True       # x goes to the q | k | v product and nowhere else
+
     def cache_need(self):
         s = self.spec
         return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window)

@@ -83,12 +83,17 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         raise NotImplementedError
 
-    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor) -> None:
+    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor, scaled_ok: bool = False):
         """residual += pending (a matrix product that its producer left for us to
-        add, or None); out = norm(residual).  A norm may do both in one kernel."""
+        add, or None); out = norm(residual).  A norm may do both in one kernel.
+        Returns what the reader is to be given: ``out``, or -- only if ``scaled_ok``
+        says that the reader hands it to the kernels' matrix products unchanged --
+        an object of the kernels that stands for ``out`` with a factor per row
+        still to be applied."""
         if pending is not None:
             pending.add_into(residual)
         self.forward(residual, out)
+        return out
 
 
 class PositionEncoding(Part):
@@ -117,6 +122,11 @@ class Mixer(Part):
     block hands it to the next norm, which may add and normalise in one kernel).
     """
 
+    # True: ``forward`` passes ``x`` on to ``kernels.linear`` / ``linear_swiglu`` / ``linear_partial``
+    # and reads it in no other way, so the block may hand it a norm output whose factor per row
+    # those products apply themselves.
+    accepts_scaled_rows = False
+
     def cache_need(self):
         return None
 
@@ -127,6 +137,8 @@ class Mixer(Part):
 class FeedForward(Part):
     """Per-token transformation; adds its result into ``residual`` (or returns it
     pending, as a mixer may)."""
+
+    accepts_scaled_rows = False      # as for a mixer
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         raise NotImplementedError

@@ -38,10 +38,10 @@ class PreNormBlock(Block):
 
     def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
         x = ctx.workspace.get("block.normed", tuple(residual.shape), self.runtime.dtype)
-        self.mixer_norm.forward_fused(residual, pending, x)
-        pending = self.mixer.forward(x, residual, ctx, cache)
-        self.feed_forward_norm.forward_fused(residual, pending, x)
-        return self.feed_forward.forward(x, residual, ctx)
+        normed = self.mixer_norm.forward_fused(residual, pending, x, self.mixer.accepts_scaled_rows)
+        pending = self.mixer.forward(x if normed is None else normed, residual, ctx, cache)
+        normed = self.feed_forward_norm.forward_fused(residual, pending, x, self.feed_forward.accepts_scaled_rows)
+        return self.feed_forward.forward(x if normed is None else normed, residual, ctx)
 
 
 register_block("prenorm", PreNormBlock, replace=True)

@@ -38,6 +38,8 @@ class GatedMLP(FeedForward):
         self.gate_up = None if self.gate_up_interleaved is not None else torch.cat([gate, up], dim=0).contiguous()
         self.down = tensors[self.names["down_proj"]].contiguous()
 
+    accepts_scaled_rows = True       # x goes to the gate | up product and nowhere else
+
     def launch_key(self, ctx):
         return ()
 

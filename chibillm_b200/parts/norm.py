@@ -34,13 +34,18 @@ class RMSNorm(Norm):
                                          self.spec.weight_offset, out.view(-1, n))
 
 
-    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor) -> None:
+    def forward_fused(self, residual: torch.Tensor, pending, out: torch.Tensor, scaled_ok: bool = False):
         k = self.runtime.kernels
-        fused = getattr(k, "reduce_residual_rmsnorm", None)
-        if pending is None or fused is None or residual.shape[-1] != self.spec.size \
-                or not hasattr(pending, "partial"):
-            return super().forward_fused(residual, pending, out)
-        fused(pending, residual, self.weight, self.spec.eps, self.spec.weight_offset, out)
+        if pending is not None and residual.shape[-1] == self.spec.size:
+            if hasattr(pending, "finish_with_norm"):
+                # a product of many rows that has not run yet: it writes the norm's output itself
+                return pending.finish_with_norm(residual, self.weight, self.spec.eps, self.spec.weight_offset,
+                                                out, scaled_ok)
+            fused = getattr(k, "reduce_residual_rmsnorm", None)
+            if fused is not None and hasattr(pending, "partial"):
+                fused(pending, residual, self.weight, self.spec.eps, self.spec.weight_offset, out)
+                return out
+        return super().forward_fused(residual, pending, out, scaled_ok)
 
 
 register_norm("rmsnorm", RMSNorm, replace=True)

@@ -357,6 +357,58 @@ def test_linear_shares_out_a_thin_last_round(k, ref, M, N, K):
     k.check_error_word()
 
 
+@pytest.mark.parametrize("M,hidden,K,wide", [(300, 512, 384, 768), (130, 256, 1024, 512), (2000, 1024, 520, 2560)])
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_linear_folds_the_norm_that_follows(k, ref, M, hidden, K, wide, wdtype):
+    """Many rows: the product that completes the residual also writes the RMSNorm of
+    the new residual up to each row's factor, and the products that read it (plain
+    and with SwiGLU) apply the factor to their sums; any other reader has it
+    applied in place."""
+    from chibillm_b200.kernels.ops import ScaledRows
+    x = rnd(M, K, dtype=torch.bfloat16, seed=50)
+    w = rnd(hidden, K, dtype=torch.bfloat16, seed=51, scale=0.05)
+    res = rnd(M, hidden, seed=52, scale=3.0)
+    nw = (1 + 0.1 * rnd(hidden, seed=53)).to(wdtype)
+    eps, offset = 1e-5, 0.25
+    exp_res = torch.empty_like(res)
+    ref.linear(x, w, exp_res, residual=res)
+    exp_normed = torch.empty(M, hidden, dtype=torch.float32, device="cuda")
+    ref.rmsnorm(exp_res, nw, eps, offset, exp_normed)
+
+    normed = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scaled = k.linear_residual_norm(x, w, res, nw, eps, offset, normed)
+    assert isinstance(scaled, ScaledRows), "the kernel refused shapes it is made for"
+    close(res, exp_res, torch.float32, "residual", rel=2e-5)
+    # the product that reads it
+    w2 = rnd(wide, hidden, dtype=torch.bfloat16, seed=54, scale=0.05)
+    out = torch.full((M, wide), float("nan"), dtype=torch.bfloat16, device="cuda")
+    before = k.launches
+    k.linear(scaled, w2, out)
+    assert k.launches == before + 1, "the factor was not applied by the product itself"
+    exp = torch.empty(M, wide, dtype=torch.float32, device="cuda")
+    ref.linear(exp_normed, w2, exp)
+    close(out, exp, torch.bfloat16, "product of rows with a factor", rel=1.2e-2)
+    # ... with SwiGLU
+    gate = rnd(wide // 2, hidden, dtype=torch.bfloat16, seed=55, scale=0.05)
+    up = rnd(wide // 2, hidden, dtype=torch.bfloat16, seed=56, scale=0.05)
+    act = torch.full((M, wide // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert k.linear_swiglu(scaled, k.interleave_gate_up(gate, up), act)
+    gu = torch.empty(M, wide, dtype=torch.float32, device="cuda")
+    ref.linear(exp_normed, torch.cat([gate, up]), gu)
+    exp_act = torch.empty(M, wide // 2, dtype=torch.float32, device="cuda")
+    ref.swiglu(gu, exp_act)
+    close(act, exp_act, torch.bfloat16, "SwiGLU of rows with a factor", rel=1.2e-2)
+    # a reader that is no product (here: a product the kernel for many rows does not take)
+    narrow = rnd(40, hidden, dtype=torch.bfloat16, seed=57, scale=0.05)
+    out2 = torch.empty(M, 40, dtype=torch.float32, device="cuda")
+    k.linear(scaled, narrow, out2)
+    exp2 = torch.empty_like(out2)
+    ref.linear(exp_normed, narrow, exp2)
+    close(out2, exp2, torch.float32, "factor applied in place first", rel=1.2e-2)
+    close(normed, exp_normed, torch.bfloat16, "the norm's output after the factor", rel=8e-3)
+    k.check_error_word()
+
+
 def test_linear_falls_back_when_unaligned(k, ref):
     x = rnd(5, 100, dtype=torch.bfloat16, seed=34)      # K = 100 is no multiple of 8
     w = rnd(40, 100, dtype=torch.bfloat16, seed=35)
