@@ -58,11 +58,13 @@ def load_peaks():
         try:
             with open(path) as f:
                 obj = json.load(f)
-            peaks = {k: float(obj[k]) for k in ("hbm_gbs", "bf16_tflops") if k in obj}
-            peaks["bf16_tflops_sustained"] = float(obj.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
-            if len(peaks) == 3:
+            def number(v):
+                return float(v["value"]) if isinstance(v, dict) else float(v)
+            peaks = {k: number(obj[k]) for k in ("hbm_gbs", "bf16_tflops") if k in obj}
+            peaks["bf16_tflops_sustained"] = number(obj.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+            if len(peaks) == 3 and all(v > 0 for v in peaks.values()):
                 return peaks, "measured"
-        except (OSError, ValueError, KeyError):
+        except (OSError, ValueError, KeyError, TypeError, AttributeError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
 
