@@ -396,7 +396,8 @@ def main() -> int:
         },
         "prefill": {"value": round(args.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": args.prefill_tokens,
                     "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4)},
+                    "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+                    "frac_of_sustained": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops_sustained"], 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
