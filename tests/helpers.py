@@ -87,6 +87,9 @@ def trace_portions(requests: Dict[str, List[int]], seed: int = 0) -> List[dict]:
     return steps
 
 
+PORTIONS = [2, 3, 5, 8, 13, 21, 40]      # sizes of the prompt portions of a mixed trace
+
+
 def trace_mixed(requests: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4,
                 decode_tail: int = 12) -> List[dict]:
     """Up to ``max_live`` requests at a time: portions of some beside single
@@ -109,7 +112,7 @@ def trace_mixed(requests: Dict[str, List[int]], max_tokens: int, seed: int = 0, 
         for r in chosen:
             rid, ids, pos, prompt_len = r
             if pos < prompt_len:
-                n = min(rng.choice([2, 3, 5, 8, 13, 21, 40]), prompt_len - pos)
+                n = min(rng.choice(PORTIONS), prompt_len - pos)
             else:
                 n = 1
             entries.append({"id": rid, "tokens": ids[pos:pos + n], "want": list(range(n))})
