@@ -6,9 +6,14 @@ formulas (the file:line of the formula is cited in the function).  It shares no
 code with the package ``chibillm_b200``; it reads config.json and the
 safetensors file with the ``safetensors`` library.
 
-This file rests on the reference's formulas: the reference's kernels are Metal
-shaders and its host code drives them through an Objective-C++ context, so its
-model code cannot be run here to produce numbers to compare with.
+The reference's kernels are Metal shaders, which nothing here can run; its host
+model code is portable C++ and does run on a CPU behind a stand-in for the
+device layer.  tests/golden/make_goldens.py does that once for the tiny models
+A and B and keeps the logits and greedy tokens under tests/golden/;
+tests/test_reference_goldens.py compares this file (and the engine) with them.
+So the layer order, weight packing, head grouping, rotation convention, paging
+and tie rule of this file are checked against the reference's own code; the
+arithmetic inside each kernel rests on the formulas cited below.
 
 All arithmetic is in the dtype given (float32 by default, float64 for a
 tighter yardstick); weights are widened to it first.
