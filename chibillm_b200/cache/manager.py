@@ -258,6 +258,30 @@ class CacheManager:
         if status < 0:
             _raise(status, f"request {request_id!r}: ")
 
+    _COMMIT, _HOLD, _SETTLE, _ROLLBACK = 0, 1, 2, 3
+
+    def _advance(self, what: int, request_ids: Sequence[Hashable], lengths: Sequence[int]) -> None:
+        n = len(request_ids)
+        if n == 0:
+            return
+        ids = (ctypes.c_longlong * n)(*[self.number_of(r) for r in request_ids])
+        status = self._lib.chibi_cache_advance(self._handle, what, n, ids, _ints([int(v) for v in lengths]))
+        if status < 0:
+            _raise(status)
+
+    def commit_many(self, request_ids: Sequence[Hashable], new_lengths: Sequence[int], hold: bool = False) -> None:
+        """``commit`` for the requests of a step in one call.  With ``hold`` the
+        lengths advance but no window page is given back until ``settle_many``;
+        until then ``rollback_many`` can take the lengths back."""
+        self._advance(self._HOLD if hold else self._COMMIT, request_ids, new_lengths)
+
+    def settle_many(self, request_ids: Sequence[Hashable]) -> None:
+        self._advance(self._SETTLE, request_ids, [0] * len(request_ids))
+
+    def rollback_many(self, request_ids: Sequence[Hashable], old_lengths: Sequence[int]) -> None:
+        """Take held commits back; the pages stay with their requests."""
+        self._advance(self._ROLLBACK, request_ids, old_lengths)
+
     def release(self, request_id: Hashable) -> None:
         number = self._numbers.pop(request_id, None)
         if number is None:

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "chibi_cache_table": ([c_void_p, c_longlong, c_int, IP, c_int], c_int),
     "chibi_cache_reserve": ([c_void_p, c_longlong, c_int], c_int),
     "chibi_cache_commit": ([c_void_p, c_longlong, c_int], c_int),
+    "chibi_cache_advance": ([c_void_p, c_int, c_int, LP, IP], c_int),
     "chibi_cache_release": ([c_void_p, c_longlong], c_int),
     "chibi_cache_free_pages": ([c_void_p, c_int], c_int),
     "chibi_cache_free_slots": ([c_void_p], c_int),

@@ -70,6 +70,12 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
                     theirs.num_kv_heads, theirs.head_dim):
                 raise CacheError("invalid_configuration",
                                  f"run step {i} cannot read the cache of step {src}: shapes differ")
+            if mine.window != theirs.window:
+                # the owner's window decides which pages are given back; a reader that looks
+                # further back would meet pages that are gone
+                raise CacheError("invalid_configuration",
+                                 f"run step {i} (window {mine.window}) cannot read the cache of step {src} "
+                                 f"(window {theirs.window}): the windows differ")
             steps.append(("paged", steps[src][1], steps[src][2], False))
         elif isinstance(need, PagedKVNeed):
             name = group_name(need)

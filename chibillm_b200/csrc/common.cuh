@@ -112,15 +112,8 @@ __device__ __forceinline__ void prefetch_l2(const void* p)
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-// CHIBI_PDL=0 in the environment launches every kernel the ordinary way.
-inline bool pdl_enabled()
-{
-    static const bool on = [] {
-        const char* v = getenv("CHIBI_PDL");
-        return !(v && v[0] == '0');
-    }();
-    return on;
-}
+// Programmatic dependent launch is how every kernel but a step's first is launched.
+inline bool pdl_enabled() { return true; }
 
 // Launches with a thread-block cluster of (1, 1, cluster_z) CTAs when cluster_z > 1.
 // `ordered`: an ordinary launch, which starts only after everything before it in

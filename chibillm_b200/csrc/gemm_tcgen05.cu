@@ -950,7 +950,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 
 // ------------------------------------------------------------------ host side
 constexpr int STREAM_K_COUNTERS = 4096;
-__device__ int stream_k_counters[STREAM_K_COUNTERS];      // zero when loaded; every use leaves them zero
+// zero when loaded; every use that ends well leaves them zero (chibi_gemm_reset_stream_counters after one that did not)
+__device__ int stream_k_counters[STREAM_K_COUNTERS];
 static struct { float* scratch; long long floats; int fill_divisor; int* counters; } stream_k = { nullptr, 0, 4, nullptr };
 
 template <int BN, int STAGES>
@@ -981,7 +982,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 template <int BN, int STAGES>
 static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
-                                  int tiles_m, int tiles_n, cudaStream_t stream)
+                                  int tiles_m, int tiles_n, cudaStream_t stream, bool share_last_round = true)
 {
     constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4 + 12) * 8 + 16
         + 4 * EPILOGUE_STAGE_BYTES + 1024;
@@ -1005,7 +1006,8 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
     // filled round run faster, and adding up the partial sums costs 15 to 20 us: 4096 x 4096 with
     // 108 tiles left, 56 -> 63 us).
     const int rest = tiles % sms, kb = p.k_blocks_total;
-    if (stream_k.scratch && stream_k.counters && rest > 0 && rest * stream_k.fill_divisor <= sms && kb >= 16
+    if (share_last_round && stream_k.scratch && stream_k.counters && rest > 0
+        && rest * stream_k.fill_divisor <= sms && kb >= 16
         && rest * 4 <= STREAM_K_COUNTERS) {
         // CTAs to a tile: what the idle SMs allow, at most eight (the first CTA adds the others' sums
         // one after the other); head and helpers' runs of about the same length
@@ -1111,7 +1113,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
                          const float* residual, int M, int N, int K, long long x_stride,
                          long long w_stride, long long out_stride, long long res_stride,
                          float* scratch, long long scratch_floats, int* error, cudaStream_t stream,
-                         bool reduce)
+                         bool reduce, bool share_last_round = true)
 {
     if (M <= 0 || N <= 0)
         return CHIBI_OK;
@@ -1176,7 +1178,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         if (grid.y > 65535)
             return CHIBI_ERR_UNSUPPORTED;
         if (bn == 256)
-            status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
+            status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream, share_last_round);
         else if (bn == 128)
             status = launch_gemm<128, 4>(ma, mb, p, grid, stream);
         else
@@ -1225,6 +1227,16 @@ CHIBI_API int chibi_gemm_set_stream_scratch(float* scratch, long long floats)
     return CHIBI_OK;
 }
 
+// After a wait of the shared-out last round ran out (error word 15 or 16) its counters may be left
+// non-zero, and the next launch that shares out the same tiles would add sums that are not written
+// yet.  This puts them back to zero, in stream order.
+CHIBI_API int chibi_gemm_reset_stream_counters(cudaStream_t stream)
+{
+    if (!stream_k.counters)
+        return CHIBI_OK;
+    return (int)cudaMemsetAsync(stream_k.counters, 0, sizeof(int) * STREAM_K_COUNTERS, stream);
+}
+
 // How many CTAs share one tile's K range in chibi_gemm_bf16_fused (1 for M > 64).
 CHIBI_API int chibi_gemm_bf16_cluster_size(int M, int N, int K)
 {
@@ -1234,13 +1246,8 @@ CHIBI_API int chibi_gemm_bf16_cluster_size(int M, int N, int K)
     const int k_blocks = (K + TILE_K - 1) / TILE_K;
     const int resident = sm_count() * (M <= 16 ? 4 : 3);
     int size = tiles >= resident ? 1 : resident / tiles;
-    static const int cap = [] {
-        const char* v = getenv("CHIBI_MAX_CLUSTER");
-        const int n = v ? atoi(v) : 16;
-        return n < 1 ? 1 : (n > 16 ? 16 : n);
-    }();
-    if (size > cap)
-        size = cap;
+    if (size > 16)
+        size = 16;
     if (size > k_blocks / 2)
         size = k_blocks / 2;
     return size < 1 ? 1 : size;
@@ -1718,6 +1725,8 @@ CHIBI_API int chibi_gemm_bf16_noalloc(const void* x, const void* w, void* out, i
         }
         scratch = device_ptr[device];
     }
-    return chibi_gemm_bf16(x, w, out, out_type, residual, M, N, K, x_stride, w_stride, out_stride,
-                           res_stride, scratch, CHIBI_NOALLOC_SCRATCH_FLOATS, error, stream);
+    // every tile of a many-row product is computed whole here: the scratch and the counters that
+    // share out a last round of tiles belong to the engine's stream
+    return gemm_bf16_impl(x, w, out, out_type, residual, M, N, K, x_stride, w_stride, out_stride,
+                          res_stride, scratch, CHIBI_NOALLOC_SCRATCH_FLOATS, error, stream, true, false);
 }

@@ -24,6 +24,11 @@
 //    CHIBI_NOALLOC_SCRATCH_FLOATS; a larger product is refused with
 //    CHIBI_ERR_SCRATCH_LIMIT and nothing is launched.  chibi_error_string()
 //    turns a code into a sentence.
+//  * A product of more than 64 rows does not split K and uses no scratch at
+//    all; each of its tiles is computed whole by one CTA (the library's other
+//    entry points may share a last, sparse round of tiles among idle CTAs
+//    through scratch and counters that belong to the engine's stream; this
+//    entry point never touches those).
 //  * The first call on a device looks up the array's device address (once per
 //    device, with that device current).  Make that first call before any stream
 //    capture begins.

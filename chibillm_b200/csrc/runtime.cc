@@ -140,6 +140,7 @@ struct Update {
 
 struct Request {
     int length = 0;      // tokens whose keys are stored (committed)
+    int settled = 0;     // length up to which window pages have been given back (<= length)
     int reserved = 0;    // tokens that the tables have room for
     int slot = -1;
     std::vector<std::vector<int>> tables;   // per group: logical block -> page, -1 once the window has passed it
@@ -215,7 +216,11 @@ public:
         return 0;
     }
     // The request now holds `new_length` tokens; pages that its windows have passed go back.
-    int commit(long long id, int new_length)
+    // With `hold` nothing is given back yet: the length can still be taken back by rollback()
+    // (a step whose result turns out to be unusable), until settle() makes it final.  The
+    // reference opens and closes a transaction on its state around every batch for the same
+    // purpose (src/model_state.h:86-99, src/qwen/qwen3_5_model_state.cc:284-370).
+    int commit(long long id, int new_length, bool hold = false)
     {
         Request* r = find(id);
         if (!r)
@@ -224,11 +229,20 @@ public:
             return fail(RT_INVALID_COMMIT, "length " + str(r->length) + " -> " + str(new_length) + ", reserved "
                                                + str(r->reserved));
         r->length = new_length;
+        return hold ? 0 : settle(id);
+    }
+    // Give back what the windows have passed at the current length.
+    int settle(long long id)
+    {
+        Request* r = find(id);
+        if (!r)
+            return fail(RT_UNKNOWN_REQUEST, "request is not admitted");
+        r->settled = r->length;
         for (size_t g = 0; g < groups_.size(); ++g) {
             if (groups_[g].window < 0)
                 continue;
             std::vector<int>& table = r->tables[g];
-            const int dead = std::min(first_needed_block(new_length, groups_[g].window, groups_[g].page_size),
+            const int dead = std::min(first_needed_block(r->length, groups_[g].window, groups_[g].page_size),
                                       static_cast<int>(table.size()));
             for (int i = 0; i < dead; ++i) {
                 if (table[i] >= 0) {
@@ -238,6 +252,19 @@ public:
                 }
             }
         }
+        return 0;
+    }
+    // Take a held commit back: the request holds `old_length` tokens again.  Pages stay
+    // reserved, so the same tokens can be run again at the same places.
+    int rollback(long long id, int old_length)
+    {
+        Request* r = find(id);
+        if (!r)
+            return fail(RT_UNKNOWN_REQUEST, "request is not admitted");
+        if (old_length < r->settled || old_length > r->length)
+            return fail(RT_INVALID_COMMIT, "rollback to " + str(old_length) + ": settled " + str(r->settled)
+                                               + ", length " + str(r->length));
+        r->length = old_length;
         return 0;
     }
     int release(long long id)
@@ -395,6 +422,25 @@ RT_API int chibi_cache_reserve(void* cache, long long id, int tokens)
 RT_API int chibi_cache_commit(void* cache, long long id, int new_length)
 {
     return static_cast<CacheManager*>(cache)->commit(id, new_length);
+}
+// A step's requests at once.  what: 0 commit, 1 commit and hold, 2 settle, 3 rollback
+// (`lengths` is unused for settle).  Stops at the first failure.
+RT_API int chibi_cache_advance(void* cache, int what, int count, const long long* ids, const int* lengths)
+{
+    CacheManager* m = static_cast<CacheManager*>(cache);
+    for (int i = 0; i < count; ++i) {
+        int st;
+        switch (what) {
+        case 0: st = m->commit(ids[i], lengths[i]); break;
+        case 1: st = m->commit(ids[i], lengths[i], true); break;
+        case 2: st = m->settle(ids[i]); break;
+        case 3: st = m->rollback(ids[i], lengths[i]); break;
+        default: return fail(RT_INVALID_CONFIGURATION, "chibi_cache_advance: unknown operation");
+        }
+        if (st < 0)
+            return st;
+    }
+    return 0;
 }
 RT_API int chibi_cache_release(void* cache, long long id) { return static_cast<CacheManager*>(cache)->release(id); }
 RT_API int chibi_cache_free_pages(void* cache, int group)

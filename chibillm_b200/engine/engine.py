@@ -1,7 +1,9 @@
 """The generation loop: schedule, build the batch, run the step, sample,
 complete (src/inference_engine.cc:73-118), with the reference's rule that a
 failure after scheduling aborts the batch and leaves the sequences untouched,
-so the same batch can be retried (src/inference_engine.cc:140-151).
+so the same batch can be retried (src/inference_engine.cc:140-151).  A step
+is run provisionally: the cache's lengths and the fixed-size state of its
+requests are taken back if anything fails before the tokens are accepted.
 
 Requests that the scheduler defers wait in a first-in first-out queue; a later
 request never passes a deferred one (src/serving_runtime.cc:243-247).
@@ -129,11 +131,17 @@ class InferenceEngine:
             entries = []
             for item in batch.items:
                 seq = sched.sequences[item.seq_id]
+                if item.first != self.runner.length(item.seq_id):
+                    raise SchedulerError("inconsistent_batch",
+                                         f"request {item.seq_id!r}: the scheduler continues at token {item.first}, "
+                                         f"the cache holds {self.runner.length(item.seq_id)}")
                 toks = seq.slice(item.first, item.count)
                 entries.append(StepEntry(item.seq_id, toks, [item.count - 1] if item.sample else []))
             kernels = self.runner.runtime.kernels
             deferred_check = hasattr(kernels, "error_word_async")
-            logits = self.runner.step(entries, check=not deferred_check)
+            # provisional: the cache's lengths advance now (a step launched ahead builds on them),
+            # but they are taken back if the error word or the tokens say that the step failed
+            logits = self.runner.step(entries, check=not deferred_check, provisional=True)
             if deferred_check:
                 kernels.error_word_async()        # read together with the tokens, below
             sampled: List[int] = []
@@ -149,13 +157,18 @@ class InferenceEngine:
                 sampled = pending.result()
                 if ahead:
                     self.runner.confirm_ahead(sampled)
-            elif deferred_check:
+            elif deferred_check and self.runner.runtime.device.type == "cuda":
                 torch.cuda.current_stream().synchronize()
             if deferred_check:
                 kernels.check_error_copy()
             if len(sampled) != batch.sample_count:
                 raise SchedulerError("result_count_mismatch")
+            self.runner.settle_step()
         except Exception:
+            # the step did not happen: lengths and state go back, a step launched ahead is
+            # dropped, the scheduler's reservations are cancelled; pages stay, so a retry
+            # runs the same tokens at the same places (src/inference_engine.cc:140-151)
+            self.runner.rollback_step()
             sched.abort(batch.batch_id)
             raise
         now = time.perf_counter()

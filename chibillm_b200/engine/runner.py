@@ -84,6 +84,9 @@ class ModelRunner:
         self.steps_ahead_used = 0
         self.steps_ahead_dropped = 0
         self._has_state = any(isinstance(v, FixedStateView) for v in self.storage.views)
+        # the last step, if it was run with ``provisional=True`` and is neither settled nor rolled
+        # back yet: (request ids, lengths before, saved rows of the fixed-size state)
+        self._provisional: Optional[tuple] = None
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -127,6 +130,9 @@ class ModelRunner:
         self.storage.zero_state_slot(rc.state_slot)
 
     def end(self, request_id: Hashable) -> None:
+        if self._ahead is not None and request_id in self._ahead["ids"]:
+            self._ahead = None              # its logits belong to a request that no longer exists
+            self.steps_ahead_dropped += 1
         self.cache.release(request_id)
 
     def has(self, request_id: Hashable) -> bool:
@@ -323,17 +329,59 @@ class ModelRunner:
         if self._ahead is not None:
             self._ahead["tokens"] = [int(t) for t in tokens]
 
-    @staticmethod
-    def _matches_ahead(ahead: dict, entries: Sequence[StepEntry]) -> bool:
+    def _matches_ahead(self, ahead: dict, entries: Sequence[StepEntry]) -> bool:
         if ahead["tokens"] is None or len(entries) != len(ahead["ids"]):
             return False
-        for e, rid, tok in zip(entries, ahead["ids"], ahead["tokens"]):
+        for e, rid, tok, new_len in zip(entries, ahead["ids"], ahead["tokens"], ahead["ctx_lens"]):
             if e.request_id != rid or len(e.tokens) != 1 or int(e.tokens[0]) != tok or list(e.want) != [0]:
+                return False
+            if not self.cache.has(rid) or self.cache.length(rid) + 1 != new_len:
                 return False
         return True
 
+    # ------------------------------------------------------------ taking a step back
+    def _begin_provisional(self, entries: Sequence[StepEntry], old_lengths: Sequence[int]) -> None:
+        saved = []
+        if self._has_state:
+            slots = torch.tensor([self.cache.state_slot(e.request_id) for e in entries], dtype=torch.long,
+                                 device=self.runtime.device)
+            for view in self.storage.views:
+                if isinstance(view, FixedStateView):
+                    for t in view.arrays.values():
+                        saved.append((t, slots, t.index_select(0, slots)))
+        self._provisional = ([e.request_id for e in entries], list(old_lengths), saved)
+
+    def settle_step(self) -> None:
+        """The last provisional step stands: windows give their pages back, the
+        saved state is dropped."""
+        if self._provisional is None:
+            return
+        ids, _, _ = self._provisional
+        self._provisional = None
+        self.cache.settle_many([r for r in ids if self.cache.has(r)])
+
+    def rollback_step(self) -> None:
+        """The last provisional step did not happen: its requests hold what they
+        held before it (lengths and fixed-size state; pages stay reserved, and what
+        the step wrote past the old lengths is written again by the retry), so the
+        same entries can be run again with the same result
+        (src/qwen/qwen3_5_model_state.cc:284-370 is the reference's counterpart for
+        its recurrent state).  A step launched ahead of it is dropped."""
+        if self._ahead is not None:
+            self._ahead = None
+            self.steps_ahead_dropped += 1
+        if self._provisional is None:
+            return
+        ids, old_lengths, saved = self._provisional
+        self._provisional = None
+        for array, slots, rows in saved:
+            array.index_copy_(0, slots, rows)
+        keep = [(r, n) for r, n in zip(ids, old_lengths) if self.cache.has(r)]
+        self.cache.rollback_many([r for r, _ in keep], [n for _, n in keep])
+
     # ------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], check: bool = True,
+             provisional: bool = False) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device in
         the order of the entries and of their ``want`` (None if nothing is
         wanted).  The array is reused by the next step.
@@ -341,14 +389,23 @@ class ModelRunner:
         A step in which every request brings one token is captured into a CUDA
         graph the second time its shape is seen and replayed from then on; what
         changes between replays (tokens, positions, lengths, table updates,
-        wanted rows) travels in the packed metadata array."""
+        wanted rows) travels in the packed metadata array.
+
+        With ``provisional`` the caller decides afterwards whether the step
+        counts: ``settle_step()`` or ``rollback_step()`` must follow before the
+        next provisional step (the generation loop reads the device's error word
+        and the sampled tokens in between)."""
         if not entries:
             raise BatchError("a step needs at least one entry")
+        if self._provisional is not None:
+            raise BatchError("the last step is neither settled nor rolled back")
         ahead, self._ahead = self._ahead, None
         if ahead is not None:
             if self._matches_ahead(ahead, entries):
-                for e, new_len in zip(entries, ahead["ctx_lens"]):
-                    self.cache.commit(e.request_id, new_len)
+                ids = [e.request_id for e in entries]
+                if provisional:
+                    self._begin_provisional(entries, [n - 1 for n in ahead["ctx_lens"]])
+                self.cache.commit_many(ids, ahead["ctx_lens"], hold=provisional)
                 self.steps_run += 1
                 self.steps_ahead_used += 1
                 if check and hasattr(self.runtime.kernels, "check_error_word"):
@@ -366,13 +423,19 @@ class ModelRunner:
                 self.admit(e.request_id)
         decode_only = all(len(e.tokens) == 1 for e in entries)
         ctx, update_views, fixed = self._build_context(entries, decode_only and self.use_graphs)
+        if provisional:
+            self._begin_provisional(entries, [n - q for n, q in zip(ctx.ctx_lens, ctx.q_lens)])
         key = self._graph_key(ctx) if fixed else None
-        if key is not None:
-            logits = self._step_with_graph(key, ctx, update_views)
-        else:
-            logits = self._run_model(ctx, update_views)
-        for e, new_len in zip(entries, ctx.ctx_lens):
-            self.cache.commit(e.request_id, new_len)
+        try:
+            if key is not None:
+                logits = self._step_with_graph(key, ctx, update_views)
+            else:
+                logits = self._run_model(ctx, update_views)
+        except Exception:
+            if provisional:
+                self.rollback_step()        # lengths are unchanged; the fixed-size state goes back
+            raise
+        self.cache.commit_many([e.request_id for e in entries], ctx.ctx_lens, hold=provisional)
         self.steps_run += 1
         if check and hasattr(self.runtime.kernels, "check_error_word"):
             self.runtime.kernels.check_error_word()

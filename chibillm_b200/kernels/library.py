@@ -30,6 +30,7 @@ _SIGNATURES = {
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_gemm_bf16_cluster_size": [I, I, I],
         "chibi_gemm_set_stream_scratch": [P, L],
+        "chibi_gemm_reset_stream_counters": [P],
         "chibi_gemm_bf16_norm_parts": [I],
         "chibi_gemm_bf16_rows": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P, P, P],
         "chibi_scale_rows": [P, L, I, L, P, I, F, I, P],

@@ -61,10 +61,22 @@ class PendingSum:
     """The partial sums [splits, M, N] (32-bit) of a matrix product whose K range
     was split over CTAs, waiting for a kernel that adds them up together with what
     follows the product (residual and norm, SwiGLU, per-head norm and rotation).
-    It must be consumed before two more split products are started."""
+    The sums live in one of two scratch arrays that split products take in turn,
+    so a pending sum is good until two more split products have been started; one
+    that is read later than that raises instead of handing out another product's
+    numbers."""
 
-    def __init__(self, kernels, partial: torch.Tensor, splits: int, M: int, N: int):
-        self.kernels, self.partial, self.splits, self.M, self.N = kernels, partial, splits, M, N
+    def __init__(self, kernels, partial: torch.Tensor, splits: int, M: int, N: int,
+                 turn: int = 0, stamp: Optional[int] = None):
+        self.kernels, self._partial, self.splits, self.M, self.N = kernels, partial, splits, M, N
+        self._turn, self._stamp = turn, stamp
+
+    @property
+    def partial(self) -> torch.Tensor:
+        if self._stamp is not None and self.kernels._partial_stamps[self._turn] != self._stamp:
+            raise KernelError("the partial sums of this product have been overwritten: a pending product "
+                              "must be consumed before two more split products are started")
+        return self._partial
 
     def add_into(self, residual: torch.Tensor) -> None:
         """residual += the product."""
@@ -148,6 +160,7 @@ class CudaKernels:
         self.use_tcgen05_attention = True
         self._partial_bufs = [None, None]
         self._partial_turn = 0
+        self._partial_stamps = [0, 0]     # how often each of the two arrays has been handed out
         self._ssq_bufs = [None, None]
         self._ssq_turn = 0
         # Many rows: the product that completes the residual also writes the following RMSNorm's
@@ -281,6 +294,8 @@ class CudaKernels:
     def _raise_for(self, code: int) -> None:
         if code:
             self.error.zero_()
+            # a shared-out round of tiles that gave up may have left its counters non-zero
+            self.lib.chibi_gemm_reset_stream_counters(self._stream())
             what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",
                     3: "a page id outside the pool (attention)",
                     4: "a block-table update outside the table",
@@ -288,6 +303,8 @@ class CudaKernels:
                     12: "a wait that ran out (matrix product: tensor-core issuer)",
                     13: "a wait that ran out (matrix product: epilogue)",
                     14: "a wait that ran out (matrix product: accumulator hand-over)",
+                    15: "a wait that ran out (matrix product: partial sums of a shared tile)",
+                    16: "a wait that ran out (matrix product: slot of a shared tile)",
                     **{c: f"a wait that ran out (tcgen05 attention, point {c})" for c in range(21, 30)}}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
@@ -323,6 +340,7 @@ class CudaKernels:
 
     def _partial_buffer(self, floats: int) -> torch.Tensor:
         self._partial_turn ^= 1
+        self._partial_stamps[self._partial_turn] += 1
         buf = self._partial_bufs[self._partial_turn]
         if buf is None or buf.numel() < floats:
             buf = torch.empty(max(floats, 1 << 21), dtype=torch.float32, device=self.device)
@@ -356,7 +374,8 @@ class CudaKernels:
         _check(status, "linear (split product)")
         self.launches += 1
         self.tensor_core_calls += 1
-        return PendingSum(self, buf[:splits * M * N].view(splits, M, N), splits, M, N)
+        return PendingSum(self, buf[:splits * M * N].view(splits, M, N), splits, M, N,
+                          self._partial_turn, self._partial_stamps[self._partial_turn])
 
     @staticmethod
     def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> Optional[torch.Tensor]:

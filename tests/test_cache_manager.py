@@ -219,3 +219,41 @@ def test_device_mirror_follows_the_tables(seed):
                     rc = m.get(rid)
                     for idx, page in enumerate(rc.tables[g]):
                         assert mirror[g].get((rc.state_slot, idx), -1) == page
+
+
+def test_a_reader_of_another_steps_cache_must_share_its_window():
+    """A run step that reads another step's cache lives by the owner's window:
+    pages behind it are given back.  A reader with another window is refused when
+    the cache is planned, not in the middle of a generation."""
+    from chibillm_b200.cache.manager import CacheError
+    from chibillm_b200.cache.storage import plan_cache
+    from chibillm_b200.parts import PagedKVNeed
+    owner = PagedKVNeed(2, 16, 24)
+    plan = plan_cache([owner, PagedKVNeed(2, 16, 24)], [None, 0], 8, 256)
+    assert plan.steps[1][3] is False and len(plan.groups) == 1
+    for reader in (PagedKVNeed(2, 16, None), PagedKVNeed(2, 16, 48), PagedKVNeed(2, 16, 8)):
+        with pytest.raises(CacheError) as e:
+            plan_cache([owner, reader], [None, 0], 8, 256)
+        assert "windows differ" in str(e.value)
+
+
+def test_held_commits_settle_and_roll_back():
+    from chibillm_b200.cache.manager import CacheError, CacheManager, GroupLayout
+    m = CacheManager([GroupLayout("w", 1, 16, 10, 4, 16, 1, 0), GroupLayout("all", 1, 16, None, 4, 16, 1, 0)], 2)
+    m.admit("a")
+    m.reserve("a", 12)
+    m.commit_many(["a"], [12])
+    free = m.free_pages("w")
+    m.reserve("a", 30)
+    m.commit_many(["a"], [30], hold=True)
+    assert m.length("a") == 30 and m.free_pages("w") == free - 5, "a held commit gives nothing back"
+    m.rollback_many(["a"], [12])
+    assert m.length("a") == 12
+    m.commit_many(["a"], [30], hold=True)
+    m.settle_many(["a"])
+    assert m.free_pages("w") > free - 5
+    with pytest.raises(CacheError):
+        m.rollback_many(["a"], [12])            # settled: the pages behind the window are gone
+    m.check_invariants()
+    m.release("a")
+    assert m.free_pages("w") == 16 and m.free_pages("all") == 16

@@ -558,10 +558,12 @@ def test_attention_tcgen05_prompts(k, ref, nq, nkv, d, window, page):
 
 @pytest.mark.parametrize("nq,nkv,window,append", [(32, 8, None, True), (8, 2, 100, True), (6, 1, None, True),
                                                   (8, 2, None, False)])
-def test_decode_attention_from_partial_sums(k, nq, nkv, window, append):
+def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
     """Decode attention that finishes the q | k | v product itself (sum of the
     partial sums, per-head norm, rotation, append of the new key and value) against
-    the two kernels it replaces, on sequences that end at and next to page edges."""
+    the plain restatement of product, norm, rotation, append and attention, and
+    against the two kernels it replaces, on sequences that end at and next to page
+    edges."""
     d, page, K = 128, 16, 1024
     seq_ctx = [1, 16, 17, 129, 300, 640, 33, 48]
     S = len(seq_ctx)
@@ -596,3 +598,41 @@ def test_decode_attention_from_partial_sums(k, nq, nkv, window, append):
     close(got, exp, torch.bfloat16, "decode attention from the partial sums", rel=8e-3)
     close(kc2, kc, torch.bfloat16, "key cache", rel=8e-3)
     assert torch.equal(vc2, vc), "value cache"
+
+    # the plain restatement, in 32-bit from the same bfloat16 inputs
+    kc3, vc3 = kc0.clone(), vc0.clone()
+    qkv = torch.empty(S, width, dtype=torch.float32, device="cuda")
+    ref.linear(x, w, qkv)
+    q3 = torch.empty(S, nq * d, dtype=torch.float32, device="cuda")
+    ref.qk_norm_rope_append(qkv, q3, kc3 if append else None, vc3 if append else None, qn, kn, inv_freq, d, 1e-6,
+                            0.0, positions, seq_of_token, table if append else None, nq, nkv, d, page)
+    plain = torch.empty(S, nq * d, dtype=torch.float32, device="cuda")
+    ref.attention(q3, kc3, vc3, plain, table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, scale,
+                  window, 1, max(seq_ctx))
+    close(got, plain, torch.bfloat16, "decode attention from the partial sums vs the plain restatement", rel=1.2e-2)
+    close(kc2, kc3, torch.bfloat16, "key cache vs the plain restatement", rel=8e-3)
+    assert torch.equal(vc2, vc3), "value cache vs the plain restatement"
+
+
+def test_a_pending_sum_that_was_overwritten_is_refused(k):
+    """Split products take two scratch arrays in turn: the third one started
+    writes over the first one's sums, and reading those then must raise."""
+    from chibillm_b200.kernels.ops import KernelError
+    k.fuse_split_products = True
+    x = rnd(4, 4096, dtype=torch.bfloat16, seed=90)
+    w = rnd(1024, 4096, dtype=torch.bfloat16, seed=91, scale=0.05)
+    res = rnd(4, 1024, seed=92)
+    first = k.linear_partial(x, w)
+    second = k.linear_partial(x, w)
+    assert first is not None and second is not None and first.splits > 1
+    good = res.clone()
+    first.add_into(good)                    # two products outstanding: both are still good
+    third = k.linear_partial(x, w)
+    with pytest.raises(KernelError) as e:
+        first.add_into(res.clone())
+    assert "overwritten" in str(e.value)
+    a, b = res.clone(), res.clone()
+    second.add_into(a)
+    third.add_into(b)
+    assert torch.equal(a, good) and torch.equal(b, good)
+    k.check_error_word()
