@@ -17,11 +17,14 @@ class LLM:
     ``context_length`` is the most tokens (prompt plus output) of one request;
     ``kv_cache_tokens`` the size of the shared cache pool (default: enough for
     ``max_sequences`` requests of ``context_length``).  The option names are the
-    reference's command-line flags (src/cli_options.cc:13-25)."""
+    reference's command-line flags (src/cli_options.cc:13-25).  The defaults of
+    the scheduler are sized for a B200 (64 requests, steps of 4,096 tokens, prompt
+    portions of 1,024 while others wait or decode); the reference's own, sized for
+    a laptop GPU, are 4 requests, 128 tokens and 64 (src/scheduler.h:30-39)."""
 
     def __init__(self, model_dir: Optional[str], dtype: str = "bfloat16", device: str = "cuda:0",
                  context_length: int = 4096, kv_cache_tokens: Optional[int] = None,
-                 max_sequences: int = 4, max_batch_tokens: int = 512, prefill_chunk_tokens: int = 64,
+                 max_sequences: int = 64, max_batch_tokens: int = 4096, prefill_chunk_tokens: int = 1024,
                  page_size: int = KV_PAGE_SIZE, kernels=None, random_config: Optional[dict] = None,
                  random_seed: int = 0):
         if context_length <= 0 or context_length % page_size != 0:

@@ -10,6 +10,8 @@ request never passes a deferred one (src/serving_runtime.cc:243-247).
 """
 from __future__ import annotations
 
+import math
+import sys
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -24,36 +26,87 @@ from .scheduler import (ADMITTED, DEFERRED, TOO_LARGE, Scheduler, SchedulerConfi
                         Sequence, SequenceUpdate)
 
 
+def latency_summary(samples: List[float]) -> dict:
+    """samples, p50 and p95 with the reference's rank rule: the value at
+    ceil(fraction * n) - 1 of the sorted samples (src/generation_metrics.cc:12-23)."""
+    if not samples:
+        return {"samples": 0, "p50_seconds": None, "p95_seconds": None}
+    ordered = sorted(samples)
+    pick = lambda fraction: ordered[max(0, math.ceil(fraction * len(ordered)) - 1)]
+    return {"samples": len(ordered), "p50_seconds": pick(0.50), "p95_seconds": pick(0.95)}
+
+
 @dataclass
 class RequestMetrics:
     """Per-request figures with the reference's definitions
-    (src/generation_metrics.cc:71-90): prefill tok/s = processed prompt tokens /
+    (src/generation_metrics.cc:40-90): prefill tok/s = processed prompt tokens /
     seconds of the steps that processed them; decode tok/s = (output tokens - 1) /
-    (time of the last token - time of the first)."""
+    (time of the last token - time of the first); decode-step latencies are the
+    durations of the steps that decoded a token of this request, inter-token
+    latencies the gaps between its tokens."""
 
     prompt_tokens: int = 0
     output_tokens: int = 0
+    requested_tokens: int = 0
+    processed_prompt_tokens: int = 0
+    prefill_batches: int = 0
     prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
     submitted_at: float = 0.0
+    admitted_at: Optional[float] = None
     first_token_at: Optional[float] = None
     last_token_at: Optional[float] = None
     finish_reason: Optional[str] = None
+    decode_samples: List[float] = field(default_factory=list)
+    inter_token_samples: List[float] = field(default_factory=list)
+
+    def record_batch(self, prefill: bool, prompt_count: int, seconds: float) -> None:
+        if prefill:
+            self.prefill_batches += 1
+            self.processed_prompt_tokens += prompt_count
+            self.prefill_seconds += seconds
+        else:
+            self.decode_seconds += seconds
+            self.decode_samples.append(seconds)
+
+    def record_token(self, at: float) -> None:
+        if self.last_token_at is not None:
+            self.inter_token_samples.append(at - self.last_token_at)
+        else:
+            self.first_token_at = at
+        self.last_token_at = at
+        self.output_tokens += 1
 
     def as_dict(self) -> dict:
         ttft = None if self.first_token_at is None else self.first_token_at - self.submitted_at
+        engine_ttft = None
+        if self.first_token_at is not None and self.admitted_at is not None:
+            engine_ttft = self.first_token_at - self.admitted_at
         decode_tps = None
         if self.output_tokens > 1 and self.last_token_at and self.last_token_at > self.first_token_at:
             decode_tps = (self.output_tokens - 1) / (self.last_token_at - self.first_token_at)
+        end_to_end = None if self.last_token_at is None else self.last_token_at - self.submitted_at
         return {
             "schema_version": 1,
-            "prompt_tokens": self.prompt_tokens,
-            "output_tokens": self.output_tokens,
-            "prefill_seconds": self.prefill_seconds,
-            "prefill_tokens_per_second": (self.prompt_tokens / self.prefill_seconds
-                                          if self.prefill_seconds > 0 else None),
-            "time_to_first_token_seconds": ttft,
-            "decode_tokens_per_second": decode_tps,
+            "type": "request",
+            "stop_reason": self.finish_reason,
             "finish_reason": self.finish_reason,
+            "prompt_tokens": self.prompt_tokens,
+            "cached_prompt_tokens": 0,
+            "processed_prompt_tokens": self.processed_prompt_tokens,
+            "output_tokens": self.output_tokens,
+            "requested_tokens": self.requested_tokens,
+            "prefill_batches": self.prefill_batches,
+            "prefill_seconds": self.prefill_seconds,
+            "decode_engine_seconds": self.decode_seconds,
+            "engine_ttft_seconds": engine_ttft,
+            "time_to_first_token_seconds": ttft,
+            "end_to_end_seconds": end_to_end,
+            "prefill_tokens_per_second": (self.processed_prompt_tokens / self.prefill_seconds
+                                          if self.prefill_seconds > 0 else None),
+            "decode_tokens_per_second": decode_tps,
+            "decode_step": latency_summary(self.decode_samples),
+            "inter_token": latency_summary(self.inter_token_samples),
         }
 
 
@@ -69,6 +122,7 @@ class InferenceEngine:
                                    on_admit=runner.admit, on_release=runner.end)
         self.sampler = Sampler(runner.runtime)
         self.run_ahead = True          # launch the next decode step before this one's tokens are on the host
+        self.profile_passes = False    # with a profiler on the kernels: one [cuda-pass] line per step
         self.pending: Deque[Sequence] = deque()
         self.metrics: Dict[Hashable, RequestMetrics] = {}
         self._keys: Dict[Hashable, int] = {}
@@ -91,7 +145,8 @@ class InferenceEngine:
             raise SchedulerError("duplicate_sequence_id", repr(seq_id))
         if not self.scheduler.fits_cache(seq):
             raise SchedulerError("sequence_too_large", f"request {seq_id!r} can never fit the cache")
-        self.metrics[seq_id] = RequestMetrics(prompt_tokens=len(prompt), submitted_at=time.perf_counter())
+        self.metrics[seq_id] = RequestMetrics(prompt_tokens=len(prompt), requested_tokens=params.max_new_tokens,
+                                              submitted_at=time.perf_counter())
         self._keys[seq_id] = self._next_key if sample_key is None else int(sample_key)
         self._next_key += 1
         self.pending.append(seq)
@@ -103,6 +158,7 @@ class InferenceEngine:
             result = self.scheduler.try_add(self.pending[0])
             if result != ADMITTED:
                 break
+            self.metrics[self.pending[0].id].admitted_at = time.perf_counter()
             self.pending.popleft()
 
     def is_finished(self) -> bool:
@@ -126,6 +182,9 @@ class InferenceEngine:
     def step(self) -> List[SequenceUpdate]:
         sched = self.scheduler
         batch = sched.schedule()
+        profiler = getattr(self.runner.runtime.kernels, "profiler", None)
+        if profiler is not None:
+            profiler.begin_step()
         started = time.perf_counter()
         try:
             entries = []
@@ -171,16 +230,20 @@ class InferenceEngine:
             self.runner.rollback_step()
             sched.abort(batch.batch_id)
             raise
+        if profiler is not None:
+            record = profiler.end_step(sum(item.count for item in batch.items))
+            if self.profile_passes:
+                print("[cuda-pass] tokens={tokens} launches={launches} encode_ms={encode_ms:.3f} "
+                      "wait_ms={wait_ms:.3f} gpu_ms={gpu_ms:.3f} total_ms={total_ms:.3f}".format(**record),
+                      file=sys.stderr)
         now = time.perf_counter()
         for item in batch.items:
-            if sched.sequences[item.seq_id].status == "waiting":
-                self.metrics[item.seq_id].prefill_seconds += now - started
+            prefill = sched.sequences[item.seq_id].status == "waiting"
+            self.metrics[item.seq_id].record_batch(prefill, item.count if prefill else 0, now - started)
         updates = sched.complete(batch.batch_id, sampled)
         for u in updates:
             m = self.metrics[u.seq_id]
-            m.output_tokens += 1
-            m.first_token_at = m.first_token_at or now
-            m.last_token_at = now
+            m.record_token(now)
             m.finish_reason = u.finish_reason
         self._admit_pending()
         return updates

@@ -146,6 +146,7 @@ class CudaKernels:
         if self.device.type != "cuda":
             raise KernelError(f"device '{device}' is not a CUDA device; chibillm_b200 has no CPU path")
         self.lib = library.load("chibi_kernels")
+        self.profiler = None        # a LaunchProfiler while the profiling mode is on
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host: Optional[torch.Tensor] = None
         self.launches = 0           # kernels of this package launched so far
@@ -183,6 +184,25 @@ class CudaKernels:
                                                        device=self.device)
             scratch = _STREAM_SCRATCH[self.device]
             _check(self.lib.chibi_gemm_set_stream_scratch(_ptr(scratch), scratch.numel()), "stream scratch")
+
+    def enable_profiling(self):
+        """Time every launch from now on (kernels/profile.py); returns the profiler.
+        Steps are no longer captured into CUDA graphs while this is on."""
+        from .profile import LaunchProfiler, ProfiledLibrary
+        if self.profiler is None:
+            self.profiler = LaunchProfiler()
+            self.lib = ProfiledLibrary(self.lib, self.profiler)
+            for libs in (self._attention_libs, self._attention_tc_libs):
+                for d in list(libs):
+                    libs[d] = ProfiledLibrary(libs[d], self.profiler)
+            self.supports_graphs = False
+        return self.profiler
+
+    def _profiled(self, lib):
+        if self.profiler is None:
+            return lib
+        from .profile import ProfiledLibrary
+        return ProfiledLibrary(lib, self.profiler)
 
     def share_out_last_round(self, enabled: bool) -> None:
         """Whether the many-row product deals the K blocks of a thinly filled last round
@@ -646,7 +666,7 @@ class CudaKernels:
             lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
             if lib.chibi_attention_mma_head_dim() != d:
                 raise KernelError(f"the attention library for head size {d} was built for another size")
-            self._attention_libs[d] = lib
+            lib = self._attention_libs[d] = self._profiled(lib)
         seqs = ctx_len.numel()
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
         if mode & 2 and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
@@ -657,7 +677,7 @@ class CudaKernels:
                 tc = library.load("chibi_attention_tc", (f"CHIBI_HEAD_DIM={d}",))
                 if tc.chibi_attention_tc_head_dim() != d:
                     raise KernelError(f"the tcgen05 attention library for head size {d} was built for another size")
-                self._attention_tc_libs[d] = tc
+                tc = self._attention_tc_libs[d] = self._profiled(tc)
             status = tc.chibi_attention_prefill_tc(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
@@ -711,7 +731,7 @@ class CudaKernels:
         lib = self._attention_libs.get(d)
         if lib is None:
             lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
-            self._attention_libs[d] = lib
+            lib = self._attention_libs[d] = self._profiled(lib)
         splits = self.decode_attention_splits(seqs, nq, nkv, max_ctx_len)
         scratch = self._scratch(seqs * nq * splits * (d + 2)) if splits > 1 else None
         status = lib.chibi_attention_decode_fused(

@@ -107,9 +107,12 @@ def write_random_model(config_object: dict, out_dir: str, seed: int,
     return out_dir
 
 
-def bind_random_weights(model, seed: int, runtime: Runtime) -> None:
-    """Fill a model with random weights made on its device (no file)."""
+def bind_random_weights(model, seed: int, runtime: Runtime, stored: torch.dtype = torch.bfloat16) -> None:
+    """Fill a model with random weights made on its device (no file): the values
+    that ``write_random_model`` would store as ``stored`` with the same seed,
+    widened to the run's type as the loader widens a checkpoint's."""
     tensors = {}
     for spec in model.expected_tensors(None):
-        tensors[spec.name] = random_tensor(spec, seed, runtime.dtype, runtime.device)
+        t = random_tensor(spec, seed, stored, runtime.device)
+        tensors[spec.name] = t if t.dtype in (runtime.dtype, torch.int32) else t.to(runtime.dtype)
     model.bind(tensors)

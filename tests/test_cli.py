@@ -93,3 +93,58 @@ def test_missing_model_is_reported(tmp_path):
     options = cli.parse_cli_options([str(tmp_path / "nowhere")])
     assert cli.run(options, io.StringIO(""), io.StringIO(), err) == 1
     assert "failed to load model from" in err.getvalue()
+
+
+def test_scheduler_options_and_their_derivation(tmp_path):
+    o = cli.parse_cli_options(["--max-seqs", "3", "--max-batch-tokens", "16", "--prefill-chunk", "8",
+                               "--kv-block-size", "8", "--kv-blocks", "40", "--context-length", "264",
+                               "--random", "cfg.json", "--weights-seed", "7", "--device", "cuda:1", "--profile"])
+    assert (o.max_seqs, o.max_batch_tokens, o.prefill_chunk, o.kv_block_size, o.kv_blocks) == (3, 16, 8, 8, 40)
+    assert (o.random_config, o.weights_seed, o.device, o.profile, o.profile_passes) == \
+           ("cfg.json", 7, "cuda:1", True, False)
+    # what is left open follows the number of sequences (one: the reference's conversation values)
+    d = cli.parse_cli_options([]).derived()
+    assert (d.max_seqs, d.max_batch_tokens, d.prefill_chunk) == (1, 512, 64)
+    d = cli.parse_cli_options(["--max-seqs", "8"]).derived()
+    assert (d.max_batch_tokens, d.prefill_chunk) == (4096, 1024)
+    prompts = tmp_path / "p.txt"
+    prompts.write_text("1 2 3\n\n# a comment\n4,5\n")
+    assert cli.parse_cli_options(["--prompt-file", str(prompts), "--prompt-ids", "6"]).prompts == \
+           [[1, 2, 3], [4, 5], [6]]
+    for argv, message in ((["--max-seqs", "0"], "invalid count for --max-seqs"),
+                          (["--kv-block-size", "12", "--context-length", "64"], "invalid token limit"),
+                          (["--device", "cpu"], "invalid device"),
+                          (["--random", "c.json", "folder"], "not both"),
+                          (["--prompt-file", str(tmp_path / "none")], "failed to read prompt file")):
+        with pytest.raises(cli.CliError) as e:
+            cli.parse_cli_options(argv)
+        assert message in str(e.value)
+
+
+def test_several_prompts_run_together_on_cpu(tmp_path):
+    """Four prompts submitted at once with room for three: portions of 8 beside
+    decoded tokens, the fourth waits for a finish.  Greedy tokens equal the plain
+    implementation's; with --random the folder is replaced by a configuration."""
+    import tiny_configs
+    folder = helpers.make_model_dir(tmp_path, "B", seed=1)
+    config, weights = plain_qwen3.read_model_folder(folder)
+    prompts = list(helpers.random_requests(384, [1, 7, 23, 40], seed=1).values())
+    expected = [plain_qwen3.generate_greedy(config, weights, p, 6) for p in prompts]
+    argv = ["--context-length", "64", "--max-tokens", "6", "--max-seqs", "3", "--max-batch-tokens", "16",
+            "--prefill-chunk", "8", "--dtype", "float32", "--ignore-eos", "--no-stream"]
+    for p in prompts:
+        argv += ["--prompt-ids", ",".join(map(str, p))]
+    out, err = io.StringIO(), io.StringIO()
+    assert cli.run(cli.parse_cli_options(argv + [folder]), io.StringIO(""), out, err,
+                   kernels=ReferenceKernels(), device="cpu") == 0, err.getvalue()
+    assert [[int(t) for t in line.split()] for line in out.getvalue().splitlines()] == expected
+    assert "sequences 3 | batch 16 tok | prompt portion 8 tok | pages 12 x 16 tok" in err.getvalue()
+    assert err.getvalue().count("[stop] len_limit") == 4
+
+    # the same weights from a configuration file and a seed
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny_configs.get("B")))
+    out2 = io.StringIO()
+    assert cli.run(cli.parse_cli_options(argv + ["--random", str(cfg_path), "--weights-seed", "1"]),
+                   io.StringIO(""), out2, io.StringIO(), kernels=ReferenceKernels(), device="cpu") == 0
+    assert out2.getvalue() == out.getvalue()

@@ -611,7 +611,7 @@ def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
                   window, 1, max(seq_ctx))
     close(got, plain, torch.bfloat16, "decode attention from the partial sums vs the plain restatement", rel=1.2e-2)
     close(kc2, kc3, torch.bfloat16, "key cache vs the plain restatement", rel=8e-3)
-    assert torch.equal(vc2, vc3), "value cache vs the plain restatement"
+    close(vc2, vc3, torch.bfloat16, "value cache vs the plain restatement", rel=8e-3)
 
 
 def test_a_pending_sum_that_was_overwritten_is_refused(k):
