@@ -18,3 +18,13 @@ def pytest_configure(config):
 def pytest_collection_modifyitems(config, items):
     # the test of the allocation-free entry point runs after every other test
     items.sort(key=lambda item: 1 if "test_zz_" in item.nodeid else 0)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How close the compared logits were, next to the limit each was held to."""
+    import helpers
+    if not helpers.MEASURED:
+        return
+    terminalreporter.section("worst |diff| / max |logit| of the compared logits")
+    for what, (worst, tol) in sorted(helpers.MEASURED.items(), key=lambda kv: -kv[1][0] / kv[1][1]):
+        terminalreporter.write_line(f"{worst:9.2e}  of limit {tol:7.1e}  ({100 * worst / tol:5.1f} %)  {what}")

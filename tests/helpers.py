@@ -164,6 +164,10 @@ def run_trace(runner, steps: List[dict]) -> Dict[str, torch.Tensor]:
     return result
 
 
+# what every comparison of logits measured: name -> (worst |diff| / max |logit|, limit)
+MEASURED: Dict[str, Tuple[float, float]] = {}
+
+
 def assert_logits_close(actual: Dict[str, torch.Tensor], expected: Dict[str, torch.Tensor], tol: float,
                         what: str) -> None:
     for rid, ref in expected.items():
@@ -173,6 +177,7 @@ def assert_logits_close(actual: Dict[str, torch.Tensor], expected: Dict[str, tor
         scale = float(ref.abs().max())
         diff = (got - ref).abs()
         worst = float(diff.max())
+        MEASURED[what] = (max(MEASURED.get(what, (0.0, tol))[0], worst / max(scale, 1e-30)), tol)
         if worst > tol * scale:
             per_pos = diff.max(dim=1).values
             first = int(torch.nonzero(per_pos > tol * scale)[0, 0])

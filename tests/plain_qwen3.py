@@ -58,7 +58,7 @@ def layer_windows(config: dict) -> List[Optional[int]]:
 # ------------------------------------------------------------------ parts
 def embedding(table: torch.Tensor, token_ids: List[int]) -> torch.Tensor:
     """h0[t, :] = float(E[token[t], :])  (src/metal/kernels/tensor_ops.metal:12-24)."""
-    return table[torch.tensor(token_ids, dtype=torch.long)]
+    return table[torch.tensor(token_ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -89,7 +89,8 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
     (src/metal/kernels/tensor_ops.metal:168-197)."""
     d = x.shape[-1]
     half = d // 2
-    inv_freq = rope_inverse_frequencies(theta, d)
+    inv_freq = rope_inverse_frequencies(theta, d).to(x.device)
+    positions = positions.to(x.device)
     if x.dtype == torch.float64:
         angle = positions.to(torch.float64)[:, None] * inv_freq.to(torch.float64)[None, :]
     else:
@@ -111,7 +112,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     group = nq // nkv
     scale = 1.0 / math.sqrt(float(d))
     out = torch.empty_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= pos[None, :] > pos[:, None] - window
@@ -140,7 +141,7 @@ def attention_block(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, co
     v = linear(x, w[prefix + "self_attn.v_proj.weight"]).view(T, nkv, d)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], eps)
-    positions = torch.arange(T)
+    positions = torch.arange(T, device=h.device)
     q = rope(q, positions, config["rope_theta"])
     k = rope(k, positions, config["rope_theta"])
     att = causal_attention(q, k, v, window).reshape(T, nq * d)
@@ -167,9 +168,11 @@ def final_logits(h: torch.Tensor, w: Dict[str, torch.Tensor], config: dict) -> t
 
 
 # ------------------------------------------------------------------ whole model
-def forward(config: dict, weights: Dict[str, torch.Tensor], token_ids: List[int]) -> torch.Tensor:
-    """Logits [T, vocab] of every position of one sequence
-    (layer order: src/qwen/qwen_layer.cc:124-146)."""
+def forward(config: dict, weights: Dict[str, torch.Tensor], token_ids: List[int],
+            rows: Optional[List[int]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of every position of one sequence, or of the positions
+    ``rows`` only (layer order: src/qwen/qwen_layer.cc:124-146).  Runs on the
+    device that holds the weights."""
     config = dict(config)
     config.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
     windows = layer_windows(config)
@@ -178,6 +181,8 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], token_ids: List[int]
         prefix = f"model.layers.{layer}."
         h = attention_block(h, weights, prefix, config, windows[layer])
         h = mlp_block(h, weights, prefix, config)
+    if rows is not None:
+        h = h[torch.tensor(rows, dtype=torch.long, device=h.device)]
     return final_logits(h, weights, config)
 
 
@@ -195,4 +200,41 @@ def generate_greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: List
         nxt = greedy(forward(config, weights, ids)[-1])
         out.append(nxt)
         ids.append(nxt)
+    return out
+
+
+# ------------------------------------------------------------------ sampling at a temperature
+def sample_uniform(seed: int, request_key: int, index: int) -> float:
+    """The number in [0, 1) that decides the ``index``-th generated token of a
+    request: 24 bits of a SHA-256 over "seed/key/index".  The reference has no
+    sampling at a temperature (src/server.cc:128-132 refuses one); this restates
+    the engine's rule so that both draw the same number."""
+    import hashlib
+    digest = hashlib.sha256(f"{seed}/{request_key}/{index}".encode()).digest()
+    return (int.from_bytes(digest[:8], "little") >> 40) / float(1 << 24)
+
+
+def sample_at_temperature(logits_row: torch.Tensor, temperature: float, u: float) -> int:
+    """p_i = exp((x_i - max) / T); the first id whose running sum of p, in id
+    order, exceeds u * sum(p).  Sums in 64-bit so that this side adds no
+    rounding of its own."""
+    if not temperature > 0.0:
+        return greedy(logits_row)
+    x = logits_row.double()
+    p = torch.exp((x - x.max()) / temperature)
+    cdf = torch.cumsum(p, dim=0)
+    target = u * float(cdf[-1])
+    idx = int(torch.searchsorted(cdf, torch.tensor(target, dtype=torch.float64), right=True))
+    return min(idx, x.numel() - 1)
+
+
+def generate_sampled(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], steps: int,
+                     temperature: float, seed: int, request_key: int) -> List[int]:
+    ids = list(prompt)
+    out = []
+    for index in range(steps):
+        row = forward(config, weights, ids, rows=[len(ids) - 1])[0]
+        tok = sample_at_temperature(row, temperature, sample_uniform(seed, request_key, index))
+        out.append(tok)
+        ids.append(tok)
     return out

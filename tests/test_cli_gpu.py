@@ -45,7 +45,7 @@ def test_four_prompts_through_the_scheduler(tmp_path):
         assert r["processed_prompt_tokens"] == r["prompt_tokens"]
         assert r["decode_step"]["samples"] == 11 and r["inter_token"]["samples"] == 11
         assert 0 < r["decode_step"]["p50_seconds"] <= r["decode_step"]["p95_seconds"]
-    assert records[3]["prefill_batches"] >= 5        # 40 tokens in portions of 8
+    assert records[3]["prefill_batches"] >= 3        # 40 tokens under a budget of 16 a step
 
     # the same model from its configuration and seed, bfloat16, one after the other
     cfg_path = tmp_path / "config.json"

@@ -1,16 +1,20 @@
 """Layer sizes of real checkpoints (Qwen3-0.6B and slices of Qwen3-8B and Qwen3-14B: head size
-128, vocabulary 151,936, tied or untied output) with random weights and two
-layers: the bfloat16 engine against the 32-bit engine, whole prompts against
-portions and decoded tokens, and a long context whose decode steps are replayed
-from CUDA graphs.  These sizes take the tensor-core kernels (tcgen05 products
-with split K ranges, tensor-core attention) that the tiny configurations do
-not reach."""
+128, vocabulary 151,936, tied or untied output) with random weights and one or
+two layers, against the plain implementation run on the GPU in true 32-bit: the
+32-bit engine and the bfloat16 engine, whole prompts, portions and decoded
+tokens, four live requests with reused pages, and contexts of 8,200 and 16,400
+tokens.  These sizes take the tensor-core kernels (tcgen05 products with split
+K ranges, tensor-core attention, decode attention over many key ranges) that
+the tiny configurations do not reach."""
 import pytest
 import torch
 
 import helpers
+import plain_qwen3
 
 pytestmark = pytest.mark.gpu
+
+DEV = torch.device("cuda:0")
 
 
 def base(**kw):
@@ -33,13 +37,50 @@ SHAPES = {
 }
 
 
+@pytest.fixture(autouse=True)
+def true_32_bit():
+    """The plain implementation's products on the GPU are 32-bit FMA, no TF32."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    yield
+    torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def plain_weights(cfg, seed):
+    """name -> 32-bit tensor on the GPU: the values that the engine's
+    ``from_random`` makes for this configuration and seed (stored as bfloat16)."""
+    from chibillm_b200.config.registry import find_architecture
+    from chibillm_b200.engine.model import DecoderModel
+    from chibillm_b200.parts.base import Runtime
+    from chibillm_b200.weights import random_tensors
+    arch = find_architecture(cfg)
+    model = DecoderModel(arch.model_spec(arch.read_config(cfg)), Runtime(DEV, torch.bfloat16, None))
+    return {name: t.float() for name, t in random_tensors(model, seed, torch.bfloat16, DEV)}
+
+
+def plain_rows(cfg, weights, reqs, want):
+    return {rid: plain_qwen3.forward(cfg, weights, ids, rows=want[rid]).float().cpu() for rid, ids in reqs.items()}
+
+
+def free():
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
 @pytest.mark.parametrize("shape", list(SHAPES))
-def test_bfloat16_engine_against_32_bit_engine(shape):
+def test_engines_against_the_plain_implementation(shape):
+    from chibillm_b200.engine.batch import StepEntry
     from chibillm_b200.engine.runner import ModelRunner
     cfg = SHAPES[shape]
     reqs = helpers.random_requests(cfg["vocab_size"], [300, 70, 1, 129], seed=3)
     # only a few places are wanted: a row of logits is 600 KB
     want = {rid: sorted({0, len(ids) // 2, len(ids) - 1}) for rid, ids in reqs.items()}
+    weights = plain_weights(cfg, 5)
+    ref = plain_rows(cfg, weights, reqs, want)
+    del weights
+    free()
 
     def run(dtype, trace_fn):
         runner = ModelRunner.from_random(cfg, seed=5, dtype=dtype, page_size=16, pool_tokens=1024, max_requests=4)
@@ -49,7 +90,6 @@ def test_bfloat16_engine_against_32_bit_engine(shape):
             fed = 0
             for portion in trace_fn(ids):
                 places = [w - fed for w in want[rid] if fed <= w < fed + len(portion)]
-                from chibillm_b200.engine.batch import StepEntry
                 logits = runner.step([StepEntry(rid, portion, places)])
                 for k, w in enumerate(places):
                     rows[fed + w] = logits[k].float().cpu().clone()
@@ -58,7 +98,7 @@ def test_bfloat16_engine_against_32_bit_engine(shape):
             out[rid] = torch.stack([rows[w] for w in want[rid]])
         replays = runner.graph_replays
         del runner
-        torch.cuda.empty_cache()
+        free()
         return out, replays
 
     whole = lambda ids: [ids]
@@ -68,15 +108,71 @@ def test_bfloat16_engine_against_32_bit_engine(shape):
         parts = [ids[:head // 2], ids[head // 2:head]] if head > 1 else [ids[:head]]
         return [p for p in parts if p] + [[t] for t in ids[head:]]
 
-    ref32, _ = run("float32", whole)
+    f32_whole, _ = run("float32", whole)
+    helpers.assert_logits_close(f32_whole, ref, helpers.TOL["float32"], f"{shape} float32 whole vs plain")
+    f32_cut, _ = run("float32", cut)
+    helpers.assert_logits_close(f32_cut, ref, helpers.TOL["float32"], f"{shape} float32 cut vs plain")
     bf_whole, _ = run("bfloat16", whole)
+    helpers.assert_logits_close(bf_whole, ref, helpers.TOL["bfloat16"], f"{shape} bfloat16 whole vs plain")
     bf_cut, replays = run("bfloat16", cut)
     assert replays > 0, "decode steps were not replayed from a graph"
-    f32_cut, _ = run("float32", cut)
-    helpers.assert_logits_close(f32_cut, ref32, helpers.TOL["float32"], f"{shape} float32 cut vs whole")
-    helpers.assert_logits_close(bf_whole, ref32, helpers.TOL["bfloat16"], f"{shape} bfloat16 vs float32")
-    helpers.assert_logits_close(bf_cut, ref32, helpers.TOL["bfloat16"], f"{shape} bfloat16 cut vs float32")
+    helpers.assert_logits_close(bf_cut, ref, helpers.TOL["bfloat16"], f"{shape} bfloat16 cut vs plain")
     helpers.assert_logits_close(bf_cut, bf_whole, helpers.TOL_SAME_DTYPE["bfloat16"], f"{shape} bfloat16 cut vs whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_at_the_8b_layer_sizes(dtype):
+    """Four live requests at the Qwen3-8B layer sizes: portions of some beside
+    decoded tokens of others, a pool so small that pages are used again, every
+    position's logits against the plain implementation."""
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = dict(SHAPES["8B"], num_hidden_layers=1)
+    reqs = helpers.random_requests(cfg["vocab_size"], [60, 90, 20, 70, 33, 64], seed=4)
+    weights = plain_weights(cfg, 7)
+    ref = {rid: plain_qwen3.forward(cfg, weights, ids).float().cpu() for rid, ids in reqs.items()}
+    del weights
+    free()
+    pool = 256
+    trace = helpers.trace_mixed(reqs, pool, seed=6)
+    assert helpers.peak_tokens(trace) <= pool < sum(helpers.round64(len(v)) for v in reqs.values())
+    assert any(len(s["entries"]) == 4 for s in trace)
+    runner = ModelRunner.from_random(cfg, seed=7, dtype=dtype, page_size=16, pool_tokens=pool, max_requests=4)
+    runner.storage.poison()
+    got = helpers.run_trace(runner, trace)
+    helpers.assert_logits_close(got, ref, helpers.TOL[dtype], f"8B sizes, mixed, {dtype}")
+    runner.cache.check_invariants()
+    assert not runner.cache.requests
+    del runner
+    free()
+
+
+@pytest.mark.parametrize("shape,held,dtype", [("14B", 8200, "float32"), ("14B", 8200, "bfloat16"),
+                                              ("8B", 16400, "bfloat16")])
+def test_long_contexts_against_the_plain_implementation(shape, held, dtype):
+    """One layer at the Qwen3-14B sizes (five query heads to a kv head) holding
+    8,200 tokens, and at the 8B sizes holding 16,400, then eight decoded tokens:
+    block tables of over a thousand pages and decode attention over dozens of key
+    ranges, against the plain implementation."""
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    cfg = dict(SHAPES[shape], num_hidden_layers=1)
+    ids = helpers.random_requests(cfg["vocab_size"], [held + 8], seed=21)["r0"]
+    prompt_rows = [0, held // 2 + 3, held - 1]
+    want = prompt_rows + list(range(held, held + 8))
+    weights = plain_weights(cfg, 9)
+    ref = {"a": plain_qwen3.forward(cfg, weights, ids, rows=want).float().cpu()}
+    del weights
+    free()
+    runner = ModelRunner.from_random(cfg, seed=9, dtype=dtype, page_size=16, pool_tokens=held + 64, max_requests=2)
+    runner.storage.poison()
+    rows = [runner.step([StepEntry("a", ids[:held], prompt_rows)]).float().cpu().clone()]
+    for t in ids[held:]:
+        rows.append(runner.step([StepEntry("a", [t], [0])]).float().cpu().clone())
+    runner.runtime.kernels.check_error_word()
+    got = {"a": torch.cat(rows)}
+    helpers.assert_logits_close(got, ref, helpers.TOL[dtype], f"{shape} sizes, {held} tokens held, {dtype}")
+    del runner
+    free()
 
 
 def test_long_context_decode():
