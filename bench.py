@@ -200,12 +200,15 @@ def measure_decode(runner, sampler, batch, ctx_start, steps, warmup, vocab, tag)
             "mean_ctx": mean_ctx}
 
 
-def measure_prefill(runner, tokens_n, vocab, repeats=3):
+def measure_prefill(runner, tokens_n, vocab, repeats=7):
+    """A prompt of ``tokens_n`` tokens in one step, timed on the device: the
+    median of ``repeats`` runs after one that warms up (and the fastest, for the
+    record).  Every run has other token ids; its weights (tens of GB) do not fit L2."""
     import torch
     from chibillm_b200.engine.batch import StepEntry
 
     g = torch.Generator().manual_seed(2)
-    best = None
+    times = []
     for r in range(repeats + 1):
         ids = torch.randint(0, vocab, (tokens_n,), generator=g).tolist()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -215,17 +218,20 @@ def measure_prefill(runner, tokens_n, vocab, repeats=3):
         end.record()
         torch.cuda.synchronize()
         runner.end("prefill")
-        ms = start.elapsed_time(end)
         if r > 0:                          # the first run warms up
-            best = ms if best is None else min(best, ms)
+            times.append(start.elapsed_time(end))
     runner.runtime.kernels.check_error_word()
-    return best
+    return statistics.median(times), min(times)
 
 
 def measure_e2e(llm, batch, prompt_len, steps, warmup, vocab):
     """The same decode steps through the public entry point: every step takes
     host token ids (the packed batch goes to the device from pinned memory) and
-    returns the sampled ids to the host."""
+    returns the sampled ids to the host.  The timed region holds the device work
+    of exactly ``steps`` steps: the engine launches a step ahead of the host
+    wherever the next step is foretold, so the last warm-up step is kept from
+    doing that, and the requests' token limit ends them with the last timed step
+    (a limit is foretold: nothing is launched past it)."""
     import torch
     from chibillm_b200.sampling import SamplingParams
 
@@ -233,11 +239,14 @@ def measure_e2e(llm, batch, prompt_len, steps, warmup, vocab):
     engine = llm.engine
     for i in range(batch):
         prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
-        engine.add(("e2e", i), prompt, SamplingParams(max_new_tokens=warmup + steps + 8, ignore_eos=True))
+        # the prompt's last step yields token 1; then `warmup` and `steps` decode steps
+        engine.add(("e2e", i), prompt, SamplingParams(max_new_tokens=1 + warmup + steps, ignore_eos=True))
     while any(s.status == "waiting" for s in engine.scheduler.sequences.values()):
         engine.step()
-    for _ in range(warmup):
+    for w in range(warmup):
+        engine.run_ahead = w != warmup - 1
         engine.step()
+    engine.run_ahead = True
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     produced = 0
@@ -245,14 +254,15 @@ def measure_e2e(llm, batch, prompt_len, steps, warmup, vocab):
         produced += len(engine.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    assert engine.is_finished() and produced == batch * steps
     h2d = llm.runner.last_meta_bytes
+    ahead = llm.runner.steps_ahead_used
     for i in range(batch):
-        engine.cancel(("e2e", i))
         engine.remove(("e2e", i))
-    return {"tok_s": produced / dt, "h2d": h2d, "d2h": batch * 4 + 4}
+    return {"tok_s": produced / dt, "h2d": h2d, "d2h": batch * 4 + 4, "steps_ahead": ahead}
 
 
-def measure_mixed(cfg, layers, full_layers, requests, shape):
+def measure_mixed(cfg, layers, full_layers, requests, shape, check_tokens=0):
     """Requests of mixed lengths through ``LLM.generate``: prompts of 16 to 2,048 uniform random
     tokens, 256 greedy tokens each (the end-of-sequence token ignored), all submitted at once, so
     that prompt portions run beside decoding requests.  Wall-clock time of the second of two runs."""
@@ -274,12 +284,35 @@ def measure_mixed(cfg, layers, full_layers, requests, shape):
         seconds = time.perf_counter() - t0
     generated = sum(len(o) for o in outs)
     prompt_tokens = sum(len(p) for p in prompts)
+    replays, ahead = llm.runner.graph_replays, llm.runner.steps_ahead_used
+    del llm
+    torch.cuda.empty_cache()
+    check = None
+    if check_tokens > 0:
+        # What was timed is tied to correct output: the 32-bit engine generates the first tokens of
+        # every request under two different budgets (other portions, other batches), which must
+        # agree with one another; the timed bfloat16 run's tokens are counted against them.
+        exact = []
+        for budget, chunk in ((2048, 2048), (640, 96)):
+            ref = chibillm_b200.LLM(None, dtype="float32", device="cuda:0", context_length=8192,
+                                    kv_cache_tokens=requests * (2048 + check_tokens + 64), max_sequences=requests,
+                                    max_batch_tokens=budget, prefill_chunk_tokens=chunk, random_config=cfg,
+                                    random_seed=0)
+            exact.append(ref.generate(prompts, max_tokens=check_tokens, ignore_eos=True))
+            del ref
+            torch.cuda.empty_cache()
+        same = sum(a == b for x, y in zip(*exact) for a, b in zip(x, y))
+        agree = sum(a == b for x, y in zip(outs, exact[0]) for a, b in zip(x, y))
+        first = sum(x[0] == y[0] for x, y in zip(outs, exact[0]))
+        total = requests * check_tokens
+        check = {"tokens_per_request": check_tokens, "fp32_budgets_agree": round(same / total, 4),
+                 "bf16_first_token_agrees": round(first / requests, 4), "bf16_tokens_agree": round(agree / total, 4)}
     return {"metric": f"generated tok/s, {requests} requests of mixed prompt lengths (Qwen3-{shape.split('-')[1].upper()} "
                       "shape, random bf16 weights)", "value": round(generated / seconds, 1), "unit": "tokens/s",
             "n_gpus": 1, "seconds": round(seconds, 3), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
             "total_tok_s": round((prompt_tokens + generated) / seconds, 1), "layers": layers,
             "layers_full": full_layers, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "steps_from_graphs": llm.runner.graph_replays, "steps_launched_ahead": llm.runner.steps_ahead_used}
+            "steps_from_graphs": replays, "steps_launched_ahead": ahead, "check": check}
 
 
 def main() -> int:
@@ -300,6 +333,9 @@ def main() -> int:
     ap.add_argument("--mixed-requests", type=int, default=0,
                     help="instead of the record: this many requests with prompts of 16 to 2,048 random tokens "
                          "and 256 new tokens each through the Python entry point; prints its own JSON line")
+    ap.add_argument("--check-tokens", type=int, default=0,
+                    help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
+                         "engine under two budgets and report how the runs agree")
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),
                     help="layer sizes (random weights); the contract's record is the default")
     args = ap.parse_args()
@@ -327,10 +363,11 @@ def main() -> int:
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
     if args.mixed_requests > 0:
-        print(json.dumps(measure_mixed(cfg, layers, full_layers, args.mixed_requests, args.shape)))
+        print(json.dumps(measure_mixed(cfg, layers, full_layers, args.mixed_requests, args.shape,
+                                       args.check_tokens)))
         return 0
     big = 64 if not args.skip_points else args.batch
-    per_request = args.prompt + args.warmup + max(args.steps, args.point_steps) + 64
+    per_request = max(args.prompt + args.warmup + args.steps, args.context) + 64
     pool = ((max(big, args.batch) * per_request + 63) // 64) * 64
     t_load = time.time()
     llm = chibillm_b200.LLM(None, dtype="bfloat16", device="cuda:0", context_length=args.context,
@@ -346,7 +383,7 @@ def main() -> int:
     torch.cuda.synchronize()
     load_s = time.time() - t_load
 
-    prefill_ms = measure_prefill(runner, args.prefill_tokens, vocab)
+    prefill_ms, prefill_best_ms = measure_prefill(runner, args.prefill_tokens, vocab)
     flops = prefill_flops(cfg, layers, args.prefill_tokens)
 
     clocks = ClockSampler()
@@ -356,12 +393,16 @@ def main() -> int:
 
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
-            r = measure_decode(runner, sampler, b, args.prompt, args.point_steps, args.warmup, vocab, f"p{b}_")
-            points[f"decode_b{b}"] = round(r["tok_s"], 1)
-            points[f"decode_b{b}_ms_per_step"] = round(r["ms_per_step"], 4)
+        # batch 1 and 64 at the same context, and the default batch further along the 2,048 -> 4,096
+        # range that the decoded tokens cross
+        later = [c for c in (3072, 4032) if args.prompt < c <= args.context - args.point_steps - args.warmup]
+        for b, held, key in [(1, args.prompt, "decode_b1"), (64, args.prompt, "decode_b64")] + \
+                [(args.batch, c, f"decode_b{args.batch}_ctx{c}") for c in later]:
+            r = measure_decode(runner, sampler, b, held, args.point_steps, args.warmup, vocab, key + "_")
+            points[key] = round(r["tok_s"], 1)
+            points[f"{key}_ms_per_step"] = round(r["ms_per_step"], 4)
             bytes_b = decode_step_bytes(cfg, layers, [r["mean_ctx"]] * b)
-            points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+            points[f"{key}_hbm_frac"] = round(bytes_b / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
 
     e2e = None
     if not args.skip_e2e:
@@ -395,7 +436,7 @@ def main() -> int:
             "peaks": peaks_src,
         },
         "prefill": {"value": round(args.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": args.prefill_tokens,
-                    "ms": round(prefill_ms, 3),
+                    "ms": round(prefill_ms, 3), "ms_best": round(prefill_best_ms, 3), "runs": 7, "stat": "median",
                     "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
                     "frac_of_sustained": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops_sustained"], 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -12,6 +12,8 @@
 //
 // Query token i of sequence s sits at position ctx_len[s] - q_len[s] + i and
 // sees keys max(0, pos - window + 1) .. pos (window 0 = all).
+#define CHIBI_UNIT attention_generic
+#define CHIBI_UNIT_ID 4
 #include "common.cuh"
 
 namespace chibi {

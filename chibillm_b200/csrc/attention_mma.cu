@@ -16,6 +16,8 @@
 // Scores are (q . k) * scale in 32-bit; softmax state (running max and sum) and
 // the output accumulator are 32-bit; probabilities are rounded to bfloat16 for
 // the second product.  A row sees keys max(0, pos - window + 1) .. pos.
+#define CHIBI_UNIT attention_mma
+#define CHIBI_UNIT_ID 6
 #include "common.cuh"
 
 #ifndef CHIBI_HEAD_DIM
@@ -484,6 +486,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         }
     }
     __syncthreads();
+    timeline_mark(0);                  // the query rows are in shared memory
     for (int i = resume; i < DEC_STAGES - 1; ++i)
         issue(i);
     uint32_t qf[KSTEPS][4];
@@ -510,6 +513,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         __syncwarp();
     }
     cp_async_wait<0>();
+    timeline_mark(1);                  // this warp has walked its tiles
     __syncthreads();
 
     // merge the warps: [warp][row][D + 1] outputs, then [warp][16] max and sum

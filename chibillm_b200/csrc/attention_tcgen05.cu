@@ -20,6 +20,8 @@
 //
 // The MMA of the next S tile is issued before the P V product of the current
 // one, so it runs while the softmax threads work.  All waits are bounded.
+#define CHIBI_UNIT attention_tcgen05
+#define CHIBI_UNIT_ID 7
 #include "common.cuh"
 #include "sm100.cuh"
 #include "tensor_map.cuh"

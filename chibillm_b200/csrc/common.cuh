@@ -93,13 +93,96 @@ __device__ __forceinline__ float block_max(float v, float* scratch)
 // before it touches global memory.  That hides the launch latency between the
 // many short kernels of a decode step.  Both instructions do nothing in a kernel
 // that was launched without the attribute.
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_now() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#ifndef CHIBI_TIMELINE
+__device__ __forceinline__ void timeline_mark(int) {}
+__device__ __forceinline__ void pdl_trigger() { pdl_trigger_now(); }
+__device__ __forceinline__ void pdl_wait() { pdl_wait_now(); }
 __device__ __forceinline__ void pdl_enter()
 {
     pdl_trigger();
     pdl_wait();
 }
+#else
+// A build with -DCHIBI_TIMELINE records, for every CTA of every kernel, when it started, when its
+// wait for the kernel before it ended and when its last warp left, with the SM it ran on
+// (%globaltimer, nanoseconds), into an array that the host hands over with
+// chibi_timeline_set_<file>.  The first statement of every kernel is pdl_trigger() or pdl_enter():
+// in this build they also open the record, and a local object closes it on every way out.  The
+// libraries of the product are built without the flag and contain none of this.
+struct TimelineRecord {
+    unsigned int unit, line, block, blocks, sm, pad;
+    unsigned long long start, waited, end;
+    unsigned long long marks[4];       // points inside a kernel (timeline_mark), latest arrival
+};
+static __device__ TimelineRecord* g_timeline_records;
+static __device__ unsigned int* g_timeline_count;
+static __device__ unsigned int g_timeline_capacity;
+
+__device__ __forceinline__ unsigned long long global_timer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned int& timeline_slot()
+{
+    __shared__ unsigned int slot;
+    return slot;
+}
+struct TimelineScope {
+    __device__ __forceinline__ TimelineScope(unsigned int line)
+    {
+        if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+            unsigned int s = 0xffffffffu;
+            if (g_timeline_records) {
+                s = atomicAdd(g_timeline_count, 1u);
+                if (s >= g_timeline_capacity) {
+                    s = 0xffffffffu;
+                } else {
+                    TimelineRecord& r = g_timeline_records[s];
+                    unsigned int sm;
+                    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+                    r.unit = CHIBI_UNIT_ID;
+                    r.line = line;
+                    r.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+                    r.blocks = gridDim.x * gridDim.y * gridDim.z;
+                    r.sm = sm;
+                    r.waited = 0;
+                    r.end = 0;
+                    r.marks[0] = r.marks[1] = r.marks[2] = r.marks[3] = 0;
+                    r.start = global_timer();
+                }
+            }
+            timeline_slot() = s;
+        }
+        __syncthreads();
+    }
+    __device__ __forceinline__ ~TimelineScope()
+    {
+        const unsigned int s = timeline_slot();
+        if (s != 0xffffffffu && (threadIdx.x & 31) == 0)
+            atomicMax(&g_timeline_records[s].end, global_timer());
+    }
+};
+__device__ __forceinline__ void timeline_waited()
+{
+    const unsigned int s = timeline_slot();
+    if (s != 0xffffffffu && (threadIdx.x & 31) == 0)
+        atomicCAS(&g_timeline_records[s].waited, 0ull, global_timer());
+}
+__device__ __forceinline__ void timeline_mark(int i)
+{
+    const unsigned int s = timeline_slot();
+    if (s != 0xffffffffu && (threadIdx.x & 31) == 0)
+        atomicMax(&g_timeline_records[s].marks[i], global_timer());
+}
+#define pdl_trigger() TimelineScope timeline_scope(__LINE__); pdl_trigger_now()
+#define pdl_wait() do { pdl_wait_now(); timeline_waited(); } while (0)
+#define pdl_enter() TimelineScope timeline_scope(__LINE__); pdl_trigger_now(); pdl_wait_now(); timeline_waited()
+#endif
 
 // Asks for the line at p in L2, and with it for the translation of its page.  A
 // kernel that was launched early does this for the addresses it will touch
@@ -224,3 +307,20 @@ inline int launch_status()
             return CHIBI_ERR_ARGUMENT;                                                             \
         }                                                                                          \
     } while (0)
+
+#ifdef CHIBI_TIMELINE
+#define CHIBI_TIMELINE_CAT2(a, b) a##b
+#define CHIBI_TIMELINE_CAT(a, b) CHIBI_TIMELINE_CAT2(a, b)
+// Where this file's kernels write their records (null: nowhere).  `count` is shared by all files
+// of all libraries, so the records of a step form one list.
+CHIBI_API int CHIBI_TIMELINE_CAT(chibi_timeline_set_, CHIBI_UNIT)(void* records, unsigned int* count,
+                                                                 unsigned int capacity)
+{
+    cudaError_t e = cudaMemcpyToSymbol(chibi::g_timeline_records, &records, sizeof(records));
+    if (e == cudaSuccess)
+        e = cudaMemcpyToSymbol(chibi::g_timeline_count, &count, sizeof(count));
+    if (e == cudaSuccess)
+        e = cudaMemcpyToSymbol(chibi::g_timeline_capacity, &capacity, sizeof(capacity));
+    return (int)e;
+}
+#endif

@@ -3,6 +3,8 @@
 // and activations are computed in 32-bit; element types of inputs, weights and
 // outputs are template parameters so the same code serves the bfloat16 and the
 // 32-bit engine.
+#define CHIBI_UNIT elementwise
+#define CHIBI_UNIT_ID 1
 #include "common.cuh"
 
 namespace chibi {

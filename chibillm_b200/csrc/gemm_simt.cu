@@ -5,6 +5,8 @@
 // bfloat16 path for shapes the tensor-core kernel refuses.  Every output
 // element is one thread's sequential sum over k = 0..K-1, so the result of a
 // row does not depend on how many rows the call has.
+#define CHIBI_UNIT gemm_simt
+#define CHIBI_UNIT_ID 2
 #include "common.cuh"
 
 namespace chibi {

@@ -16,6 +16,8 @@
 #include <mutex>
 #include <unordered_map>
 
+#define CHIBI_UNIT gemm_tcgen05
+#define CHIBI_UNIT_ID 3
 #include "common.cuh"
 #include "sm100.cuh"
 #include "tensor_map.cuh"
@@ -200,6 +202,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (kb_count > 0)
             ok = mbar_wait(tmem_full_bar, 0, p.error, 13);
         tcgen05_fence_after();
+        timeline_mark(0);              // the accumulator is complete
         constexpr int CHUNK = BN < 32 ? 16 : 32;
         if (p.cluster > 0) {
             // this CTA's partial sums -> shared memory, [column][row] (the stages are free now)
@@ -1543,6 +1546,7 @@ reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int sp
         *res = acc;
         s = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
     }
+    timeline_mark(0);                  // the sums are added up
     if (!w)
         return;
     s = block_sum(s, scratch);
@@ -1551,6 +1555,7 @@ reduce_residual_rmsnorm_cluster_kernel(const float* __restrict__ partial, int sp
     if ((int)threadIdx.x < parts)
         st_peer_shared_f32(smem_addr(&sums[cluster_cta_rank()]), threadIdx.x, s);
     cluster_sync();
+    timeline_mark(1);                  // the row's sum of squares is known
     float total = 0.f;
     for (int r = 0; r < parts; ++r)
         total += sums[r];

@@ -1,6 +1,8 @@
 // Token selection from 32-bit logits: argmax (ties go to the lowest id, as in
 // the reference's reduction, src/metal/kernels/sampling.metal:55-60,145-149)
 // and temperature sampling by inverse CDF with one given uniform per row.
+#define CHIBI_UNIT sampling
+#define CHIBI_UNIT_ID 5
 #include "common.cuh"
 
 namespace chibi {

@@ -139,13 +139,20 @@ class CudaKernels:
 
     name = "cuda"
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, timeline: bool = False):
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device is available; chibillm_b200 has no CPU path")
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise KernelError(f"device '{device}' is not a CUDA device; chibillm_b200 has no CPU path")
-        self.lib = library.load("chibi_kernels")
+        # timeline: libraries built with -DCHIBI_TIMELINE, whose CTAs note their times (kernels/timeline.py)
+        self.timeline = None
+        self._defines = ()
+        if timeline:
+            from .timeline import DEFINE, Timeline
+            self.timeline = Timeline(self.device)
+            self._defines = (DEFINE,)
+        self.lib = self._load("chibi_kernels")
         self.profiler = None        # a LaunchProfiler while the profiling mode is on
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host: Optional[torch.Tensor] = None
@@ -197,6 +204,12 @@ class CudaKernels:
                     libs[d] = ProfiledLibrary(libs[d], self.profiler)
             self.supports_graphs = False
         return self.profiler
+
+    def _load(self, name: str, defines=()):
+        lib = library.load(name, tuple(defines) + self._defines)
+        if self.timeline is not None:
+            self.timeline.attach(lib, name)
+        return lib
 
     def _profiled(self, lib):
         if self.profiler is None:
@@ -663,7 +676,7 @@ class CudaKernels:
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:
         lib = self._attention_libs.get(d)
         if lib is None:
-            lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
+            lib = self._load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
             if lib.chibi_attention_mma_head_dim() != d:
                 raise KernelError(f"the attention library for head size {d} was built for another size")
             lib = self._attention_libs[d] = self._profiled(lib)
@@ -674,7 +687,7 @@ class CudaKernels:
             # prompt portions on tcgen05; one-token sequences stay with the split-key kernel
             tc = self._attention_tc_libs.get(d)
             if tc is None:
-                tc = library.load("chibi_attention_tc", (f"CHIBI_HEAD_DIM={d}",))
+                tc = self._load("chibi_attention_tc", (f"CHIBI_HEAD_DIM={d}",))
                 if tc.chibi_attention_tc_head_dim() != d:
                     raise KernelError(f"the tcgen05 attention library for head size {d} was built for another size")
                 tc = self._attention_tc_libs[d] = self._profiled(tc)
@@ -730,7 +743,7 @@ class CudaKernels:
             raise KernelError("attention_decode_from_partial: shapes")
         lib = self._attention_libs.get(d)
         if lib is None:
-            lib = library.load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
+            lib = self._load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
             lib = self._attention_libs[d] = self._profiled(lib)
         splits = self.decode_attention_splits(seqs, nq, nkv, max_ctx_len)
         scratch = self._scratch(seqs * nq * splits * (d + 2)) if splits > 1 else None
