@@ -372,7 +372,8 @@ def main() -> int:
     t_load = time.time()
     llm = chibillm_b200.LLM(None, dtype="bfloat16", device="cuda:0", context_length=args.context,
                             kv_cache_tokens=pool, max_sequences=max(big, args.batch),
-                            max_batch_tokens=max(8192, args.prefill_tokens), prefill_chunk_tokens=2048,
+                            max_batch_tokens=max(8192, args.prefill_tokens, args.batch * args.prompt),
+                            prefill_chunk_tokens=max(2048, args.prompt),
                             random_config=cfg, random_seed=0)
     runner = llm.runner
     # the pool holds random values, so decoding from "filled" requests reads real numbers

@@ -17,10 +17,13 @@ import tiny_configs
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of
 # the request.  32-bit: orders of summation differ, nothing else.  bfloat16:
 # weights are exact (they are stored in bfloat16) but every activation between
-# kernels is rounded to 8 bits of mantissa.
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# kernels is rounded to 8 bits of mantissa.  The limits are about twice the worst
+# value that the suite measures on a B200 (the run prints every comparison's
+# worst value next to its limit): 6.4e-6 in 32-bit (Qwen3-14B layer sizes) and
+# 1.1e-2 in bfloat16 (the same sizes, portions against whole prompts).
+TOL = {"float32": 1.5e-5, "bfloat16": 2.5e-2}
 # bfloat16 runs against each other (same kernels, other batching)
-TOL_SAME_DTYPE = {"float32": 2e-5, "bfloat16": 3e-2}
+TOL_SAME_DTYPE = {"float32": 1.5e-5, "bfloat16": 2.5e-2}
 
 
 def make_model_dir(tmp_path, name: str, seed: int = 0, dtype=torch.bfloat16, **overrides) -> str:

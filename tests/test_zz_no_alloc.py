@@ -79,6 +79,48 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(lib):
     assert int(error.item()) == 0
 
 
+def test_the_call_allocates_nothing_and_forgets_the_call_before(lib):
+    """Free device memory is the same before and after warmed calls, and a call
+    that does not split K (more than 64 rows) right after one that does gives
+    the result of a call on its own: nothing of the array's old contents is read."""
+    stream = torch.cuda.current_stream().cuda_stream
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    shapes = [(8, 4096, 4096), (5, 1024, 8192), (96, 512, 1024)]
+    assert lib.chibi_gemm_bf16_splits(*shapes[0]) != lib.chibi_gemm_bf16_splits(*shapes[1]) > 1
+    assert lib.chibi_gemm_bf16_splits(*shapes[2]) == 1
+    cases = []
+    for seed, (M, N, K) in enumerate(shapes):
+        x, w, _ = _inputs(M, N, K, 20 + seed)
+        cases.append((M, N, K, x, w, torch.empty(M, N, dtype=torch.float32, device="cuda")))
+
+    def call(case):
+        M, N, K, x, w, out = case
+        out.fill_(float("nan"))
+        status = lib.chibi_gemm_bf16_noalloc(x.data_ptr(), w.data_ptr(), out.data_ptr(), 0, None, M, N, K,
+                                             K, K, N, 0, error.data_ptr(), stream)
+        assert status == 0, lib.chibi_error_string(status).decode()
+
+    for case in cases:                      # warm: kernel images, attributes, the array's address
+        call(case)
+    torch.cuda.synchronize()
+    alone = []
+    for case in cases:
+        call(case)
+        torch.cuda.synchronize()
+        alone.append(case[5].clone())
+    free_before, _ = torch.cuda.mem_get_info()
+    for order in ((0, 1, 2), (1, 0, 2), (2, 1, 0)):
+        for i in order:
+            call(cases[i])
+            torch.cuda.synchronize()
+            assert torch.equal(cases[i][5], alone[i]), f"shape {shapes[i]} after another call"
+            plain = cases[i][3].float() @ cases[i][4].float().t()
+            assert float((cases[i][5] - plain).abs().max()) <= 2e-5 * float(plain.abs().max())
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "device memory was allocated or freed by the calls"
+    assert int(error.item()) == 0
+
+
 def test_a_product_beyond_the_built_in_scratch_is_refused(lib):
     M, N, K = 32, 4096, 12288
     splits = lib.chibi_gemm_bf16_splits(M, N, K)
