@@ -42,8 +42,6 @@ struct GemmParams {
     const float* residual;
     long long res_stride;
     float* partial;        // [splits][M][N] when the K range is split through global memory, else null
-    int cluster;           // > 0: swapped operands, the gridDim.z CTAs of a cluster add their partial
-                           // sums through distributed shared memory (1 = a cluster of one)
     int swiglu;            // the rows of w come in blocks of 64 gate rows then 64 up rows; out[M, N / 2] =
                            // silu(gate) * up
     int* error;
@@ -204,30 +202,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         tcgen05_fence_after();
         timeline_mark(0);              // the accumulator is complete
         constexpr int CHUNK = BN < 32 ? 16 : 32;
-        if (p.cluster > 0) {
-            // this CTA's partial sums -> shared memory, [column][row] (the stages are free now)
-            float* part = reinterpret_cast<float*>(smem);
-            const int row = quarter * 32 + lane;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += CHUNK) {
-                uint32_t r[CHUNK];
-                if (kb_count > 0 && ok) {
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
-                    if constexpr (CHUNK == 32)
-                        tmem_load_32x32(taddr, r);
-                    else
-                        tmem_load_32x16(taddr, r);
-                    tmem_load_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < CHUNK; ++j)
-                        r[j] = 0;
-                }
-#pragma unroll
-                for (int j = 0; j < CHUNK; ++j)
-                    part[(c0 + j) * TILE_A + row] = __uint_as_float(r[j]);
-            }
-        } else if (p.swiglu) {
+        if (p.swiglu) {
             // x is the A operand: this thread has row m and the BN columns of w's rows, which come
             // as [64 gate | 64 up] blocks
             const int m = a_row;
@@ -342,46 +317,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
             }
         }
-    }
-    if (p.cluster > 0) {
-        // Add the cluster's partial sums: CTA `rank` takes the rows (or gate/up pairs) whose index is
-        // rank modulo the cluster size and reads them from every CTA, in rank order.
-        const int csize = gridDim.z;
-        cluster_sync();
-        if (warp >= 2) {
-            const uint32_t rank = cluster_cta_rank();
-            const uint32_t part_addr = smem_addr(smem);
-            const int et = threadIdx.x - 64;                       // 0 .. 127
-            const int units = p.swiglu ? 64 : TILE_A;              // rows, or gate/up pairs
-            const int mine = (units - (int)rank + csize - 1) / csize;
-            for (int e = et; e < mine * BN; e += 128) {
-                const int c = e / mine, row = (int)rank + (e - c * mine) * csize;
-                const int m = tile_b * BN + c;
-                // all loads first (they are independent), then the sums in rank order
-                float pv[16], pu[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    pv[j] = j < csize ? ld_peer_shared_f32(part_addr + (uint32_t)(c * TILE_A + row) * 4, j) : 0.f;
-                    pu[j] = (p.swiglu && j < csize)
-                        ? ld_peer_shared_f32(part_addr + (uint32_t)(c * TILE_A + 64 + row) * 4, j) : 0.f;
-                }
-                float v = 0.f, u = 0.f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    v += pv[j];
-                    u += pu[j];
-                }
-                if (p.swiglu) {
-                    const int feat = tile_a * 64 + row;
-                    if (m < p.M && feat < (p.N >> 1))
-                        static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + feat] =
-                            __float2bfloat16_rn((v / (1.f + expf(-v))) * u);
-                } else {
-                    store_value(p, m, tile_a * TILE_A + row, v);
-                }
-            }
-        }
-        cluster_sync();          // nobody leaves while its shared memory may still be read
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -959,7 +894,7 @@ static struct { float* scratch; long long floats; int fill_divisor; int* counter
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
-                       cudaStream_t stream, int cluster_z = 1)
+                       cudaStream_t stream)
 {
     constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
@@ -970,16 +905,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
             return (int)e;
         configured = true;
     }
-    static bool wide_clusters = false;
-    if (cluster_z > 8 && !wide_clusters) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
-                                                   cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (e != cudaSuccess)
-            return (int)e;
-        wide_clusters = true;
-    }
-    launch_cluster(gemm_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, stream, cluster_z,
-                   ma, mb, p);
+    launch(gemm_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, stream, ma, mb, p);
     return launch_status();
 }
 
@@ -1240,28 +1166,10 @@ CHIBI_API int chibi_gemm_reset_stream_counters(cudaStream_t stream)
     return (int)cudaMemsetAsync(stream_k.counters, 0, sizeof(int) * STREAM_K_COUNTERS, stream);
 }
 
-// How many CTAs share one tile's K range in chibi_gemm_bf16_fused (1 for M > 64).
-CHIBI_API int chibi_gemm_bf16_cluster_size(int M, int N, int K)
-{
-    if (M <= 0 || N <= 0 || K <= 0 || M > 64)
-        return 1;
-    const int tiles = (N + TILE_A - 1) / TILE_A;
-    const int k_blocks = (K + TILE_K - 1) / TILE_K;
-    const int resident = sm_count() * (M <= 16 ? 4 : 3);
-    int size = tiles >= resident ? 1 : resident / tiles;
-    if (size > 16)
-        size = 16;
-    if (size > k_blocks / 2)
-        size = k_blocks / 2;
-    return size < 1 ? 1 : size;
-}
-
-// out = x * w^T with what follows it done in the same kernel: + residual, or
-// (epilogue 1) SwiGLU over w's rows arranged as blocks of 64 gate rows followed
-// by their 64 up rows (out is then [M, N / 2], bfloat16).  For M <= 64 the K range
-// of a tile is shared by the CTAs of a thread-block cluster, which add their
-// partial sums through distributed shared memory in a fixed order: no scratch in
-// global memory and no second kernel.
+// out = x * w^T of more than 64 rows with what follows it done in the same kernel: + residual, or
+// (epilogue 1) SwiGLU over w's rows arranged as blocks of 64 gate rows followed by their 64 up
+// rows (out is then [M, N / 2], bfloat16).  Few rows split their K range instead
+// (chibi_gemm_bf16_partial and the kernels that finish a split product).
 CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int out_type,
                                     const float* residual, int M, int N, int K, long long x_stride,
                                     long long w_stride, long long out_stride, long long res_stride,
@@ -1290,24 +1198,8 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     p.swiglu = epilogue == 1 ? 1 : 0;
     p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
     CUtensorMap ma, mb;
-    if (M <= 64) {
-        const int size = chibi_gemm_bf16_cluster_size(M, N, K);
-        p.k_blocks_per_split = (p.k_blocks_total + size - 1) / size;
-        const int used = (p.k_blocks_total + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
-        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-        p.swap = 1;
-        p.cluster = used;
-        p.rows_a = N;
-        p.rows_b = M;
-        if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &ma) || !tensor_map_2d(x, M, K, x_stride, bn, &mb))
-            return CHIBI_ERR_UNSUPPORTED;
-        const dim3 grid((N + TILE_A - 1) / TILE_A, 1, used);
-        if (bn == 16)
-            return launch_gemm<16, 3>(ma, mb, p, grid, stream, used);
-        if (bn == 32)
-            return launch_gemm<32, 3>(ma, mb, p, grid, stream, used);
-        return launch_gemm<64, 3>(ma, mb, p, grid, stream, used);
-    }
+    if (M <= 64)
+        return CHIBI_ERR_UNSUPPORTED;
     p.k_blocks_per_split = p.k_blocks_total;
     p.swap = 0;
     p.rows_a = M;

@@ -107,16 +107,6 @@ __device__ __forceinline__ void cluster_sync()
                  "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Reads a 32-bit value at the same shared-memory offset in CTA `rank` of the cluster.
-__device__ __forceinline__ float ld_peer_shared_f32(uint32_t own_smem_addr, uint32_t rank)
-{
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_smem_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
 // Writes a 32-bit value to the same shared-memory offset in CTA `rank` of the cluster.
 __device__ __forceinline__ void st_peer_shared_f32(uint32_t own_smem_addr, uint32_t rank, float v)
 {

@@ -28,7 +28,6 @@ _SIGNATURES = {
         "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
         "chibi_gemm_bf16_splits": [I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
-        "chibi_gemm_bf16_cluster_size": [I, I, I],
         "chibi_gemm_set_stream_scratch": [P, L],
         "chibi_gemm_reset_stream_counters": [P],
         "chibi_gemm_bf16_norm_parts": [I],

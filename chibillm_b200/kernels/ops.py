@@ -175,11 +175,7 @@ class CudaKernels:
         # output, up to the factor of each row, which the next product applies to its sums.
         self.fold_norms = True
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
-        # global scratch to a second kernel that also does what follows the product (the default), or
-        # the CTAs form a cluster and add up through distributed shared memory (use_clusters; measured
-        # slower on B200: clusters of 8..16 CTAs are scheduled together and lose the overlap of
-        # consecutive kernels).
-        self.use_clusters = False
+        # global scratch to a second kernel that also does what follows the product.
         self.fuse_split_products = True
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # the many-row product shares its last, partly filled round of tiles out by K blocks and
@@ -440,11 +436,17 @@ class CudaKernels:
             raise KernelError("linear_swiglu: shapes or element types")
         if not self.use_tensor_cores:
             return False
-        if M <= 64 and not self.use_clusters:
+        if M <= 64:
             pending = self.linear_partial(x, w_interleaved)
-            if pending is not None:
-                self.reduce_swiglu(pending, out, interleaved=True)
-                return True
+            if pending is None:
+                # a shape whose K range is not split: the whole product, then the same kernel
+                # that otherwise adds up the splits (here: one) applies SwiGLU
+                buf = self._partial_buffer(M * N)
+                self.linear(x, w_interleaved, buf[:M * N].view(M, N))
+                pending = PendingSum(self, buf[:M * N].view(1, M, N), 1, M, N, self._partial_turn,
+                                     self._partial_stamps[self._partial_turn])
+            self.reduce_swiglu(pending, out, interleaved=True)
+            return True
         status = self.lib.chibi_gemm_bf16_fused(
             _ptr(x), _ptr(w_interleaved), _ptr(out), BF16, None, M, N, K, x.stride(0),
             w_interleaved.stride(0), out.stride(0), 0, 1, _ptr(self.error), self._stream())
@@ -551,18 +553,6 @@ class CudaKernels:
             _rows_contiguous(residual, "linear: residual")
             if residual.dtype != torch.float32 or residual.shape != (M, N):
                 raise KernelError("linear: residual must be float32 [M, N]")
-        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.use_tensor_cores \
-                and self.use_clusters and M <= 64:
-            status = self.lib.chibi_gemm_bf16_fused(
-                _ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(residual), M, N, K, x.stride(0),
-                w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, 0,
-                _ptr(self.error), self._stream())
-            if status == 0:
-                self.launches += 1
-                self.tensor_core_calls += 1
-                return
-            if status != -2:
-                _check(status, "linear (tensor cores)")
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.use_tensor_cores:
             splits = self.lib.chibi_gemm_bf16_splits(M, N, K)
             if splits > 0:

@@ -282,19 +282,12 @@ def test_sample_temperature(k, vocab):
 
 @pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64, 65, 128, 300])
 @pytest.mark.parametrize("N,K", [(203, 96), (256, 512), (1000, 1000), (384, 4096)])
-@pytest.mark.parametrize("clusters", [False, True])
-def test_linear_tensor_cores(k, ref, M, N, K, clusters):
+def test_linear_tensor_cores(k, ref, M, N, K):
     """The tcgen05 kernel at sizes that are no multiple of its tiles: rows and
     features past the edge, a K tail, K ranges split over CTAs for few rows
-    (through global scratch, or through a cluster's shared memory), and enough K
-    blocks that the ring of stages wraps several times."""
-    if clusters and M > 64:
-        pytest.skip("clusters share a K range only for few rows")
-    k.use_clusters = clusters
-    try:
-        _linear_tensor_cores(k, ref, M, N, K)
-    finally:
-        k.use_clusters = False
+    (through global scratch), and enough K blocks that the ring of stages wraps
+    several times."""
+    _linear_tensor_cores(k, ref, M, N, K)
 
 
 def _linear_tensor_cores(k, ref, M, N, K):
@@ -504,12 +497,6 @@ def test_linear_swiglu(k, ref, M, inter, K):
     assert torch.equal(w[:64], gate[:64]) and torch.equal(w[64:128], up[:64])
     out = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
     assert k.linear_swiglu(x, w, out)
-    if M <= 64:        # the other way for few rows: a cluster of CTAs adds up through shared memory
-        k.use_clusters = True
-        out2 = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
-        assert k.linear_swiglu(x, w, out2)
-        k.use_clusters = False
-        close(out2, out, torch.bfloat16, "cluster vs split product", rel=8e-3)
     gu = torch.empty(M, 2 * inter, dtype=torch.float32, device="cuda")
     ref.linear(x, torch.cat([gate, up]), gu)
     exp = torch.empty_like(out)
