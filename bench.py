@@ -15,7 +15,9 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
 
-``--shape`` runs the same at the Qwen3-0.6B or Qwen3-14B layer sizes, and
+``--timeline`` prints, instead of the record, when the CTAs of every kernel of one
+decode step started, waited and ended.  ``--shape`` runs the same at the Qwen3-0.6B or
+Qwen3-14B layer sizes, and
 ``--mixed-requests N`` replaces the record by a serving run: N requests with
 prompts of 16 to 2,048 tokens and 256 new tokens each through ``LLM.generate``.
 """
@@ -315,6 +317,42 @@ def measure_mixed(cfg, layers, full_layers, requests, shape, check_tokens=0):
             "steps_from_graphs": replays, "steps_launched_ahead": ahead, "check": check}
 
 
+def print_timeline(cfg, batch, held):
+    """One decode step, replayed from its CUDA graph, as its CTAs saw it: for every launch when
+    its first and last CTA started, when their wait for the launch before ended and when they
+    left (microseconds from the step's start), and the points that kernels mark inside
+    (chibillm_b200/kernels/timeline.py; the libraries are built with -DCHIBI_TIMELINE for this)."""
+    import torch
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    from chibillm_b200.kernels.ops import CudaKernels
+
+    kernels = CudaKernels(torch.device("cuda:0"), timeline=True)
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", page_size=16, pool_tokens=batch * (held + 128),
+                                     max_requests=batch, kernels=kernels)
+    for name in runner.storage.keys:
+        runner.storage.keys[name].normal_()
+        runner.storage.values[name].normal_()
+    ids = [f"r{i}" for i in range(batch)]
+    for rid in ids:
+        fill_request(runner, rid, held)
+    for i in range(6):
+        runner.step([StepEntry(rid, [5 + i], [0]) for rid in ids])
+    torch.cuda.synchronize()
+    kernels.timeline.reset()
+    runner.step([StepEntry(rid, [77], [0]) for rid in ids])
+    launches = kernels.timeline.launches()
+    cell = lambda v: "       -" if v is None else f"{v:8.2f}"
+    print(f"# decode step of {batch} x {held} tokens, {cfg['num_hidden_layers']} layers, from a graph: "
+          f"{runner.graph_replays > 0}; times in us")
+    print(f"{'kernel':42s} {'ctas':>5s} {'sms':>4s} {'start0':>8s} {'start1':>8s} {'wait0':>8s} {'wait1':>8s} "
+          f"{'end0':>8s} {'end1':>8s}  marks (first..last CTA)")
+    for l in launches:
+        marks = "  ".join(f"{m[0]:.2f}..{m[1]:.2f}" for m in l["marks"] if m is not None)
+        print(f"{l['kernel'][:42]:42s} {l['blocks']:5d} {l['sms']:4d} {cell(l['first_start'])} {cell(l['last_start'])} "
+              f"{cell(l['first_waited'])} {cell(l['last_waited'])} {cell(l['first_end'])} {cell(l['last_end'])}  {marks}")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -333,6 +371,8 @@ def main() -> int:
     ap.add_argument("--mixed-requests", type=int, default=0,
                     help="instead of the record: this many requests with prompts of 16 to 2,048 random tokens "
                          "and 256 new tokens each through the Python entry point; prints its own JSON line")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the record: the timeline of one decode step (use with --layers 4 or so)")
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
@@ -362,6 +402,9 @@ def main() -> int:
     cfg["num_hidden_layers"] = layers
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
+    if args.timeline:
+        print_timeline(cfg, args.batch, args.prompt)
+        return 0
     if args.mixed_requests > 0:
         print(json.dumps(measure_mixed(cfg, layers, full_layers, args.mixed_requests, args.shape,
                                        args.check_tokens)))
