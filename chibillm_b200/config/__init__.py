@@ -1,6 +1,6 @@
 """Configuration: typed reading of config.json and the architecture registry."""
 from .base import ConfigError, KeyReader, read_config_json
-from .spec import (AttentionSpec, FeedForwardSpec, GatedMLPSpec, LayerSpec, MixerSpec,
+from .spec import (AdapterSpec, AttentionSpec, FeedForwardSpec, GatedMLPSpec, LayerSpec, MixerSpec,
                    ModelSpec, NormSpec, PositionSpec, RunStep)
 from .registry import (Architecture, find_architecture, load_config, register_architecture,
                        registered_architectures, unregister_architecture)
@@ -11,7 +11,7 @@ register_architecture(QWEN3_ARCHITECTURE, Qwen3Config.from_dict, Qwen3Config.mod
 
 __all__ = [
     "ConfigError", "KeyReader", "read_config_json",
-    "AttentionSpec", "FeedForwardSpec", "GatedMLPSpec", "LayerSpec", "MixerSpec", "ModelSpec",
+    "AdapterSpec", "AttentionSpec", "FeedForwardSpec", "GatedMLPSpec", "LayerSpec", "MixerSpec", "ModelSpec",
     "NormSpec", "PositionSpec", "RunStep",
     "Architecture", "find_architecture", "load_config", "register_architecture",
     "registered_architectures", "unregister_architecture", "Qwen3Config",

@@ -122,8 +122,28 @@ class RunStep:
 
 
 @dataclass(frozen=True)
+class AdapterSpec:
+    """A part at one of the decoder's ends: after the token embedding (it
+    changes the residual stream in place: a learned or absolute position table,
+    a scale of the embeddings) or on the logits of the wanted rows (a soft cap,
+    a bias).  ``kind`` names a registered adapter part; ``weight_names`` maps
+    its tensor roles to checkpoint names; ``params`` are its constants."""
+
+    kind: str
+    weight_names: Tuple[Tuple[str, str], ...] = ()
+    params: Tuple[Tuple[str, float], ...] = ()
+
+    def names(self) -> dict:
+        return dict(self.weight_names)
+
+    def constants(self) -> dict:
+        return dict(self.params)
+
+
+@dataclass(frozen=True)
 class ModelSpec:
-    """A whole decoder: embedding, layers, run order, final norm, output."""
+    """A whole decoder: embedding, what follows it at once, layers, run order,
+    final norm, output, what is done to the logits."""
 
     architecture: str
     vocab_size: int
@@ -139,3 +159,5 @@ class ModelSpec:
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
     extra: dict = field(default_factory=dict, compare=False)
+    input_adapters: Tuple[AdapterSpec, ...] = ()      # run on the residual right after the embedding
+    logit_adapters: Tuple[AdapterSpec, ...] = ()      # run on the 32-bit logits of the wanted rows

@@ -1,5 +1,6 @@
-"""A decoder put together from a ModelSpec: embedding, blocks in run order,
-final norm, vocabulary projection on the wanted rows.
+"""A decoder put together from a ModelSpec: embedding (and the adapters that
+follow it at once), blocks in run order, final norm, vocabulary projection on
+the wanted rows (and the adapters of the logits).
 
 The class is the same for every architecture; what differs is the spec that
 the architecture's configuration produced.  The vocabulary projection uses the
@@ -14,7 +15,7 @@ from typing import Dict, Iterable, List, Optional, Sequence
 import torch
 
 from ..config.spec import ModelSpec
-from ..parts.base import Block, Runtime, TensorSpec, make_block, make_norm
+from ..parts.base import Block, Runtime, TensorSpec, make_adapter, make_block, make_norm
 from .batch import StepContext
 
 
@@ -24,6 +25,8 @@ class DecoderModel:
         self.runtime = runtime
         self.blocks: List[Block] = [make_block(layer, runtime) for layer in spec.layers]
         self.final_norm = make_norm(spec.final_norm, spec.final_norm_name, runtime)
+        self.input_adapters = [make_adapter(a, runtime) for a in spec.input_adapters]
+        self.logit_adapters = [make_adapter(a, runtime) for a in spec.logit_adapters]
         self.embedding: torch.Tensor = None
         self.output: torch.Tensor = None
         for i, step in enumerate(spec.run_order):
@@ -42,6 +45,8 @@ class DecoderModel:
             out.append(TensorSpec(s.output_name, (s.vocab_size, s.hidden_size)))
         for b in self.blocks:
             out += b.expected_tensors()
+        for a in self.input_adapters + self.logit_adapters:
+            out += a.expected_tensors()
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -51,6 +56,8 @@ class DecoderModel:
         self.final_norm.bind(tensors)
         for b in self.blocks:
             b.bind(tensors)
+        for a in self.input_adapters + self.logit_adapters:
+            a.bind(tensors)
 
     # ---- cache
     def cache_needs(self) -> List[object]:
@@ -64,6 +71,11 @@ class DecoderModel:
         numbers of tokens, sequences and wanted rows), as a hashable; None if any
         part cannot promise that a captured step stays valid."""
         keys = []
+        for a in self.input_adapters + self.logit_adapters:
+            key = a.launch_key(ctx)
+            if key is None:
+                return None
+            keys.append(key)
         for step in self.spec.run_order:
             block = self.blocks[step.layer]
             key = block.launch_key(ctx)
@@ -82,6 +94,8 @@ class DecoderModel:
         hidden = self.spec.hidden_size
         residual = ctx.workspace.get("model.residual", (T, hidden), torch.float32)
         k.embed(ctx.tokens, self.embedding, residual)
+        for a in self.input_adapters:
+            a.forward(residual, ctx)
         pending = None      # a last product that a block left to be added to the residual
         for i, step in enumerate(self.spec.run_order):
             pending = self.blocks[step.layer].forward(residual, ctx, cache_views[i], pending)
@@ -96,4 +110,6 @@ class DecoderModel:
         self.final_norm.forward(rows, normed)
         logits = ctx.workspace.get("model.logits", (R, self.spec.vocab_size), torch.float32)
         k.linear(normed, self.output, logits)
+        for a in self.logit_adapters:
+            a.forward(logits, ctx)
         return logits

@@ -155,12 +155,23 @@ class Block(Part):
         raise NotImplementedError
 
 
+class Adapter(Part):
+    """A part at one of the decoder's ends (AdapterSpec).  An input adapter gets
+    the 32-bit residual [T, hidden] right after the token embedding, a logit
+    adapter the 32-bit logits [R, vocab] of the wanted rows; both change their
+    argument in place.  ``ctx`` is the step's context (positions, sequences)."""
+
+    def forward(self, x: torch.Tensor, ctx) -> None:
+        raise NotImplementedError
+
+
 # ------------------------------------------------------------------ registries
 _NORMS: Dict[str, Callable] = {}
 _POSITIONS: Dict[str, Callable] = {}
 _MIXERS: Dict[str, Callable] = {}
 _FEED_FORWARDS: Dict[str, Callable] = {}
 _BLOCKS: Dict[str, Callable] = {}
+_ADAPTERS: Dict[str, Callable] = {}
 
 
 def _register(table: Dict[str, Callable], what: str, kind: str, factory: Callable, replace: bool):
@@ -199,6 +210,15 @@ def register_feed_forward(kind: str, factory: Callable, replace: bool = False) -
 def register_block(kind: str, factory: Callable, replace: bool = False) -> None:
     """factory(layer: LayerSpec, runtime) -> Block"""
     _register(_BLOCKS, "block arrangement", kind, factory, replace)
+
+
+def register_adapter(kind: str, factory: Callable, replace: bool = False) -> None:
+    """factory(spec: AdapterSpec, runtime) -> Adapter"""
+    _register(_ADAPTERS, "adapter", kind, factory, replace)
+
+
+def make_adapter(spec, runtime: Runtime) -> Adapter:
+    return _lookup(_ADAPTERS, "adapter", spec.kind)(spec, runtime)
 
 
 def make_norm(spec, weight_name: str, runtime: Runtime) -> Norm:

@@ -133,3 +133,32 @@ def test_a_step_refuses_what_it_cannot_run(tmp_path):
     logits = runner.step([StepEntry("a", [4], [0])])
     assert logits.shape == (1, cfg["vocab_size"]) and runner.length("a") == 4
     runner.cache.check_invariants()
+
+
+def test_parts_at_the_decoders_ends_on_cpu(tmp_path):
+    """A toy architecture with a learned table of absolute positions added to the
+    (scaled) embeddings and soft-capped logits, both registered as adapters from
+    outside the package: whole, in portions and mixed, against its plain restatement."""
+    import toy_parts
+    from chibillm_b200.config import unregister_architecture
+    from chibillm_b200.weights import write_random_model
+    toy_parts.register_absolute_toy()
+    try:
+        obj = dict(toy_parts.ABSOLUTE_TOY_CONFIG)
+        folder = write_random_model(obj, str(tmp_path / "absolute"), seed=6, dtype=torch.float32)
+        _, w = plain_qwen3.read_model_folder(folder)
+        assert "positions.weight" in w and w["positions.weight"].shape == (96, 64)
+        reqs = helpers.random_requests(113, [30, 8, 61, 17], seed=2)
+        ref = {rid: toy_parts.absolute_toy_plain(obj, w, ids) for rid, ids in reqs.items()}
+        assert float(max(r.abs().max() for r in ref.values())) <= obj["cap"]
+        # the positions matter: the same tokens further along give other logits
+        shifted = toy_parts.absolute_toy_plain(obj, w, reqs["r1"] + reqs["r1"])
+        assert float((shifted[8:] - ref["r1"]).abs().max()) > 1e-3
+        runner = cpu_runner(folder, 4, 128, max_requests=3)
+        for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, 3), "portions"),
+                            (helpers.trace_mixed(reqs, 128, seed=4, max_live=3, decode_tail=5), "mixed")):
+            got = helpers.run_trace(runner, trace)
+            helpers.assert_logits_close(got, ref, 2e-5, f"absolute toy {what}")
+            runner.cache.check_invariants()
+    finally:
+        unregister_architecture("ToyAbsoluteForCausalLM")

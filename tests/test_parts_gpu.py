@@ -387,3 +387,30 @@ def test_toy_architecture_with_routing_and_its_own_position_encoding(tmp_path):
         assert runner.graph_replays == 0
     finally:
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+def test_toy_architecture_with_parts_at_the_decoders_ends(tmp_path):
+    """Learned absolute positions after the embedding and soft-capped logits as
+    adapters registered from the tests: nothing in the decoder changes for them."""
+    import toy_parts
+    from chibillm_b200.config import unregister_architecture
+    from chibillm_b200.engine.runner import ModelRunner
+    from chibillm_b200.weights import write_random_model
+    toy_parts.register_absolute_toy()
+    try:
+        obj = dict(toy_parts.ABSOLUTE_TOY_CONFIG)
+        for dtype, tol in (("float32", 2e-5), ("bfloat16", helpers.TOL["bfloat16"])):
+            folder = write_random_model(obj, str(tmp_path / f"absolute_{dtype}"), seed=6, dtype=torch.float32)
+            _, w = plain_qwen3.read_model_folder(folder)
+            reqs = helpers.random_requests(113, [30, 8, 61, 17], seed=2)
+            ref = {rid: toy_parts.absolute_toy_plain(obj, w, ids) for rid, ids in reqs.items()}
+            runner = ModelRunner.from_folder(folder, dtype=dtype, device=DEV, page_size=4, pool_tokens=128,
+                                             max_requests=3)
+            for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, 3), "portions"),
+                                (helpers.trace_mixed(reqs, 128, seed=4, max_live=3, decode_tail=5), "mixed")):
+                got = helpers.run_trace(runner, trace)
+                helpers.assert_logits_close(got, ref, tol, f"absolute toy {dtype} {what}")
+                runner.cache.check_invariants()
+            assert runner.graph_replays == 0        # the adapters give no launch key
+    finally:
+        unregister_architecture("ToyAbsoluteForCausalLM")

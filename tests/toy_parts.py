@@ -122,3 +122,85 @@ def toy_plain(obj, w, ids):
     h, _ = attn(h, "layers.0.", kv_from=kv)
     h = mlp(h, "layers.0.")
     return plain_qwen3.rms_norm(h, w["norm.weight"], eps) @ w["embed.weight"].t()
+
+
+# ------------------------------------------------------------------ a toy with parts at the decoder's ends
+def register_absolute_toy():
+    """Attention without any position encoding inside the mixer; instead a
+    learned table of absolute positions is added to the embeddings (an input
+    adapter), the embeddings are scaled by a constant, and the logits are
+    soft-capped, c * tanh(logits / c) (a logit adapter).  None of this needs a
+    change to the decoder: the adapters are registered like any other part."""
+    from chibillm_b200.config import (AdapterSpec, AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
+                                      PositionSpec, RunStep, register_architecture)
+    from chibillm_b200.parts import Adapter, TensorSpec, register_adapter
+
+    class AbsolutePositions(Adapter):
+        def __init__(self, spec, rt):
+            self.spec, self.rt = spec, rt
+            self.scale = spec.constants()["embedding_scale"]
+            self.rows = int(spec.constants()["positions"])
+            self.width = int(spec.constants()["width"])
+
+        def expected_tensors(self):
+            return [TensorSpec(self.spec.names()["table"], (self.rows, self.width))]
+
+        def bind(self, tensors):
+            self.table = tensors[self.spec.names()["table"]].float()
+
+        def forward(self, x, ctx):
+            x.mul_(self.scale).add_(self.table[ctx.positions.long()])
+
+    class SoftCap(Adapter):
+        def __init__(self, spec, rt):
+            self.cap = spec.constants()["cap"]
+
+        def forward(self, x, ctx):
+            x.copy_(torch.tanh(x / self.cap) * self.cap)
+
+    register_adapter("toy_absolute_positions", AbsolutePositions, replace=True)
+    register_adapter("toy_soft_cap", SoftCap, replace=True)
+
+    def model_spec(obj):
+        H = obj["hidden_size"]
+        norm = NormSpec("rmsnorm", H, obj["eps"], 0.0)
+        mlp = GatedMLPSpec("gated_mlp", hidden_size=H, intermediate_size=obj["intermediate_size"], activation="silu")
+        attn = AttentionSpec(kind="attention", hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16,
+                             scale=0.25, window=None, qk_norm=None, position=PositionSpec("none"))
+        names = (("mixer_norm", "n1.weight"), ("feed_forward_norm", "n2.weight"), ("q_proj", "q.weight"),
+                 ("k_proj", "k.weight"), ("v_proj", "v.weight"), ("o_proj", "o.weight"),
+                 ("gate_proj", "gate.weight"), ("up_proj", "up.weight"), ("down_proj", "down.weight"))
+        layers = tuple(LayerSpec("prenorm", attn, mlp, norm, norm, f"layers.{i}.", names) for i in range(2))
+        return ModelSpec(architecture="ToyAbsoluteForCausalLM", vocab_size=obj["vocab_size"], hidden_size=H,
+                         max_positions=obj["max_positions"], layers=layers, run_order=(RunStep(0), RunStep(1)),
+                         final_norm=norm, embedding_name="embed.weight", final_norm_name="norm.weight",
+                         output_name="head.weight", tie_output_to_embedding=True,
+                         input_adapters=(AdapterSpec("toy_absolute_positions", (("table", "positions.weight"),),
+                                                     (("embedding_scale", obj["embedding_scale"]),
+                                                      ("positions", obj["max_positions"]), ("width", H))),),
+                         logit_adapters=(AdapterSpec("toy_soft_cap", (), (("cap", obj["cap"]),)),))
+
+    register_architecture("ToyAbsoluteForCausalLM", lambda obj: obj, model_spec, replace=True)
+
+
+ABSOLUTE_TOY_CONFIG = {"architectures": ["ToyAbsoluteForCausalLM"], "hidden_size": 64, "intermediate_size": 80,
+                       "vocab_size": 113, "eps": 1e-5, "max_positions": 96, "embedding_scale": 8.0, "cap": 0.4}
+
+
+def absolute_toy_plain(obj, w, ids):
+    """Whole sequence, no cache."""
+    T = len(ids)
+    eps = obj["eps"]
+    h = plain_qwen3.embedding(w["embed.weight"], ids) * obj["embedding_scale"] + w["positions.weight"][:T]
+    for i in range(2):
+        p = f"layers.{i}."
+        x = plain_qwen3.rms_norm(h, w[p + "n1.weight"], eps)
+        q = (x @ w[p + "q.weight"].t()).view(T, 4, 16)
+        k = (x @ w[p + "k.weight"].t()).view(T, 2, 16)
+        v = (x @ w[p + "v.weight"].t()).view(T, 2, 16)
+        h = h + plain_qwen3.causal_attention(q, k, v, None).reshape(T, 64) @ w[p + "o.weight"].t()
+        x = plain_qwen3.rms_norm(h, w[p + "n2.weight"], eps)
+        gate, up = x @ w[p + "gate.weight"].t(), x @ w[p + "up.weight"].t()
+        h = h + ((gate / (1 + torch.exp(-gate))) * up) @ w[p + "down.weight"].t()
+    logits = plain_qwen3.rms_norm(h, w["norm.weight"], eps) @ w["embed.weight"].t()
+    return torch.tanh(logits / obj["cap"]) * obj["cap"]
