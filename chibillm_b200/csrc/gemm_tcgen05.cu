@@ -1003,7 +1003,8 @@ static bool few_deep_ctas(int M, int N)
 // the weights' bytes (they mostly stay in L2; measured at 64 rows, 0.15 left a
 // product of 64 CTAs that could not keep the memory busy: 105 against 97 us per
 // layer), and a split has at least two K blocks.
-CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K)
+// `max_splits` > 0: no more splits than that (a consumer that has only so many loads in flight).
+CHIBI_API int chibi_gemm_bf16_splits_capped(int M, int N, int K, int max_splits)
 {
     if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0)
         return 0;
@@ -1028,13 +1029,23 @@ CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K)
         splits = traffic_cap;
     if (splits > k_blocks / 2)
         splits = k_blocks / 2;
-    if (splits > 24)
-        splits = 24;
+    // Whoever adds the partial sums up has the loads of sixteen splits in flight at once; a
+    // seventeenth costs a second trip to L2 on the critical path of a decode step (measured:
+    // 18 -> 16 splits of the down product of Qwen3-8B, 1.5 us a layer).  And a CTA should have
+    // at least five K blocks to stream, or its three stages are most of its work.
+    if (splits > 16)
+        splits = 16;
+    if (k_blocks >= 20 && splits > k_blocks / 5)
+        splits = k_blocks / 5;
+    if (max_splits > 0 && splits > max_splits)
+        splits = max_splits;
     if (splits < 1)
         splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
     return (k_blocks + per - 1) / per;
 }
+
+CHIBI_API int chibi_gemm_bf16_splits(int M, int N, int K) { return chibi_gemm_bf16_splits_capped(M, N, K, 0); }
 
 // Returns CHIBI_ERR_UNSUPPORTED for shapes or alignments it does not take; the
 // caller then uses the plain kernel.
@@ -1042,7 +1053,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
                          const float* residual, int M, int N, int K, long long x_stride,
                          long long w_stride, long long out_stride, long long res_stride,
                          float* scratch, long long scratch_floats, int* error, cudaStream_t stream,
-                         bool reduce, bool share_last_round = true)
+                         bool reduce, bool share_last_round = true, int max_splits = 0)
 {
     if (M <= 0 || N <= 0)
         return CHIBI_OK;
@@ -1069,7 +1080,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
     p.res_stride = res_stride;
     p.error = error;
     p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
-    const int splits = chibi_gemm_bf16_splits(M, N, K);
+    const int splits = chibi_gemm_bf16_splits_capped(M, N, K, max_splits);
     if (splits <= 0)
         return CHIBI_ERR_UNSUPPORTED;
     p.k_blocks_per_split = (p.k_blocks_total + splits - 1) / splits;
@@ -1303,17 +1314,18 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
     return launch_gemm_persistent<256, 4>(ma, mb, p, (M + TILE_A - 1) / TILE_A, N / 256, stream);
 }
 
-// The first half only, for shapes that chibi_gemm_bf16_splits splits (> 1): the
+// The first half only, for shapes that chibi_gemm_bf16_splits_capped splits (> 1): the
 // partial sums [splits][M][N] stay in `scratch` for a kernel that adds them up
 // together with what follows the product (chibi_reduce_* below and elsewhere).
+// `max_splits` > 0: at most so many splits (what the adding kernel fetches in one go).
 CHIBI_API int chibi_gemm_bf16_partial(const void* x, const void* w, int M, int N, int K,
                                       long long x_stride, long long w_stride, float* scratch,
-                                      long long scratch_floats, int* error, cudaStream_t stream)
+                                      long long scratch_floats, int max_splits, int* error, cudaStream_t stream)
 {
-    if (chibi_gemm_bf16_splits(M, N, K) <= 1 || (reinterpret_cast<uintptr_t>(scratch) & 15))
+    if (chibi_gemm_bf16_splits_capped(M, N, K, max_splits) <= 1 || (reinterpret_cast<uintptr_t>(scratch) & 15))
         return CHIBI_ERR_UNSUPPORTED;
     return gemm_bf16_impl(x, w, scratch, CHIBI_F32, nullptr, M, N, K, x_stride, w_stride, N, 0, scratch,
-                          scratch_floats, error, stream, false);
+                          scratch_floats, error, stream, false, true, max_splits);
 }
 
 // ------------------------------------------------------------------ kernels that finish a split product

@@ -27,6 +27,7 @@ _SIGNATURES = {
         "chibi_add_into": [P, P, I, L, P],
         "chibi_gemm_simt": [P, I, P, I, P, I, P, I, I, I, L, L, L, L, P],
         "chibi_gemm_bf16_splits": [I, I, I],
+        "chibi_gemm_bf16_splits_capped": [I, I, I, I],
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_gemm_set_stream_scratch": [P, L],
         "chibi_gemm_reset_stream_counters": [P],
@@ -34,7 +35,7 @@ _SIGNATURES = {
         "chibi_gemm_bf16_rows": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P, P, P],
         "chibi_scale_rows": [P, L, I, L, P, I, F, I, P],
         "chibi_gemm_bf16_fused": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P],
-        "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, P, P],
+        "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, I, P, P],
         "chibi_reduce_residual_rmsnorm": [P, I, I, I, P, L, P, I, P, I, L, F, F, P],
         "chibi_reduce_swiglu": [P, I, I, I, P, I, I, P],
         "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,

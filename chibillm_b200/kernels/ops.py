@@ -377,10 +377,11 @@ class CudaKernels:
             self.scratch_generation += 1
         return buf
 
-    def linear_partial(self, x: torch.Tensor, w: torch.Tensor) -> Optional[PendingSum]:
+    def linear_partial(self, x: torch.Tensor, w: torch.Tensor, max_splits: int = 0) -> Optional[PendingSum]:
         """Start x @ w^T with the K range split over CTAs and leave the partial
         sums for a fused consumer; None if this product is not one that is split
-        (then use ``linear``)."""
+        (then use ``linear``).  ``max_splits``: at most so many splits (a consumer
+        that fetches only so many partial sums in one go says so)."""
         if isinstance(x, ScaledRows):
             return None                  # many rows: such a product is not split
         if not (self.use_tensor_cores and self.fuse_split_products and x.is_cuda
@@ -392,12 +393,13 @@ class CudaKernels:
         N = w.shape[0]
         if w.shape[1] != K:
             raise KernelError(f"linear: shapes x {tuple(x.shape)} w {tuple(w.shape)}")
-        splits = self.lib.chibi_gemm_bf16_splits(M, N, K)
+        splits = self.lib.chibi_gemm_bf16_splits_capped(M, N, K, int(max_splits))
         if splits <= 1 or N % 4 != 0:
             return None
         buf = self._partial_buffer(splits * M * N)
         status = self.lib.chibi_gemm_bf16_partial(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                                                  _ptr(buf), buf.numel(), _ptr(self.error), self._stream())
+                                                  _ptr(buf), buf.numel(), int(max_splits), _ptr(self.error),
+                                                  self._stream())
         if status == -2:
             return None
         _check(status, "linear (split product)")

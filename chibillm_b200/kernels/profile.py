@@ -24,7 +24,7 @@ from typing import Callable, Dict, List, Optional, Tuple
 import torch
 
 # entry points that ask a question or set something and launch nothing
-_NOT_LAUNCHES = ("chibi_gemm_bf16_splits", "chibi_gemm_bf16_norm_parts",
+_NOT_LAUNCHES = ("chibi_gemm_bf16_splits", "chibi_gemm_bf16_splits_capped", "chibi_gemm_bf16_norm_parts",
                  "chibi_gemm_set_stream_scratch", "chibi_gemm_reset_stream_counters",
                  "chibi_attention_mma_head_dim", "chibi_attention_tc_head_dim")
 

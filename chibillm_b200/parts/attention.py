@@ -86,7 +86,9 @@ class PagedAttention(Mixer):
         split = getattr(k, "linear_partial", None)
         pending = None
         if split is not None and fused is not None and d % 4 == 0:
-            pending = split(x, self.qkv if writes else self.qkv[:qw])
+            # the kernels that add these sums up (decode attention; norm + rotation + append) fetch
+            # eight splits of a head in one go
+            pending = split(x, self.qkv if writes else self.qkv[:qw], max_splits=8)
         if pending is None:
             qkv = ctx.workspace.get("attn.qkv", (T, width), rt.dtype)
             k.linear(x, self.qkv if writes else self.qkv[:qw], qkv)

@@ -38,7 +38,7 @@ class ReferenceKernels:
         inv = torch.rsqrt((xf * xf).sum(-1, keepdim=True) / n + eps)
         out.copy_(((xf * inv) * (weight.float() + offset)).to(out.dtype))
 
-    def linear_partial(self, x, w):
+    def linear_partial(self, x, w, max_splits=0):
         return None
 
     def linear(self, x, w, out, residual=None, defer=False):
