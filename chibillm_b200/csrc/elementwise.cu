@@ -880,3 +880,70 @@ CHIBI_API int chibi_apply_table_updates(int* table, int table_stride, int table_
                                                            capacity, error);
     return launch_status();
 }
+
+// Per-token tables that every layer of a step shares when the q | k | v product finishes its heads
+// itself.  rope: [tokens][2 * half], the cosines then the sines of float(position) * inv_freq[j],
+// the same arithmetic as the norm + rotation kernels.  slots: the element offset of the token's slot
+// in a paged cache [pages][nkv][page_size][d] for kv head 0, or -1 (and error word 2) if the block
+// table holds no valid page for the position.
+namespace chibi {
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  long long tokens, int half, float* __restrict__ out)
+{
+    pdl_enter();
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < tokens * half;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / half;
+        const int j = (int)(idx - t * half);
+        float sn, cn;
+        sincosf((float)positions[t] * inv_freq[j], &sn, &cn);
+        out[t * 2 * half + j] = cn;
+        out[t * 2 * half + half + j] = sn;
+    }
+}
+
+__global__ void cache_slots_kernel(const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ seq_rows, const int* __restrict__ block_table,
+                                   int table_stride, long long tokens, int nkv, int page_size, int num_pages, int d,
+                                   long long* __restrict__ out, int* __restrict__ error)
+{
+    pdl_enter();
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < tokens;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int pos = positions[t];
+        const int seq = seq_of_token[t];
+        const int table_row = seq_rows ? seq_rows[seq] : seq;
+        const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (error)
+                atomicExch(error, 2);
+            out[t] = -1;
+        } else {
+            out[t] = ((long long)page * nkv * page_size + (pos % page_size)) * d;
+        }
+    }
+}
+} // namespace chibi
+
+CHIBI_API int chibi_rope_table(const int* positions, const float* inv_freq, long long tokens, int half, float* out,
+                               cudaStream_t stream)
+{
+    if (tokens <= 0 || half <= 0)
+        return CHIBI_OK;
+    launch(chibi::rope_table_kernel, dim3(grid_for(tokens * half, 256)), dim3(256), 0, stream, positions, inv_freq,
+           tokens, half, out);
+    return launch_status();
+}
+
+CHIBI_API int chibi_cache_slots(const int* positions, const int* seq_of_token, const int* seq_rows,
+                                const int* block_table, int table_stride, long long tokens, int nkv, int page_size,
+                                int num_pages, int d, long long* out, int* error, cudaStream_t stream)
+{
+    if (tokens <= 0)
+        return CHIBI_OK;
+    if (nkv <= 0 || page_size <= 0 || d <= 0)
+        return CHIBI_ERR_ARGUMENT;
+    launch(chibi::cache_slots_kernel, dim3(grid_for(tokens, 256)), dim3(256), 0, stream, positions, seq_of_token,
+           seq_rows, block_table, table_stride, tokens, nkv, page_size, num_pages, d, out, error);
+    return launch_status();
+}

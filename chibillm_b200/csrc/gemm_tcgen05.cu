@@ -71,6 +71,20 @@ struct GemmParams {
     int row_ssq_parts;
     float row_eps;
     int row_n;
+    // Many rows, the q | k | v product finished head by head (head size 128: a 256-column tile is two
+    // heads, and a thread of the epilogue holds a token's whole head).  Query and key heads get their
+    // RMSNorm (weights may be null) and the split-half rotation with the token's cosines and sines;
+    // query heads go to q_out [M][nq * 128], key and value heads to the token's slot of the paged
+    // caches.  Nothing is written to `out`.
+    const float* h_cos_sin;        // [M][128]: 64 cosines then 64 sines of each token; null: not this mode
+    const long long* h_slots;      // [M]: element offset of the token's slot for kv head 0, or -1 (no write)
+    __nv_bfloat16* h_q_out;
+    __nv_bfloat16* h_k_cache;
+    __nv_bfloat16* h_v_cache;
+    const void* h_q_norm_w;
+    const void* h_k_norm_w;
+    int h_w_type, h_nq, h_nkv, h_page_size;
+    float h_eps, h_offset;
 };
 
 template <int BN>
@@ -347,6 +361,151 @@ __device__ __forceinline__ float silu_mul(float g, float u)
     return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
+// One 128 x 256 tile of the q | k | v product as two heads (see GemmParams): this thread's token is
+// row m0 + lane, `inv` the factor that the row of x lacked.  The rotation pairs column j with column
+// j + 64 of the same row, so the head is read in pairs of 32-column pieces; the results pass
+// through the staging buffer as two lines of 64 columns, as everywhere in this epilogue.
+__device__ __forceinline__ float head_weight(const void* w, int type, int col, float offset)
+{
+    return (type == CHIBI_F32 ? static_cast<const float*>(w)[col]
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[col])) + offset;
+}
+
+__device__ __forceinline__ void write_staged_line(uint8_t* stage, __nv_bfloat16* dst, int lane)
+{
+    const int sub = lane >> 3, unit = lane & 7;
+    const unsigned long long mine = reinterpret_cast<unsigned long long>(dst);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + sub;
+        const uint4 v = *stage_unit(stage, r, unit);
+        const unsigned long long d = __shfl_sync(0xffffffffu, mine, r);        // row r's destination
+        if (d)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(d) + unit * 8) = v;
+    }
+    __syncwarp();
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b)
+{
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t taddr, int m0, int lane, int tile_b,
+                                               uint8_t* stage, float inv)
+{
+    const int m = m0 + lane;
+    const bool row_ok = m < p.M;
+    const long long slot = (row_ok && p.h_slots) ? p.h_slots[m] : -1;
+    const float* cs = p.h_cos_sin + (size_t)(row_ok ? m : 0) * 128;
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        const int head = tile_b * 2 + hh;                         // the same for the whole warp
+        const uint32_t t0 = taddr + hh * 128;
+        const int kind = head < p.h_nq ? 0 : (head < p.h_nq + p.h_nkv ? 1 : 2);
+        __nv_bfloat16* dst = nullptr;                             // this thread's row of the head
+        if (row_ok) {
+            if (kind == 0)
+                dst = p.h_q_out + ((size_t)m * p.h_nq + head) * 128;
+            else if (slot >= 0 && kind == 1)
+                dst = p.h_k_cache + slot + (size_t)(head - p.h_nq) * p.h_page_size * 128;
+            else if (slot >= 0)
+                dst = p.h_v_cache + slot + (size_t)(head - p.h_nq - p.h_nkv) * p.h_page_size * 128;
+        }
+        if (kind == 2) {
+            // a value head: the sums as they are
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 64) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r32[32];
+                    tmem_load_32x32(t0 + c0 + 32 * h, r32);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *stage_unit(stage, lane, 4 * h + j) =
+                            make_uint4(pack_bf16(inv * __uint_as_float(r32[8 * j]), inv * __uint_as_float(r32[8 * j + 1])),
+                                       pack_bf16(inv * __uint_as_float(r32[8 * j + 2]), inv * __uint_as_float(r32[8 * j + 3])),
+                                       pack_bf16(inv * __uint_as_float(r32[8 * j + 4]), inv * __uint_as_float(r32[8 * j + 5])),
+                                       pack_bf16(inv * __uint_as_float(r32[8 * j + 6]), inv * __uint_as_float(r32[8 * j + 7])));
+                }
+                write_staged_line(stage, dst ? dst + c0 : nullptr, lane);
+            }
+            continue;
+        }
+        const void* w = kind == 0 ? p.h_q_norm_w : p.h_k_norm_w;
+        float inv_h = 1.f;
+        if (w) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+                uint32_t r32[32];
+                tmem_load_32x32(t0 + c0, r32);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float x = inv * __uint_as_float(r32[j]);
+                    ss = fmaf(x, x, ss);
+                }
+            }
+            inv_h = rsqrtf(ss / 128.f + p.h_eps);
+        }
+        uint32_t lo_keep[16], hi_keep[16];                        // columns 0..31 and 64..95 as bfloat16 pairs
+#pragma unroll
+        for (int c = 0; c < 64; c += 32) {
+            uint32_t a[32], b[32];
+            tmem_load_32x32(t0 + c, a);
+            tmem_load_32x32(t0 + 64 + c, b);
+            tmem_load_wait();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int j4 = 0; j4 < 32; j4 += 4) {
+                const float4 cv = *reinterpret_cast<const float4*>(cs + c + j4);
+                const float4 sv = *reinterpret_cast<const float4*>(cs + 64 + c + j4);
+                const float cosv[4] = { cv.x, cv.y, cv.z, cv.w }, sinv[4] = { sv.x, sv.y, sv.z, sv.w };
+                float ol[4], oh[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j4 + e;
+                    float x = inv * __uint_as_float(a[j]), y = inv * __uint_as_float(b[j]);
+                    if (w) {
+                        x = (x * inv_h) * head_weight(w, p.h_w_type, c + j, p.h_offset);
+                        y = (y * inv_h) * head_weight(w, p.h_w_type, 64 + c + j, p.h_offset);
+                    }
+                    ol[e] = x * cosv[e] - y * sinv[e];
+                    oh[e] = y * cosv[e] + x * sinv[e];
+                }
+                lo[j4 >> 1] = pack_bf16(ol[0], ol[1]);
+                lo[(j4 >> 1) + 1] = pack_bf16(ol[2], ol[3]);
+                hi[j4 >> 1] = pack_bf16(oh[0], oh[1]);
+                hi[(j4 >> 1) + 1] = pack_bf16(oh[2], oh[3]);
+            }
+            if (c == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    lo_keep[j] = lo[j];
+                    hi_keep[j] = hi[j];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    *stage_unit(stage, lane, j) = make_uint4(lo_keep[4 * j], lo_keep[4 * j + 1], lo_keep[4 * j + 2], lo_keep[4 * j + 3]);
+                    *stage_unit(stage, lane, 4 + j) = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+                }
+                write_staged_line(stage, dst, lane);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    *stage_unit(stage, lane, j) = make_uint4(hi_keep[4 * j], hi_keep[4 * j + 1], hi_keep[4 * j + 2], hi_keep[4 * j + 3]);
+                    *stage_unit(stage, lane, 4 + j) = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+                }
+                write_staged_line(stage, dst ? dst + 64 : nullptr, lane);
+            }
+        }
+    }
+}
+
 template <int BN>
 __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m0, int lane,
                                                     int tile_b, uint8_t* stage)
@@ -363,6 +522,12 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         inv = rsqrtf(ss / (float)p.row_n + p.row_eps);
     }
     // every branch below is taken by whole warps: tcgen05.ld is a warp-wide instruction
+    if constexpr (BN == 256) {
+        if (p.h_cos_sin) {
+            epilogue_heads(p, taddr, m0, lane, tile_b, stage, inv);
+            return;
+        }
+    }
     if (p.swiglu && inside && p.out_stride % 8 == 0) {
         // the BN columns are rows of w, which come as [64 gate | 64 up] blocks
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
@@ -1251,15 +1416,45 @@ struct ChibiNormOut {
 
 CHIBI_API int chibi_gemm_bf16_norm_parts(int N) { return N > 0 && N % 256 == 0 ? N / 256 : 0; }
 
+// `heads` (may be null; then `out` is not written and may be null): the product is q | k | v of
+// head size 128 (N = (nq + 2 nkv) * 128, or nq * 128 without caches) and every head is finished in
+// the epilogue: per-head RMSNorm for query and key heads (weights may be null), rotation of the whole
+// head with the token's cosines and sines, query heads to q_out, key and value heads to the token's
+// cache slot.
+struct ChibiHeadsOut {
+    const float* cos_sin;      // [M][128] from chibi_rope_table
+    const long long* slots;    // [M] from chibi_cache_slots; null without caches
+    void* q_out;               // [M][nq * 128] bfloat16
+    void* k_cache;             // [pages][nkv][page_size][128] bfloat16, or null
+    void* v_cache;
+    const void* q_norm_w;      // [128] or null
+    const void* k_norm_w;
+    int w_type, nq, nkv, page_size;
+    float eps, offset;
+};
+
 CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int out_type, const float* residual,
                                    int M, int N, int K, long long x_stride, long long w_stride, long long out_stride,
                                    long long res_stride, int epilogue, const ChibiRowScale* scale,
-                                   const ChibiNormOut* norm, int* error, cudaStream_t stream)
+                                   const ChibiNormOut* norm, const ChibiHeadsOut* heads, int* error,
+                                   cudaStream_t stream)
 {
     if (M <= 64 || N <= 0 || N % 256 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
         || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
         || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
         return CHIBI_ERR_UNSUPPORTED;
+    if (heads) {
+        const bool caches = heads->k_cache != nullptr;
+        if (epilogue != 0 || norm || residual)
+            return CHIBI_ERR_ARGUMENT;
+        if (!heads->cos_sin || !heads->q_out || heads->nq < 1 || heads->nkv < 0 || (caches && (!heads->v_cache || !heads->slots || heads->nkv < 1 || heads->page_size < 1))
+            || ((heads->q_norm_w || heads->k_norm_w) && heads->w_type != CHIBI_F32 && heads->w_type != CHIBI_BF16))
+            return CHIBI_ERR_ARGUMENT;
+        if ((long long)N != (long long)(heads->nq + (caches ? 2 * heads->nkv : 0)) * 128
+            || (reinterpret_cast<uintptr_t>(heads->q_out) & 15) || (reinterpret_cast<uintptr_t>(heads->cos_sin) & 15)
+            || (caches && ((reinterpret_cast<uintptr_t>(heads->k_cache) & 15) || (reinterpret_cast<uintptr_t>(heads->v_cache) & 15))))
+            return CHIBI_ERR_UNSUPPORTED;
+    }
     GemmParams p {};
     p.K = K;
     p.M = M;
@@ -1283,6 +1478,20 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         // the path that adds the residual in 32-bit, whole tiles only
         if (out_type != CHIBI_F32 || !residual || out_stride % 4 != 0 || res_stride % 4 != 0 || scale)
             return CHIBI_ERR_UNSUPPORTED;
+    } else if (heads) {
+        p.h_cos_sin = heads->cos_sin;
+        p.h_slots = heads->k_cache ? heads->slots : nullptr;
+        p.h_q_out = static_cast<__nv_bfloat16*>(heads->q_out);
+        p.h_k_cache = static_cast<__nv_bfloat16*>(heads->k_cache);
+        p.h_v_cache = static_cast<__nv_bfloat16*>(heads->v_cache);
+        p.h_q_norm_w = heads->q_norm_w;
+        p.h_k_norm_w = heads->k_norm_w;
+        p.h_w_type = heads->w_type;
+        p.h_nq = heads->nq;
+        p.h_nkv = heads->k_cache ? heads->nkv : 0;
+        p.h_page_size = heads->page_size;
+        p.h_eps = heads->eps;
+        p.h_offset = heads->offset;
     } else if (out_type != CHIBI_BF16 || residual || out_stride % 8 != 0) {
         return CHIBI_ERR_UNSUPPORTED;      // a factor is applied where the sums become bfloat16
     }

@@ -82,6 +82,9 @@ class StepContext:
     max_q_len: int = 0
     min_q_len: int = 0
     max_ctx_len: int = 0
+    # what several layers of this step share: a part computes a value when it first needs it and
+    # files it under a key that says what it depends on (a table of rotation angles, cache slots)
+    shared: Dict[Hashable, object] = field(default_factory=dict)
 
     @property
     def seq_rows(self) -> torch.Tensor:

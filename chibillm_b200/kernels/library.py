@@ -32,7 +32,9 @@ _SIGNATURES = {
         "chibi_gemm_set_stream_scratch": [P, L],
         "chibi_gemm_reset_stream_counters": [P],
         "chibi_gemm_bf16_norm_parts": [I],
-        "chibi_gemm_bf16_rows": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P, P, P],
+        "chibi_gemm_bf16_rows": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P, P, P, P],
+        "chibi_rope_table": [P, P, L, I, P, P],
+        "chibi_cache_slots": [P, P, P, P, I, L, I, I, I, I, P, P, P],
         "chibi_scale_rows": [P, L, I, L, P, I, F, I, P],
         "chibi_gemm_bf16_fused": [P, P, P, I, P, I, I, I, L, L, L, L, I, P, P],
         "chibi_gemm_bf16_partial": [P, P, I, I, I, L, L, P, L, I, P, P],
@@ -65,6 +67,13 @@ class NormOut(ctypes.Structure):
     """ChibiNormOut of gemm_tcgen05.cu: the norm output that a product writes beside the residual."""
     _fields_ = [("w", c_void_p), ("w_type", c_int), ("offset", c_float), ("out", c_void_p),
                 ("out_stride", c_longlong), ("ssq", c_void_p), ("ssq_floats", c_longlong)]
+
+
+class HeadsOut(ctypes.Structure):
+    """ChibiHeadsOut of gemm_tcgen05.cu: where the heads of a q | k | v product go."""
+    _fields_ = [("cos_sin", c_void_p), ("slots", c_void_p), ("q_out", c_void_p), ("k_cache", c_void_p),
+                ("v_cache", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_type", c_int),
+                ("nq", c_int), ("nkv", c_int), ("page_size", c_int), ("eps", c_float), ("offset", c_float)]
 
 
 class KernelLibraryError(RuntimeError):

@@ -174,6 +174,7 @@ class CudaKernels:
         # Many rows: the product that completes the residual also writes the following RMSNorm's
         # output, up to the factor of each row, which the next product applies to its sums.
         self.fold_norms = True
+        self.fold_heads = True           # many rows: the q | k | v product finishes its heads itself
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
         # global scratch to a second kernel that also does what follows the product.
         self.fuse_split_products = True
@@ -250,7 +251,8 @@ class CudaKernels:
                                ssq.numel())
         status = self.lib.chibi_gemm_bf16_rows(
             _ptr(x), _ptr(w), _ptr(residual), F32, _ptr(residual), M, N, K, x.stride(0), w.stride(0),
-            residual.stride(0), residual.stride(0), 0, None, ctypes.byref(norm), _ptr(self.error), self._stream())
+            residual.stride(0), residual.stride(0), 0, None, ctypes.byref(norm), None, _ptr(self.error),
+            self._stream())
         if status == -2:
             return None
         _check(status, "linear (+ residual, + norm output)")
@@ -285,10 +287,95 @@ class CudaKernels:
         scale = library.RowScale(_ptr(x.ssq), x.parts, float(x.eps), x.n)
         status = self.lib.chibi_gemm_bf16_rows(
             _ptr(t), _ptr(w), _ptr(out), BF16, None, M, N, K, t.stride(0), w.stride(0), out.stride(0), 0,
-            1 if swiglu else 0, ctypes.byref(scale), None, _ptr(self.error), self._stream())
+            1 if swiglu else 0, ctypes.byref(scale), None, None, _ptr(self.error), self._stream())
         if status == -2:
             return False
         _check(status, "linear (rows with a factor)")
+        self.launches += 1
+        self.tensor_core_calls += 1
+        return True
+
+    # ---- the q | k | v product of many rows that finishes its heads itself
+    def finishes_heads(self, rows: int, d: int, rotary_dim: int, dtype: torch.dtype) -> bool:
+        """Whether ``linear_heads`` takes a step of so many rows with this head size."""
+        return bool(self.use_tensor_cores and self.fold_heads and rows > 64 and d == 128 and rotary_dim == d
+                    and dtype == torch.bfloat16)
+
+    def rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                   out: torch.Tensor) -> None:
+        """out[t] = the cosines, then the sines, of float(positions[t]) * inv_freq[j]."""
+        _need_cuda(positions, inv_freq, out)
+        T, half = positions.numel(), rotary_dim // 2
+        if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32 or inv_freq.numel() < half \
+                or out.dtype != torch.float32 or out.shape != (T, 2 * half) or not out.is_contiguous():
+            raise KernelError("rope_table: int32 positions, float32 inv_freq and out [T, rotary_dim]")
+        self.launches += 1
+        _check(self.lib.chibi_rope_table(_ptr(positions), _ptr(inv_freq), T, half, _ptr(out), self._stream()),
+               "rope_table")
+
+    def cache_slots(self, positions: torch.Tensor, seq_of_token: torch.Tensor, seq_rows: Optional[torch.Tensor],
+                    block_table: torch.Tensor, nkv: int, page_size: int, num_pages: int, d: int,
+                    out: torch.Tensor) -> None:
+        """out[t] = where token t's key (and value) of kv head 0 lies in a cache
+        [pages, nkv, page_size, d], in elements; -1 and a recorded error if its
+        block table has no page there."""
+        _need_cuda(positions, seq_of_token, seq_rows, block_table, out)
+        _rows_contiguous(block_table, "cache_slots: block_table")
+        T = positions.numel()
+        if out.dtype != torch.int64 or out.numel() != T or not out.is_contiguous():
+            raise KernelError("cache_slots: out must be contiguous int64 [T]")
+        self.launches += 1
+        _check(self.lib.chibi_cache_slots(_ptr(positions), _ptr(seq_of_token), _ptr(seq_rows), _ptr(block_table),
+                                          block_table.stride(0), T, nkv, page_size, num_pages, d, _ptr(out),
+                                          _ptr(self.error), self._stream()), "cache_slots")
+
+    def linear_heads(self, x, w: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], q_norm_w: Optional[torch.Tensor],
+                     k_norm_w: Optional[torch.Tensor], cos_sin: torch.Tensor, slots: Optional[torch.Tensor],
+                     nq: int, nkv: int, d: int, page_size: int, eps: float, norm_offset: float) -> bool:
+        """q | k | v = x @ w^T of many rows with every head finished by the product's
+        own epilogue: per-head RMSNorm (if weights are given), rotation of the whole
+        head with ``cos_sin`` (``rope_table``), query heads to ``q_out``, key and
+        value heads to the cache slots ``slots`` (``cache_slots``).  x may be
+        ScaledRows.  False if the kernel does not take the shapes; nothing has run then."""
+        scale = None
+        if isinstance(x, ScaledRows):
+            scale = library.RowScale(_ptr(x.ssq), x.parts, float(x.eps), x.n)
+            x = x.tensor
+        append = k_cache is not None
+        T, K = x.shape
+        N = w.shape[0]
+        if not self.finishes_heads(T, d, d, x.dtype) or w.dtype != torch.bfloat16 or w.shape[1] != K \
+                or N != (nq + (2 * nkv if append else 0)) * d or N % 256 != 0 or q_out.dtype != torch.bfloat16:
+            return False
+        for t in (q_norm_w, k_norm_w):
+            if t is not None and (t.dtype not in (torch.bfloat16, torch.float32) or t.numel() != d
+                                  or not t.is_contiguous()):
+                return False
+        if (q_norm_w is None) != (k_norm_w is None) or (q_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype):
+            return False
+        _need_cuda(x, w, q_out, k_cache, v_cache, q_norm_w, k_norm_w, cos_sin, slots)
+        _rows_contiguous(x, "linear_heads: x")
+        _rows_contiguous(w, "linear_heads: w")
+        if q_out.shape != (T, nq * d) or not q_out.is_contiguous() or cos_sin.dtype != torch.float32 \
+                or cos_sin.shape != (T, d) or not cos_sin.is_contiguous():
+            raise KernelError("linear_heads: q_out [T, nq * d] bfloat16 and cos_sin [T, d] float32")
+        if append and (k_cache.dtype != torch.bfloat16 or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                       or not k_cache.is_contiguous() or v_cache is None or v_cache.shape != k_cache.shape
+                       or not v_cache.is_contiguous() or slots is None or slots.dtype != torch.int64
+                       or slots.numel() != T):
+            raise KernelError("linear_heads: caches [pages, nkv, page_size, d] bfloat16 and int64 slots [T]")
+        heads = library.HeadsOut(_ptr(cos_sin), _ptr(slots) if append else None, _ptr(q_out), _ptr(k_cache),
+                                 _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w),
+                                 _code(q_norm_w) if q_norm_w is not None else F32, nq, nkv if append else 0,
+                                 page_size, float(eps), float(norm_offset))
+        status = self.lib.chibi_gemm_bf16_rows(
+            _ptr(x), _ptr(w), None, BF16, None, T, N, K, x.stride(0), w.stride(0), N, 0, 0,
+            ctypes.byref(scale) if scale is not None else None, None, ctypes.byref(heads), _ptr(self.error),
+            self._stream())
+        if status == -2:
+            return False
+        _check(status, "linear (q | k | v heads)")
         self.launches += 1
         self.tensor_core_calls += 1
         return True

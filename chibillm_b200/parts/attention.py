@@ -83,6 +83,8 @@ class PagedAttention(Mixer):
         writes = cache.writes
         width = qw + 2 * kw if writes else qw
         fused = self.position.fused_rotation()
+        if fused is not None and fused[0] is not None and self._heads_from_the_product(x, ctx, cache, fused):
+            return self._attend(residual, ctx, cache)
         split = getattr(k, "linear_partial", None)
         pending = None
         if split is not None and fused is not None and d % 4 == 0:
@@ -127,10 +129,54 @@ class PagedAttention(Mixer):
             norm.weight_offset if norm is not None else 0.0,
             ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size,
             ctx.seq_rows)
-        k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len,
+        return self._attend(residual, ctx, cache)
+
+    def _attend(self, residual, ctx, cache):
+        """Attention over the cache from the step's q, then the output product, left
+        for the next norm to add into the residual."""
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
+        T = ctx.num_tokens
+        q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
+        att = ctx.workspace.get("attn.out", (T, nq * d), rt.dtype)
+        k.attention(q, cache.keys, cache.values, att, ctx.tables[cache.group], ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
                     s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows)
         return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
+
+    def _heads_from_the_product(self, x, ctx, cache, fused) -> bool:
+        """Many rows on kernels that can do it: the q | k | v product normalises and
+        rotates its heads itself and writes q and the cache entries; no q | k | v
+        array exists.  The rotation table and the tokens' cache slots are made once
+        per step and shared by the layers."""
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        takes = getattr(k, "finishes_heads", None)
+        T = ctx.num_tokens
+        nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
+        if takes is None or not takes(T, d, fused[1], rt.dtype):
+            return False
+        cos_sin = self.position.step_table(ctx)
+        if cos_sin is None:
+            return False
+        writes = cache.writes
+        slots = None
+        if writes:
+            key = ("cache slots", cache.group, nkv, d, cache.page_size)
+            slots = ctx.shared.get(key)
+            if slots is None:
+                slots = ctx.workspace.get(f"attn.slots.{cache.group}", (T,), torch.int64)
+                k.cache_slots(ctx.positions, ctx.seq_of_token, ctx.seq_rows, ctx.tables[cache.group], nkv,
+                              cache.page_size, cache.keys.shape[0], d, slots)
+                ctx.shared[key] = slots
+        norm = s.qk_norm
+        q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
+        return k.linear_heads(x, self.qkv if writes else self.qkv[:nq * d], q, cache.keys if writes else None,
+                              cache.values if writes else None, self.q_norm if norm is not None else None,
+                              self.k_norm if norm is not None else None, cos_sin, slots, nq, nkv, d,
+                              cache.page_size, norm.eps if norm is not None else 0.0,
+                              norm.weight_offset if norm is not None else 0.0)
 
 
 register_mixer("attention", PagedAttention, replace=True)

@@ -107,6 +107,13 @@ class PositionEncoding(Part):
     def fused_rotation(self):
         return None
 
+    def step_table(self, ctx):
+        """[tokens, rotary_dim] float32: the cosines, then the sines, of every token
+        of the step, for kernels that rotate from a table; computed once per step
+        and shared through ``ctx.shared`` by all layers with the same constants.
+        None if the encoding has no such table."""
+        return None
+
     def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], ctx) -> None:
         raise NotImplementedError
 

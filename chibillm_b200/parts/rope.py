@@ -34,6 +34,19 @@ class RotaryEncoding(PositionEncoding):
     def fused_rotation(self):
         return self.inv_freq, self.spec.rotary_dim
 
+    def step_table(self, ctx):
+        table_of = getattr(self.runtime.kernels, "rope_table", None)
+        if table_of is None:
+            return None
+        key = ("rope", float(self.spec.theta), int(self.spec.rotary_dim))
+        table = ctx.shared.get(key)
+        if table is None:
+            table = ctx.workspace.get(f"rope.table.{key[1]}.{key[2]}", (ctx.num_tokens, self.spec.rotary_dim),
+                                      torch.float32)
+            table_of(ctx.positions, self.inv_freq, self.spec.rotary_dim, table)
+            ctx.shared[key] = table
+        return table
+
 
 class NoPosition(PositionEncoding):
     def __init__(self, spec, runtime: Runtime):

@@ -601,6 +601,88 @@ def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
     close(vc2, vc3, torch.bfloat16, "value cache vs the plain restatement", rel=8e-3)
 
 
+@pytest.mark.parametrize("nq,nkv,norms,wdtype,append", [(6, 2, True, torch.bfloat16, True),
+                                                        (4, 1, True, torch.float32, True),
+                                                        (8, 4, False, torch.bfloat16, True),
+                                                        (4, 2, True, torch.bfloat16, False)])
+@pytest.mark.parametrize("seq_ctx,q_lens,scaled", [([70, 8, 300], [40, 1, 133], False),
+                                                   ([257, 130, 64, 90], [257, 2, 64, 77], True)])
+def test_product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled):
+    """The q | k | v product of many rows whose epilogue normalises and rotates the
+    heads and writes q and the cache entries (head size 128), against the plain
+    product followed by the plain norm + rotation + append; with and without a row
+    factor left by the norm before (``ScaledRows``); rows that end inside a tile."""
+    from chibillm_b200.kernels.ops import ScaledRows
+    d, page, K = 128, 16, 520
+    T = sum(q_lens)
+    pages = sum((c + page - 1) // page for c in seq_ctx) + 3
+    table, positions, seq_of_token, _, _ = _paged_setup(seq_ctx, q_lens, page, pages, seed=120)
+    width = (nq + 2 * nkv) * d if append else nq * d
+    x = rnd(T, K, dtype=torch.bfloat16, seed=121)
+    w = rnd(width, K, dtype=torch.bfloat16, seed=122, scale=0.05)
+    qn = (1 + 0.1 * rnd(d, seed=123)).to(wdtype) if norms else None
+    kn = (1 + 0.1 * rnd(d, seed=124)).to(wdtype) if norms else None
+    inv_freq = torch.pow(torch.tensor(1e6), -2 * torch.arange(d // 2, dtype=torch.float32) / d).cuda()
+    kc0 = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=125)
+    vc0 = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=126)
+
+    given, x_plain = x, x.float()
+    if scaled:
+        parts, n, eps = 3, 4 * K, 1e-5
+        ssq = (rnd(T, parts, seed=127).abs() * n).contiguous()
+        given = ScaledRows(k, x, ssq, parts, eps, n)
+        x_plain = x.float() * torch.rsqrt(ssq.sum(dim=1, keepdim=True) / n + eps)
+
+    cos_sin = torch.full((T, d), float("nan"), dtype=torch.float32, device="cuda")
+    k.rope_table(positions, inv_freq, d, cos_sin)
+    angles = positions.float()[:, None] * inv_freq[None, :]
+    assert torch.equal(cos_sin[:, :d // 2], torch.cos(angles)) or float((cos_sin[:, :d // 2] - torch.cos(angles)).abs().max()) < 1e-6
+    assert float((cos_sin[:, d // 2:] - torch.sin(angles)).abs().max()) < 1e-6
+    slots = None
+    if append:
+        slots = torch.full((T,), -7, dtype=torch.int64, device="cuda")
+        k.cache_slots(positions, seq_of_token, None, table, nkv, page, pages, d, slots)
+        exp_slots = (table[seq_of_token.long(), (positions // page).long()].long() * nkv * page + positions.long() % page) * d
+        assert torch.equal(slots, exp_slots)
+
+    q = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc, vc = kc0.clone(), vc0.clone()
+    assert k.linear_heads(given, w, q, kc if append else None, vc if append else None, qn, kn, cos_sin, slots,
+                          nq, nkv, d, page, 1e-6, 0.0)
+    k.check_error_word()
+
+    qkv = x_plain @ w.float().t()
+    q_exp = torch.empty(T, nq * d, dtype=torch.float32, device="cuda")
+    kc_exp, vc_exp = kc0.float(), vc0.float()
+    ref.qk_norm_rope_append(qkv, q_exp, kc_exp if append else None, vc_exp if append else None, qn, kn, inv_freq,
+                            d, 1e-6, 0.0, positions, seq_of_token, table if append else None, nq, nkv, d, page)
+    close(q, q_exp, torch.bfloat16, "heads from the product: q", rel=8e-3)
+    if append:
+        close(kc, kc_exp, torch.bfloat16, "heads from the product: key cache", rel=8e-3)
+        close(vc, vc_exp, torch.bfloat16, "heads from the product: value cache", rel=8e-3)
+        # slots of tokens that were not in the step are untouched
+        written = torch.zeros(pages * nkv * page, dtype=torch.bool, device="cuda")
+        for h in range(nkv):
+            written[(slots // d + h * page).long()] = True
+        untouched = ~written.view(pages, nkv, page)
+        assert torch.equal(kc[untouched], kc0[untouched]) and torch.equal(vc[untouched], vc0[untouched])
+
+
+def test_product_that_finishes_its_heads_refuses_what_it_does_not_take(k):
+    """Few rows, another head size or an odd number of heads: False, nothing runs."""
+    d, K = 128, 256
+    cos_sin = torch.zeros(300, d, device="cuda")
+    x = rnd(300, K, dtype=torch.bfloat16, seed=1)
+    q = torch.zeros(300, 3 * d, dtype=torch.bfloat16, device="cuda")
+    w = rnd(3 * d, K, dtype=torch.bfloat16, seed=2)
+    assert not k.linear_heads(x, w, q, None, None, None, None, cos_sin, None, 3, 0, d, 16, 1e-6, 0.0)
+    assert not k.finishes_heads(64, 128, 128, torch.bfloat16)
+    assert not k.finishes_heads(300, 64, 64, torch.bfloat16)
+    assert not k.finishes_heads(300, 128, 64, torch.bfloat16)
+    assert not k.finishes_heads(300, 128, 128, torch.float32)
+    assert float(q.abs().max()) == 0.0
+
+
 def test_a_pending_sum_that_was_overwritten_is_refused(k):
     """Split products take two scratch arrays in turn: the third one started
     writes over the first one's sums, and reading those then must raise."""
