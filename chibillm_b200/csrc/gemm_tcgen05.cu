@@ -393,8 +393,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// head_w: [2][128] floats in shared memory, the norm weights (+ offset) of query and key heads
+// (ones without a norm).
 __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t taddr, int m0, int lane, int tile_b,
-                                               uint8_t* stage, float inv)
+                                               uint8_t* stage, float inv, const float* head_w)
 {
     const int m = m0 + lane;
     const bool row_ok = m < p.M;
@@ -435,9 +437,18 @@ __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t tad
             }
             continue;
         }
-        const void* w = kind == 0 ? p.h_q_norm_w : p.h_k_norm_w;
-        float inv_h = 1.f;
-        if (w) {
+        const bool normed = (kind == 0 ? p.h_q_norm_w : p.h_k_norm_w) != nullptr;
+        const float* w = head_w + kind * 128;
+        // the row's cosines and sines of the first columns are on their way while the sum of
+        // squares is taken
+        float4 cv[4], sv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            cv[u] = *reinterpret_cast<const float4*>(cs + 4 * u);
+            sv[u] = *reinterpret_cast<const float4*>(cs + 64 + 4 * u);
+        }
+        float scale = inv;                                        // the row's factor times the head's
+        if (normed) {
             float ss = 0.f;
 #pragma unroll 1
             for (int c0 = 0; c0 < 128; c0 += 32) {
@@ -450,65 +461,63 @@ __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t tad
                     ss = fmaf(x, x, ss);
                 }
             }
-            inv_h = rsqrtf(ss / 128.f + p.h_eps);
+            scale = inv * rsqrtf(ss / 128.f + p.h_eps);
         }
-        uint32_t lo_keep[16], hi_keep[16];                        // columns 0..31 and 64..95 as bfloat16 pairs
+        uint32_t lo[32], hi[32];                                  // columns 0..63 and 64..127 as bfloat16 pairs
 #pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-            uint32_t a[32], b[32];
-            tmem_load_32x32(t0 + c, a);
-            tmem_load_32x32(t0 + 64 + c, b);
+        for (int c = 0; c < 64; c += 16) {
+            uint32_t a[16], b[16];
+            tmem_load_32x16(t0 + c, a);
+            tmem_load_32x16(t0 + 64 + c, b);
+            float4 cn[4], sn[4];                                  // the next columns' angles
+            if (c + 16 < 64) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    cn[u] = *reinterpret_cast<const float4*>(cs + c + 16 + 4 * u);
+                    sn[u] = *reinterpret_cast<const float4*>(cs + 64 + c + 16 + 4 * u);
+                }
+            }
             tmem_load_wait();
-            uint32_t lo[16], hi[16];
 #pragma unroll
-            for (int j4 = 0; j4 < 32; j4 += 4) {
-                const float4 cv = *reinterpret_cast<const float4*>(cs + c + j4);
-                const float4 sv = *reinterpret_cast<const float4*>(cs + 64 + c + j4);
-                const float cosv[4] = { cv.x, cv.y, cv.z, cv.w }, sinv[4] = { sv.x, sv.y, sv.z, sv.w };
+            for (int u = 0; u < 4; ++u) {
+                const float cosv[4] = { cv[u].x, cv[u].y, cv[u].z, cv[u].w };
+                const float sinv[4] = { sv[u].x, sv[u].y, sv[u].z, sv[u].w };
                 float ol[4], oh[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int j = j4 + e;
-                    float x = inv * __uint_as_float(a[j]), y = inv * __uint_as_float(b[j]);
-                    if (w) {
-                        x = (x * inv_h) * head_weight(w, p.h_w_type, c + j, p.h_offset);
-                        y = (y * inv_h) * head_weight(w, p.h_w_type, 64 + c + j, p.h_offset);
-                    }
+                    const int j = 4 * u + e;
+                    const float x = (scale * __uint_as_float(a[j])) * w[c + j];
+                    const float y = (scale * __uint_as_float(b[j])) * w[64 + c + j];
                     ol[e] = x * cosv[e] - y * sinv[e];
                     oh[e] = y * cosv[e] + x * sinv[e];
                 }
-                lo[j4 >> 1] = pack_bf16(ol[0], ol[1]);
-                lo[(j4 >> 1) + 1] = pack_bf16(ol[2], ol[3]);
-                hi[j4 >> 1] = pack_bf16(oh[0], oh[1]);
-                hi[(j4 >> 1) + 1] = pack_bf16(oh[2], oh[3]);
+                lo[(c >> 1) + 2 * u] = pack_bf16(ol[0], ol[1]);
+                lo[(c >> 1) + 2 * u + 1] = pack_bf16(ol[2], ol[3]);
+                hi[(c >> 1) + 2 * u] = pack_bf16(oh[0], oh[1]);
+                hi[(c >> 1) + 2 * u + 1] = pack_bf16(oh[2], oh[3]);
             }
-            if (c == 0) {
+            if (c + 16 < 64) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    lo_keep[j] = lo[j];
-                    hi_keep[j] = hi[j];
+                for (int u = 0; u < 4; ++u) {
+                    cv[u] = cn[u];
+                    sv[u] = sn[u];
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    *stage_unit(stage, lane, j) = make_uint4(lo_keep[4 * j], lo_keep[4 * j + 1], lo_keep[4 * j + 2], lo_keep[4 * j + 3]);
-                    *stage_unit(stage, lane, 4 + j) = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
-                }
-                write_staged_line(stage, dst, lane);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    *stage_unit(stage, lane, j) = make_uint4(hi_keep[4 * j], hi_keep[4 * j + 1], hi_keep[4 * j + 2], hi_keep[4 * j + 3]);
-                    *stage_unit(stage, lane, 4 + j) = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
-                }
-                write_staged_line(stage, dst ? dst + 64 : nullptr, lane);
             }
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *stage_unit(stage, lane, j) = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+        write_staged_line(stage, dst, lane);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *stage_unit(stage, lane, j) = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+        write_staged_line(stage, dst ? dst + 64 : nullptr, lane);
     }
 }
 
 template <int BN>
 __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m0, int lane,
-                                                    int tile_b, uint8_t* stage)
+                                                    int tile_b, uint8_t* stage, const float* head_w = nullptr)
 {
     const int m = m0 + lane;
     const int sub = lane >> 3, unit = lane & 7;      // the write-out: rows 4 * i + sub, 16-byte unit `unit`
@@ -524,7 +533,7 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
     // every branch below is taken by whole warps: tcgen05.ld is a warp-wide instruction
     if constexpr (BN == 256) {
         if (p.h_cos_sin) {
-            epilogue_heads(p, taddr, m0, lane, tile_b, stage, inv);
+            epilogue_heads(p, taddr, m0, lane, tile_b, stage, inv, head_w);
             return;
         }
     }
@@ -910,8 +919,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t* collect_bar = tmem_empty_bar + 2;       // [4][3]: the bulk copies of a shared-out tile's other sums
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(collect_bar + 12);
     uint8_t* stage_base = reinterpret_cast<uint8_t*>(tmem_slot + 4);      // 16-byte aligned
+    float* head_w = reinterpret_cast<float*>(stage_base + 4 * EPILOGUE_STAGE_BYTES);   // [2][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr uint32_t TMEM_COLS = 2 * BN;
+    if (p.h_cos_sin && threadIdx.x < 128) {
+        // the norm weights of query and key heads (weights: nothing of this step writes them)
+        head_w[threadIdx.x] = p.h_q_norm_w ? head_weight(p.h_q_norm_w, p.h_w_type, threadIdx.x, p.h_offset) : 1.f;
+        head_w[128 + threadIdx.x] = p.h_k_norm_w ? head_weight(p.h_k_norm_w, p.h_w_type, threadIdx.x, p.h_offset) : 1.f;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -1015,7 +1030,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                               collect_bar + 3 * quarter);
                 }
                 epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
-                                        stage_base + quarter * EPILOGUE_STAGE_BYTES);
+                                        stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
             }
             tcgen05_fence_before();
             mbar_arrive(&tmem_empty_bar[buf]);
@@ -1079,7 +1094,7 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
                                   int tiles_m, int tiles_n, cudaStream_t stream, bool share_last_round = true)
 {
     constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4 + 12) * 8 + 16
-        + 4 * EPILOGUE_STAGE_BYTES + 1024;
+        + 4 * EPILOGUE_STAGE_BYTES + 2 * 128 * sizeof(float) + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
