@@ -133,6 +133,11 @@ class DeferredProduct:
 
 _STREAM_SCRATCH: Dict[torch.device, torch.Tensor] = {}
 
+# torch's own fast path to the current stream's handle (a plain integer): the public
+# torch.cuda.current_stream() builds a Stream object through several Python layers, a quarter
+# of the host time of a step that launches a few hundred kernels
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
 
 class CudaKernels:
     """The one set of operations of the product path."""
@@ -154,6 +159,7 @@ class CudaKernels:
             self._defines = (DEFINE,)
         self.lib = self._load("chibi_kernels")
         self.profiler = None        # a LaunchProfiler while the profiling mode is on
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host: Optional[torch.Tensor] = None
         self.launches = 0           # kernels of this package launched so far
@@ -388,9 +394,12 @@ class CudaKernels:
         return self._scratch_buf
 
     # ------------------------------------------------------------------ helpers
-    @staticmethod
-    def _stream() -> int:
-        return torch.cuda.current_stream().cuda_stream
+    def _stream(self) -> int:
+        """The handle of this device's current stream (asked for at every launch:
+        the caller may be inside a stream capture or a stream context)."""
+        if _raw_current_stream is not None:
+            return _raw_current_stream(self._device_index)
+        return torch.cuda.current_stream(self.device).cuda_stream
 
     def error_word_async(self) -> None:
         """Starts the copy of the error word to the host; ``check_error_copy`` reads it
