@@ -321,34 +321,47 @@ def measure_mixed(cfg, layers, full_layers, requests, shape, check_tokens=0):
             "steps_from_graphs": replays, "steps_launched_ahead": ahead, "check": check}
 
 
-def print_timeline(cfg, batch, held):
+def print_timeline(cfg, batch, held, prompt_tokens=0):
     """One decode step, replayed from its CUDA graph, as its CTAs saw it: for every launch when
     its first and last CTA started, when their wait for the launch before ended and when they
     left (microseconds from the step's start), and the points that kernels mark inside
-    (chibillm_b200/kernels/timeline.py; the libraries are built with -DCHIBI_TIMELINE for this)."""
+    (chibillm_b200/kernels/timeline.py; the libraries are built with -DCHIBI_TIMELINE for this).
+    With ``prompt_tokens`` the step is a prompt of so many tokens instead."""
     import torch
     from chibillm_b200.engine.batch import StepEntry
     from chibillm_b200.engine.runner import ModelRunner
     from chibillm_b200.kernels.ops import CudaKernels
 
     kernels = CudaKernels(torch.device("cuda:0"), timeline=True)
-    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", page_size=16, pool_tokens=batch * (held + 128),
+    pool = max(batch * (held + 128), prompt_tokens + 128)
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", page_size=16, pool_tokens=pool,
                                      max_requests=batch, kernels=kernels)
     for name in runner.storage.keys:
         runner.storage.keys[name].normal_()
         runner.storage.values[name].normal_()
-    ids = [f"r{i}" for i in range(batch)]
-    for rid in ids:
-        fill_request(runner, rid, held)
-    for i in range(6):
-        runner.step([StepEntry(rid, [5 + i], [0]) for rid in ids])
-    torch.cuda.synchronize()
-    kernels.timeline.reset()
-    runner.step([StepEntry(rid, [77], [0]) for rid in ids])
+    if prompt_tokens > 0:
+        g = torch.Generator().manual_seed(2)
+        for i in range(3):
+            ids = torch.randint(0, cfg["vocab_size"], (prompt_tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            kernels.timeline.reset()
+            runner.step([StepEntry("prompt", ids, [prompt_tokens - 1])])
+            torch.cuda.synchronize()
+            runner.end("prompt")
+        print(f"# prompt step of {prompt_tokens} tokens, {cfg['num_hidden_layers']} layers; times in us")
+    else:
+        ids = [f"r{i}" for i in range(batch)]
+        for rid in ids:
+            fill_request(runner, rid, held)
+        for i in range(6):
+            runner.step([StepEntry(rid, [5 + i], [0]) for rid in ids])
+        torch.cuda.synchronize()
+        kernels.timeline.reset()
+        runner.step([StepEntry(rid, [77], [0]) for rid in ids])
+        print(f"# decode step of {batch} x {held} tokens, {cfg['num_hidden_layers']} layers, from a graph: "
+              f"{runner.graph_replays > 0}; times in us")
     launches = kernels.timeline.launches()
     cell = lambda v: "       -" if v is None else f"{v:8.2f}"
-    print(f"# decode step of {batch} x {held} tokens, {cfg['num_hidden_layers']} layers, from a graph: "
-          f"{runner.graph_replays > 0}; times in us")
     print(f"{'kernel':42s} {'ctas':>5s} {'sms':>4s} {'start0':>8s} {'start1':>8s} {'wait0':>8s} {'wait1':>8s} "
           f"{'end0':>8s} {'end1':>8s}  marks (first..last CTA)")
     for l in launches:
@@ -377,6 +390,8 @@ def main() -> int:
                          "and 256 new tokens each through the Python entry point; prints its own JSON line")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the record: the timeline of one decode step (use with --layers 4 or so)")
+    ap.add_argument("--timeline-prompt", type=int, default=0,
+                    help="with --timeline: the step is a prompt of so many tokens instead of a decode step")
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
@@ -407,7 +422,7 @@ def main() -> int:
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
     if args.timeline:
-        print_timeline(cfg, args.batch, args.prompt)
+        print_timeline(cfg, args.batch, args.prompt, args.timeline_prompt)
         return 0
     if args.mixed_requests > 0:
         print(json.dumps(measure_mixed(cfg, layers, full_layers, args.mixed_requests, args.shape,

@@ -546,6 +546,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
+    timeline_mark(0);                  // the query rows are in shared memory
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -748,7 +749,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             tmem_store_wait();
             tcgen05_fence_before();
             mbar_arrive(&p_full[q]);
+            if (j == 0)
+                timeline_mark(1);      // the first tile's probabilities are written
         }
+        timeline_mark(2);              // the last tile's probabilities are written
         // the last product has landed: normalise and write the rows out
         if (my_tiles > 0) {
             mbar_wait(&o_done[q], (my_tiles - 1) & 1, p.error, 48);
