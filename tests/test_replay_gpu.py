@@ -27,10 +27,13 @@ CASES = {
     # finishes the q|k|v product itself (a window of 200 on the second layer)
     "D64": ("D64", 16, [2, 90, 260, 400]),
     "D128": ("D128", 16, [4, 65, 300, 520]),
+    # sizes that the many-row products take with the norms folded in and the heads finished in the
+    # q|k|v epilogue (prompts of more than 64 tokens), a window of 150 on the second layer
+    "E128": ("E128", 8, [3, 70, 200, 410]),
 }
 MIXED_LENGTHS = {"A": [50, 100, 30, 128, 64, 90, 17], "B": [1, 200, 33, 250, 64, 129, 7],
                  "C": [300, 20, 150, 65, 333, 2, 180], "D64": [400, 31, 129, 64, 350, 3, 222],
-                 "D128": [17, 520, 66, 250, 2, 480, 128]}
+                 "D128": [17, 520, 66, 250, 2, 480, 128], "E128": [410, 9, 130, 65, 300, 1, 222]}
 
 
 @pytest.fixture(scope="module")
@@ -70,6 +73,10 @@ def test_cutting_and_batching(folders, expected, case, dtype):
     whole = helpers.run_trace(runner, helpers.trace_whole(reqs))
     helpers.assert_logits_close(whole, ref, tol, f"{case} {dtype} whole")
     runner.cache.check_invariants()
+    if case == "E128" and dtype == "bfloat16":
+        # the prompts of more than 64 tokens went the way this case is here for: the q|k|v product
+        # wrote q and the cache itself, from the per-step table of cache slots
+        assert any(name.startswith("attn.slots") for name, _ in runner.workspace._buffers)
 
     tail = helpers.run_trace(runner, helpers.trace_last_decoded(reqs, 32))
     helpers.assert_logits_close(tail, ref, tol, f"{case} {dtype} last 32 decoded")

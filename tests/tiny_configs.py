@@ -49,7 +49,16 @@ SMALL_D128 = _base(num_hidden_layers=2, hidden_size=384, num_attention_heads=5, 
                    rms_norm_eps=1e-5, max_position_embeddings=4096, tie_word_embeddings=True,
                    use_sliding_window=True, sliding_window=200, max_window_layers=1)
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D64": SMALL_D64, "D128": SMALL_D128}
+# head size 128 with an even number of heads in q | k | v and widths that are multiples of 256: the
+# kernels for many rows that fold the norms into the products and finish the heads in the q | k | v
+# product's epilogue take these sizes; a window on the second layer
+SMALL_E128 = _base(num_hidden_layers=3, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                   head_dim=128, intermediate_size=384, vocab_size=1201, rope_theta=250000.0,
+                   rms_norm_eps=2e-6, max_position_embeddings=1024, tie_word_embeddings=False,
+                   use_sliding_window=True, sliding_window=150,
+                   layer_types=["full_attention", "sliding_attention", "full_attention"])
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D64": SMALL_D64, "D128": SMALL_D128, "E128": SMALL_E128}
 
 
 def get(name):
