@@ -321,6 +321,58 @@ def measure_mixed(cfg, layers, full_layers, requests, shape, check_tokens=0):
             "steps_from_graphs": replays, "steps_launched_ahead": ahead, "check": check}
 
 
+def measure_products(cfg, rows, seconds=2.0):
+    """The four matrix products of a layer at ``rows`` rows, plain (bfloat16 in and out, nothing
+    folded in): this package's kernel beside the library's (torch.matmul) at the same shapes, each
+    as a burst (best of 10 launches) and back to back for ``seconds`` (under the power cap)."""
+    import torch
+    from chibillm_b200.kernels.ops import CudaKernels
+
+    k = CudaKernels(torch.device("cuda:0"))
+    h, inter = cfg["hidden_size"], cfg["intermediate_size"]
+    d = cfg.get("head_dim") or h // cfg["num_attention_heads"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * d
+    shapes = {"qkv": (qkv, h), "o": (h, cfg["num_attention_heads"] * d), "gate_up": (2 * inter, h), "down": (h, inter)}
+
+    def rate(fn, flops):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            best = a.elapsed_time(b) if best is None else min(best, a.elapsed_time(b))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.perf_counter()
+        a.record()
+        while time.perf_counter() - t0 < seconds:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        return round(flops / best / 1e9, 1), round(flops / (a.elapsed_time(b) / n) / 1e9, 1)
+
+    out = {}
+    for name, (n, kk) in shapes.items():
+        x = torch.randn(rows, kk, device="cuda").bfloat16()
+        w = (0.02 * torch.randn(n, kk, device="cuda")).bfloat16()
+        y = torch.empty(rows, n, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * rows * n * kk
+        ours = rate(lambda: k.linear(x, w, y), flops)
+        lib = rate(lambda: torch.matmul(x, w.t(), out=y), flops)
+        out[name] = {"n": n, "k": kk, "ours_burst": ours[0], "ours_sustained": ours[1], "library_burst": lib[0],
+                     "library_sustained": lib[1]}
+    k.check_error_word()
+    return {"metric": f"TFLOP/s of a layer's four products at {rows} rows, this package's kernel and torch.matmul",
+            "unit": "TFLOP/s", "rows": rows, "products": out, "n_gpus": 1, "dtype": "bf16", "data": "synthetic"}
+
+
 def print_timeline(cfg, batch, held, prompt_tokens=0):
     """One decode step, replayed from its CUDA graph, as its CTAs saw it: for every launch when
     its first and last CTA started, when their wait for the launch before ended and when they
@@ -388,6 +440,9 @@ def main() -> int:
     ap.add_argument("--mixed-requests", type=int, default=0,
                     help="instead of the record: this many requests with prompts of 16 to 2,048 random tokens "
                          "and 256 new tokens each through the Python entry point; prints its own JSON line")
+    ap.add_argument("--products", action="store_true",
+                    help="instead of the record: the four matrix products of a layer at --prefill-tokens rows, "
+                         "this package's kernel beside torch.matmul, burst and sustained")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the record: the timeline of one decode step (use with --layers 4 or so)")
     ap.add_argument("--timeline-prompt", type=int, default=0,
@@ -421,6 +476,9 @@ def main() -> int:
     cfg["num_hidden_layers"] = layers
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
+    if args.products:
+        print(json.dumps(measure_products(cfg, args.prefill_tokens)), flush=True)
+        return 0
     if args.timeline:
         print_timeline(cfg, args.batch, args.prompt, args.timeline_prompt)
         return 0
