@@ -897,10 +897,25 @@ __device__ __forceinline__ void collect_partial_tiles(const GemmParams& p, uint3
     }
 }
 
-// x is the A operand (many rows).  One CTA per SM walks over the output tiles
-// (tile t -> row block t % tiles_m, column block t / tiles_m, so that CTAs working
-// at the same time share a block of w).  Two accumulators in TMEM: while the four
-// epilogue warps read one tile out, the MMA thread already fills the other.
+// Tile t of the many-row kernel -> (row block, column block).  The row blocks are taken in bands
+// of 16 (2,048 rows): within a band the row block runs fastest, so the CTAs that work at the same
+// time share a few blocks of w and the band's rows of x (16 x 128 x K values) stay in L2 while
+// the column blocks go by; without bands, with 64 row blocks and K = 8,192, x (134 MB) was
+// fetched from memory again for every pair of column blocks.
+constexpr int TILE_BAND = 16;
+__device__ __forceinline__ void tile_of(int t, int tiles_m, int tiles_total, int& tile_a, int& tile_b)
+{
+    const int tiles_n = tiles_total / tiles_m;
+    const int per_band = TILE_BAND * tiles_n;
+    const int band = t / per_band, within = t - band * per_band;
+    const int rows = min(TILE_BAND, tiles_m - band * TILE_BAND);
+    tile_b = within / rows;
+    tile_a = band * TILE_BAND + (within - tile_b * rows);
+}
+
+// x is the A operand (many rows).  One CTA per SM walks over the output tiles (tile_of above).
+// Two accumulators in TMEM: while the four epilogue warps read one tile out, the MMA thread
+// already fills the other.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -959,7 +974,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             WorkWalk walk(p, tiles_total);
             int t, k0, k1, kind, piece_slot;
             while (walk.next(t, k0, k1, kind, piece_slot)) {
-                const int tile_a = t % tiles_m, tile_b = t / tiles_m;
+                int tile_a, tile_b;
+                tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
                 for (int kb = k0; kb < k1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -1014,7 +1030,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         WorkWalk walk(p, tiles_total);
         int t, k0, k1, kind, piece_slot;
         for (; walk.next(t, k0, k1, kind, piece_slot); ++lt) {
-            const int tile_a = t % tiles_m, tile_b = t / tiles_m;
+            int tile_a, tile_b;
+            tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
             const uint32_t buf = lt & 1, use = lt >> 1;
             mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 13);
             tcgen05_fence_after();

@@ -316,7 +316,8 @@ def _linear_tensor_cores(k, ref, M, N, K):
     close(out, exp, torch.float32, "tensor-core linear on views", rel=2e-5)
 
 
-@pytest.mark.parametrize("M,N,K", [(1300, 4096, 1024), (2000, 5120, 5160), (300, 1000, 1000), (257, 512, 8192)])
+@pytest.mark.parametrize("M,N,K", [(1300, 4096, 1024), (2000, 5120, 5160), (300, 1000, 1000), (257, 512, 8192),
+                                   (2100, 768, 512), (4500, 1024, 264)])      # more than one band of row blocks
 def test_linear_shares_out_a_thin_last_round(k, ref, M, N, K):
     """Many rows whose tiles leave a last round that fills a quarter of the SMs or
     less: the K blocks of those tiles are dealt out to all SMs and the partial
