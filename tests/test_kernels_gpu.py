@@ -684,6 +684,41 @@ def test_product_that_finishes_its_heads_refuses_what_it_does_not_take(k):
     assert float(q.abs().max()) == 0.0
 
 
+def test_a_token_without_a_page_is_skipped_and_reported(k):
+    """A block table without a page for some positions: the slot table says -1 for
+    those tokens, the product writes their q and nothing else, every other token's
+    cache entries are written, and the error word names the append."""
+    from chibillm_b200.kernels.ops import KernelError
+    nq, nkv, d, page, K = 4, 2, 128, 16, 256
+    seq_ctx, q_lens = [100, 90], [100, 90]
+    T = sum(q_lens)
+    pages = 16
+    table, positions, seq_of_token, _, _ = _paged_setup(seq_ctx, q_lens, page, pages, seed=130)
+    table[1, 2] = -1                                  # positions 32..47 of the second sequence
+    table[1, 4] = pages + 5                           # positions 64..79: a page that is not there
+    bad = (seq_of_token == 1) & (((positions >= 32) & (positions < 48)) | ((positions >= 64) & (positions < 80)))
+    slots = torch.full((T,), 123, dtype=torch.int64, device="cuda")
+    k.cache_slots(positions, seq_of_token, None, table, nkv, page, pages, d, slots)
+    assert torch.equal(slots < 0, bad) and int(bad.sum()) == 32
+    inv_freq = torch.pow(torch.tensor(1e4), -2 * torch.arange(d // 2, dtype=torch.float32) / d).cuda()
+    cos_sin = torch.empty(T, d, dtype=torch.float32, device="cuda")
+    k.rope_table(positions, inv_freq, d, cos_sin)
+    x = rnd(T, K, dtype=torch.bfloat16, seed=131)
+    w = rnd((nq + 2 * nkv) * d, K, dtype=torch.bfloat16, seed=132, scale=0.05)
+    q = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc = torch.full((pages, nkv, page, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    vc = torch.full_like(kc, 7.0)
+    assert k.linear_heads(x, w, q, kc, vc, None, None, cos_sin, slots, nq, nkv, d, page, 1e-6, 0.0)
+    with pytest.raises(KernelError) as e:
+        k.check_error_word()
+    assert "append" in str(e.value)
+    assert not bool(torch.isnan(q.float()).any())
+    written = (kc != 7.0).any(dim=-1)                 # [pages, nkv, page]: slots that hold a new key
+    assert int(written.sum()) == (T - 32) * nkv
+    assert int((vc != 7.0).any(dim=-1).sum()) == (T - 32) * nkv
+    k.check_error_word()                              # the word was cleared: nothing new
+
+
 def test_a_pending_sum_that_was_overwritten_is_refused(k):
     """Split products take two scratch arrays in turn: the third one started
     writes over the first one's sums, and reading those then must raise."""
