@@ -762,7 +762,24 @@ class CudaKernels:
         1.250 ms a step of 12 layers, 16 ranges 1.207; of 8,192 keys: 37 ranges
         1.296, 32 ranges 1.279, 64 ranges 1.374)."""
         ctas = seqs * nkv * ((nq // nkv + 15) // 16)
-        return max(1, min(2 * self.sm_count // ctas, -(-max_ctx_len // 128), 32))
+        slots = 2 * self.sm_count
+        if ctas <= slots:
+            return max(1, min(slots // ctas, -(-max_ctx_len // 128), 32))
+        # More CTAs than slots even with one range each: a last round with a few CTAs in it
+        # costs as much as a full one (38 sequences x 8 kv heads = 304 CTAs on 296 slots: 21 %
+        # of a step more than 36 sequences).  With s ranges there are ceil(ctas * s / slots)
+        # rounds of 1 / s of the keys each, and every CTA pays for its prologue and for its
+        # share of the merge what about 550 keys take (fitted to steps of 12 layers at 38 to 64
+        # sequences of 2,048 and 8,192 keys): the s that makes rounds * (1 / s + 550 / keys) least.
+        prologue = min(1.0, 550.0 / max(max_ctx_len, 1))
+        best, least = 1, None
+        for s in range(1, 9):
+            if s > 1 and max_ctx_len // s < 256:
+                break
+            cost = -(-ctas * s // slots) * (1.0 / s + prologue)
+            if least is None or cost < least - 1e-9:
+                best, least = s, cost
+        return best
 
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:

@@ -187,6 +187,31 @@ def test_attention_against_plain(k, ref, dtype, nq, nkv, d, window, seq_ctx, q_l
     close(out, exp, dtype, "attention", rel=1e-5 if dtype == torch.float32 else 1.2e-2)
 
 
+def test_decode_attention_with_more_ctas_than_resident_slots(k, ref):
+    """So many sequences that even one key range each is more CTAs than are resident
+    at once: the policy then cuts every sequence into a few ranges (so that a last
+    round with a few CTAs does not cost a whole one), and the result must not care."""
+    nq, nkv, d, page = 16, 8, 128, 16
+    seqs = 2 * k.sm_count // nkv + 3                          # a few CTAs past the resident slots
+    seq_ctx = [1600 + 37 * (i % 7) for i in range(seqs)]
+    assert k.decode_attention_splits(seqs, nq, nkv, max(seq_ctx)) > 1
+    assert k.decode_attention_splits(seqs, nq, nkv, 600) == 1            # short sequences: a prologue more costs more
+    assert k.decode_attention_splits(2 * k.sm_count // nkv, nq, nkv, 4096) == 1
+    pages = sum((c + page - 1) // page for c in seq_ctx) + 1
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, [1] * seqs, page, pages, seed=21)
+    q = rnd(seqs, nq * d, dtype=torch.bfloat16, seed=22)
+    kc = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=23)
+    vc = rnd(pages, nkv, page, d, dtype=torch.bfloat16, seed=24)
+    out = torch.full((seqs, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    exp = torch.empty_like(out)
+    args = (table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, 1.0 / math.sqrt(d), None, 1,
+            max(seq_ctx), 1)
+    k.attention(q, kc, vc, out, *args)
+    ref.attention(q, kc, vc, exp, *args)
+    k.check_error_word()
+    close(out, exp, torch.bfloat16, "decode attention, more CTAs than slots", rel=1.2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("needle,window", [(0, None), (3, None), (255, None), (256, None), (700, None),
                                            (1000 - 40, 40), (1000 - 41, 40)])
