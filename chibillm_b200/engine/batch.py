@@ -38,9 +38,16 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        # the views handed out, by (name, type, shape): a step asks for the same few dozen views
+        # layer after layer, and building one costs as much host time as a fifth of a launch
+        self._views: Dict[Tuple[str, torch.dtype, Tuple[int, ...]], torch.Tensor] = {}
         self.generation = 0        # counts allocations: a captured graph is valid for one value
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -53,7 +60,13 @@ class Workspace:
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._buffers[key] = buf
             self.generation += 1
-        return buf[:count].view(*shape)
+            for old in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[old]           # views of the array that was replaced
+        if len(self._views) > 4096:
+            self._views.clear()                # many different step sizes: start over
+        view = buf[:count].view(*shape)
+        self._views[(name, dtype, shape)] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
