@@ -361,7 +361,7 @@ __device__ __forceinline__ float silu_mul(float g, float u)
     return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
-// One 128 x 256 tile of the q | k | v product as two heads (see GemmParams): this thread's token is
+// One 128-row tile of the q | k | v product as one or two heads (see GemmParams): this thread's token is
 // row m0 + lane, `inv` the factor that the row of x lacked.  The rotation pairs column j with column
 // j + 64 of the same row, so the head is read in pairs of 32-column pieces; the results pass
 // through the staging buffer as two lines of 64 columns, as everywhere in this epilogue.
@@ -396,15 +396,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
 // head_w: [2][128] floats in shared memory, the norm weights (+ offset) of query and key heads
 // (ones without a norm).
 __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t taddr, int m0, int lane, int tile_b,
-                                               uint8_t* stage, float inv, const float* head_w)
+                                               int heads_per_tile, uint8_t* stage, float inv, const float* head_w)
 {
     const int m = m0 + lane;
     const bool row_ok = m < p.M;
     const long long slot = (row_ok && p.h_slots) ? p.h_slots[m] : -1;
     const float* cs = p.h_cos_sin + (size_t)(row_ok ? m : 0) * 128;
 #pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
-        const int head = tile_b * 2 + hh;                         // the same for the whole warp
+    for (int hh = 0; hh < heads_per_tile; ++hh) {
+        const int head = tile_b * heads_per_tile + hh;            // the same for the whole warp
         const uint32_t t0 = taddr + hh * 128;
         const int kind = head < p.h_nq ? 0 : (head < p.h_nq + p.h_nkv ? 1 : 2);
         __nv_bfloat16* dst = nullptr;                             // this thread's row of the head
@@ -531,9 +531,9 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         inv = rsqrtf(ss / (float)p.row_n + p.row_eps);
     }
     // every branch below is taken by whole warps: tcgen05.ld is a warp-wide instruction
-    if constexpr (BN == 256) {
+    if constexpr (BN % 128 == 0) {
         if (p.h_cos_sin) {
-            epilogue_heads(p, taddr, m0, lane, tile_b, stage, inv, head_w);
+            epilogue_heads(p, taddr, m0, lane, tile_b, BN / 128, stage, inv, head_w);
             return;
         }
     }
@@ -1037,18 +1037,21 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
             const int shared_tile = t - walk.whole_tiles;
-            if (kind == 2) {
-                contribute_partial_tile<BN>(p, taddr, quarter, lane, shared_tile, piece_slot);
-            } else {
-                if (kind == 1) {
+            bool piece = false;
+            if constexpr (BN == 256) {              // only tiles of 256 columns are ever shared out
+                if (kind == 2) {
+                    contribute_partial_tile<BN>(p, taddr, quarter, lane, shared_tile, piece_slot);
+                    piece = true;
+                } else if (kind == 1) {
                     // (this is the CTA's last piece of work and its products are done: the stages are free)
                     static_assert(STAGES >= 4 && S::STAGE_BYTES >= 3 * SK_HALF_FLOATS * 4, "a stage per epilogue warp");
                     collect_partial_tiles<BN>(p, taddr, quarter, lane, shared_tile, smem + quarter * S::STAGE_BYTES,
                                               collect_bar + 3 * quarter);
                 }
+            }
+            if (!piece)
                 epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
                                         stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
-            }
             tcgen05_fence_before();
             mbar_arrive(&tmem_empty_bar[buf]);
         }
@@ -1184,6 +1187,25 @@ static int sm_count()
     return count;
 }
 
+// Tile width of the kernel for many rows: 256 columns, or 128 where that fills the rounds of
+// one CTA per SM better.  Tiles of 128 columns are about a tenth less efficient each (the rows
+// of x are fetched for half as many columns), so they are taken where they fill the SMs at least
+// that much better: 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy) or 128 of
+// 128.  Where the tiles of 256 columns leave a last round that is shared out by K blocks
+// (a quarter of the SMs or less), that is kept.
+static int many_rows_tile_width(int M, int N)
+{
+    if (N % 256 != 0)
+        return N % 128 == 0 ? 128 : 0;
+    const int sms = sm_count();
+    const long long t256 = (long long)((M + TILE_A - 1) / TILE_A) * (N / 256);
+    const long long rest = t256 % sms;
+    if (rest > 0 && rest * 4 <= sms)
+        return 256;
+    auto fill = [sms](long long tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
+    return fill(2 * t256) * 0.9 > fill(t256) ? 128 : 256;
+}
+
 // 33 to 64 rows and so few tiles that two or more splits fit the SMs once: one CTA per SM with
 // eight stages in flight instead of three CTAs with three.  Measured at 64 rows (q|k|v 6144 x 4096,
 // o 4096 x 4096, down 4096 x 12288): 12.7, 10.0 and 20.8 us against 14.2, 12.4 and 21.6, and the
@@ -1308,7 +1330,8 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         p.swap = 0;
         p.rows_a = M;
         p.rows_b = N;
-        const int bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+        const int chosen = many_rows_tile_width(M, N);       // 0: N is no multiple of 128
+        const int bn = chosen ? chosen : (N >= 256 ? 256 : (N > 64 ? 128 : 64));
         if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
             return CHIBI_ERR_UNSUPPORTED;
         const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
@@ -1316,6 +1339,8 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
             return CHIBI_ERR_UNSUPPORTED;
         if (bn == 256)
             status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream, share_last_round);
+        else if (bn == 128 && chosen == 128)
+            status = launch_gemm_persistent<128, 6>(ma, mb, p, grid.x, grid.y, stream, false);
         else if (bn == 128)
             status = launch_gemm<128, 4>(ma, mb, p, grid, stream);
         else
@@ -1412,7 +1437,8 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     p.swap = 0;
     p.rows_a = M;
     p.rows_b = N;
-    const int bn = N >= 256 ? 256 : (N > 64 || p.swiglu ? 128 : 64);
+    const int chosen = many_rows_tile_width(M, N);
+    const int bn = chosen ? chosen : (N >= 256 ? 256 : (N > 64 || p.swiglu ? 128 : 64));
     if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
         return CHIBI_ERR_UNSUPPORTED;
     const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
@@ -1420,6 +1446,8 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
         return CHIBI_ERR_UNSUPPORTED;
     if (bn == 256)
         return launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
+    if (bn == 128 && chosen == 128)
+        return launch_gemm_persistent<128, 6>(ma, mb, p, grid.x, grid.y, stream, false);
     if (bn == 128)
         return launch_gemm<128, 4>(ma, mb, p, grid, stream);
     return launch_gemm<64, 4>(ma, mb, p, grid, stream);
@@ -1446,7 +1474,13 @@ struct ChibiNormOut {
     long long ssq_floats;
 };
 
-CHIBI_API int chibi_gemm_bf16_norm_parts(int N) { return N > 0 && N % 256 == 0 ? N / 256 : 0; }
+// Sums of squares per row that a product of M rows with a norm output writes: one for each of its
+// column tiles (0: the kernel does not take the width).
+CHIBI_API int chibi_gemm_bf16_norm_parts(int M, int N)
+{
+    const int bn = M > 64 && N > 0 ? many_rows_tile_width(M, N) : 0;
+    return bn ? N / bn : 0;
+}
 
 // `heads` (may be null; then `out` is not written and may be null): the product is q | k | v of
 // head size 128 (N = (nq + 2 nkv) * 128, or nq * 128 without caches) and every head is finished in
@@ -1471,10 +1505,11 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
                                    const ChibiNormOut* norm, const ChibiHeadsOut* heads, int* error,
                                    cudaStream_t stream)
 {
-    if (M <= 64 || N <= 0 || N % 256 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
+    if (M <= 64 || N <= 0 || N % 128 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
         || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
         || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
         return CHIBI_ERR_UNSUPPORTED;
+    const int bn = many_rows_tile_width(M, N);
     if (heads) {
         const bool caches = heads->k_cache != nullptr;
         if (epilogue != 0 || norm || residual)
@@ -1536,7 +1571,7 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         p.row_n = scale->n;
     }
     if (norm) {
-        const int parts = N / 256;
+        const int parts = N / bn;
         if (!norm->w || !norm->out || !norm->ssq || norm->ssq_floats < (long long)M * parts
             || (norm->w_type != CHIBI_F32 && norm->w_type != CHIBI_BF16) || norm->out_stride % 4 != 0
             || (reinterpret_cast<uintptr_t>(norm->out) & 7))
@@ -1550,8 +1585,10 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         p.ssq_out_parts = parts;
     }
     CUtensorMap ma, mb;
-    if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, 256, &mb))
+    if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
         return CHIBI_ERR_UNSUPPORTED;
+    if (bn == 128)
+        return launch_gemm_persistent<128, 6>(ma, mb, p, (M + TILE_A - 1) / TILE_A, N / 128, stream, false);
     return launch_gemm_persistent<256, 4>(ma, mb, p, (M + TILE_A - 1) / TILE_A, N / 256, stream);
 }
 

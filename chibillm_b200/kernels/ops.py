@@ -243,7 +243,7 @@ class CudaKernels:
         many rows does not take these shapes; nothing has run then."""
         M, K = x.shape
         N = w.shape[0]
-        parts = self.lib.chibi_gemm_bf16_norm_parts(N)
+        parts = self.lib.chibi_gemm_bf16_norm_parts(M, N)
         if not (self.use_tensor_cores and self.fold_norms and M > 64 and parts > 0 and x.dtype == torch.bfloat16
                 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and residual.dtype == torch.float32
                 and residual.shape == (M, N) and out.shape == (M, N) and weight.shape == (N,)
@@ -283,7 +283,7 @@ class CudaKernels:
         t = x.tensor
         M, K = t.shape
         N = w.shape[0]
-        if not (self.use_tensor_cores and M > 64 and N % 256 == 0 and w.dtype == torch.bfloat16
+        if not (self.use_tensor_cores and M > 64 and N % 128 == 0 and w.dtype == torch.bfloat16
                 and out.dtype == torch.bfloat16 and w.shape[1] == K
                 and out.shape == (M, N // 2 if swiglu else N)):
             return False
@@ -352,7 +352,7 @@ class CudaKernels:
         T, K = x.shape
         N = w.shape[0]
         if not self.finishes_heads(T, d, d, x.dtype) or w.dtype != torch.bfloat16 or w.shape[1] != K \
-                or N != (nq + (2 * nkv if append else 0)) * d or N % 256 != 0 or q_out.dtype != torch.bfloat16:
+                or N != (nq + (2 * nkv if append else 0)) * d or q_out.dtype != torch.bfloat16:
             return False
         for t in (q_norm_w, k_norm_w):
             if t is not None and (t.dtype not in (torch.bfloat16, torch.float32) or t.numel() != d

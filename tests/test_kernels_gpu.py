@@ -342,7 +342,8 @@ def _linear_tensor_cores(k, ref, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1300, 4096, 1024), (2000, 5120, 5160), (300, 1000, 1000), (257, 512, 8192),
-                                   (2100, 768, 512), (4500, 1024, 264)])      # more than one band of row blocks
+                                   (2100, 768, 512), (4500, 1024, 264),       # more than one band of row blocks
+                                   (512, 4096, 264), (1024, 6144, 136), (400, 384, 512)])   # tiles of 128 columns
 def test_linear_shares_out_a_thin_last_round(k, ref, M, N, K):
     """Many rows whose tiles leave a last round that fills a quarter of the SMs or
     less: the K blocks of those tiles are dealt out to all SMs and the partial
@@ -376,7 +377,8 @@ def test_linear_shares_out_a_thin_last_round(k, ref, M, N, K):
     k.check_error_word()
 
 
-@pytest.mark.parametrize("M,hidden,K,wide", [(300, 512, 384, 768), (130, 256, 1024, 512), (2000, 1024, 520, 2560)])
+@pytest.mark.parametrize("M,hidden,K,wide", [(300, 512, 384, 768), (130, 256, 1024, 512), (2000, 1024, 520, 2560),
+                                             (512, 4096, 136, 1024), (1024, 2048, 264, 6144)])   # tiles of 128 columns
 @pytest.mark.parametrize("wdtype", DTYPES)
 def test_linear_folds_the_norm_that_follows(k, ref, M, hidden, K, wide, wdtype):
     """Many rows: the product that completes the residual also writes the RMSNorm of
@@ -628,6 +630,8 @@ def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
 
 
 @pytest.mark.parametrize("nq,nkv,norms,wdtype,append", [(6, 2, True, torch.bfloat16, True),
+                                                        (24, 4, True, torch.bfloat16, True),     # tiles of one head
+                                                        (5, 1, True, torch.float32, True),       # an odd number of heads
                                                         (4, 1, True, torch.float32, True),
                                                         (8, 4, False, torch.bfloat16, True),
                                                         (4, 2, True, torch.bfloat16, False)])
@@ -695,13 +699,15 @@ def test_product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append,
 
 
 def test_product_that_finishes_its_heads_refuses_what_it_does_not_take(k):
-    """Few rows, another head size or an odd number of heads: False, nothing runs."""
+    """Few rows, another head size, a width that does not match the heads: False, nothing runs."""
     d, K = 128, 256
     cos_sin = torch.zeros(300, d, device="cuda")
     x = rnd(300, K, dtype=torch.bfloat16, seed=1)
     q = torch.zeros(300, 3 * d, dtype=torch.bfloat16, device="cuda")
-    w = rnd(3 * d, K, dtype=torch.bfloat16, seed=2)
+    w = rnd(4 * d, K, dtype=torch.bfloat16, seed=2)
     assert not k.linear_heads(x, w, q, None, None, None, None, cos_sin, None, 3, 0, d, 16, 1e-6, 0.0)
+    assert not k.linear_heads(x[:64], w[:3 * d], q[:64], None, None, None, None, cos_sin[:64], None, 3, 0, d, 16,
+                              1e-6, 0.0)
     assert not k.finishes_heads(64, 128, 128, torch.bfloat16)
     assert not k.finishes_heads(300, 64, 64, torch.bfloat16)
     assert not k.finishes_heads(300, 128, 64, torch.bfloat16)
