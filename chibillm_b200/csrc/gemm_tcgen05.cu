@@ -1212,10 +1212,29 @@ static int many_rows_tile_width(int M, int N)
 // partial sums that the next kernel has to add shrink from 4, 4 and 13 splits to 3, 4 and 4.
 static bool few_deep_ctas(int M, int N)
 {
-    return M > 32 && M <= 64 && ((N + TILE_A - 1) / TILE_A) * 2 <= sm_count();
+    if (M > 64)
+        return true;       // tiles of 128 or 256 tokens: one CTA per SM is all that fits
+    return M > 32 && ((N + TILE_A - 1) / TILE_A) * 2 <= sm_count();
 }
 
-// For few rows (M <= 64) the K range is split so that the CTAs of one launch
+// Up to so many rows the weights may be the operand on the 128-row side with the rows as the
+// columns of the instruction (16 to 128 of them): every weight is fetched once by N / 128 x splits
+// CTAs that do little but stream it.  A CTA also fetches its K range of all the rows, though: with
+// 128 rows that is as many bytes again as its weights, with 256 rows twice as many, and what an
+// SM can take in bounds the product (measured: 256-row tiles lose to the kernel for many rows).
+// (Before, this ended at 64 rows, and a decode step of 65 sequences took 22 % longer than one of 64.)
+constexpr int FEW_ROWS_MAX = 128;
+CHIBI_API int chibi_gemm_few_rows_max() { return FEW_ROWS_MAX; }
+
+// 65 to FEW_ROWS_MAX rows: the weights stay the streamed operand only where the K range is split
+// at least in two (N / 128 tiles fill half the SMs or less: q|k|v, o, down of the usual shapes);
+// a wide product (gate | up) has CTAs enough without and is faster in the kernel for many rows.
+static bool few_rows_kernel(int M, int N)
+{
+    return M <= 64 || (M <= FEW_ROWS_MAX && ((N + TILE_A - 1) / TILE_A) * 2 <= sm_count());
+}
+
+// For few rows (M <= FEW_ROWS_MAX) the K range is split so that the CTAs of one launch
 // fill the SMs once, evenly: with three stages four CTAs of the 16-token variant
 // (three of the wider ones) fit an SM.  The partial sums are written and read
 // once, 8 bytes per value against 2 N K bytes of weights: they may reach 0.3 of
@@ -1227,7 +1246,7 @@ CHIBI_API int chibi_gemm_bf16_splits_capped(int M, int N, int K, int max_splits)
 {
     if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0)
         return 0;
-    if (M > 64)
+    if (!few_rows_kernel(M, N))
         return 1;
     const int tiles = (N + TILE_A - 1) / TILE_A;
     const int k_blocks = (K + TILE_K - 1) / TILE_K;
@@ -1310,8 +1329,8 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
     }
     CUtensorMap ma, mb;
     int status;
-    if (M <= 64) {
-        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (few_rows_kernel(M, N)) {
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         p.swap = 1;
         p.rows_a = N;
         p.rows_b = M;
@@ -1322,6 +1341,8 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
             status = launch_gemm<16, 3>(ma, mb, p, grid, stream);
         else if (bn == 32)
             status = launch_gemm<32, 3>(ma, mb, p, grid, stream);
+        else if (bn == 128)
+            status = launch_gemm<128, 6>(ma, mb, p, grid, stream);      // 6 x 32 KB, one CTA per SM
         else if (few_deep_ctas(M, N))
             status = launch_gemm<64, 8>(ma, mb, p, grid, stream);
         else
@@ -1478,7 +1499,7 @@ struct ChibiNormOut {
 // column tiles (0: the kernel does not take the width).
 CHIBI_API int chibi_gemm_bf16_norm_parts(int M, int N)
 {
-    const int bn = M > 64 && N > 0 ? many_rows_tile_width(M, N) : 0;
+    const int bn = M > FEW_ROWS_MAX && N > 0 ? many_rows_tile_width(M, N) : 0;
     return bn ? N / bn : 0;
 }
 
@@ -1505,7 +1526,7 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
                                    const ChibiNormOut* norm, const ChibiHeadsOut* heads, int* error,
                                    cudaStream_t stream)
 {
-    if (M <= 64 || N <= 0 || N % 128 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
+    if (M <= FEW_ROWS_MAX || N <= 0 || N % 128 != 0 || K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || w_stride % 8 != 0
         || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
         || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
         return CHIBI_ERR_UNSUPPORTED;

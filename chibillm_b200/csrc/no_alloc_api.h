@@ -24,7 +24,8 @@
 //    CHIBI_NOALLOC_SCRATCH_FLOATS; a larger product is refused with
 //    CHIBI_ERR_SCRATCH_LIMIT and nothing is launched.  chibi_error_string()
 //    turns a code into a sentence.
-//  * A product of more than 64 rows does not split K and uses no scratch at
+//  * A product that chibi_gemm_bf16_splits() does not split (more than 128 rows;
+//    65 to 128 rows of a wide one) uses no scratch at
 //    all; each of its tiles is computed whole by one CTA (the library's other
 //    entry points may share a last, sparse round of tiles among idle CTAs
 //    through scratch and counters that belong to the engine's stream; this

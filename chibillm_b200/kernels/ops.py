@@ -179,6 +179,9 @@ class CudaKernels:
         self._ssq_turn = 0
         # Many rows: the product that completes the residual also writes the following RMSNorm's
         # output, up to the factor of each row, which the next product applies to its sums.
+        # up to so many rows a product streams the weights once with the rows as the instruction's
+        # columns (and its K range split over CTAs); beyond, the kernel for many rows runs
+        self.few_rows_max = int(self.lib.chibi_gemm_few_rows_max())
         self.fold_norms = True
         self.fold_heads = True           # many rows: the q | k | v product finishes its heads itself
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
@@ -244,7 +247,7 @@ class CudaKernels:
         M, K = x.shape
         N = w.shape[0]
         parts = self.lib.chibi_gemm_bf16_norm_parts(M, N)
-        if not (self.use_tensor_cores and self.fold_norms and M > 64 and parts > 0 and x.dtype == torch.bfloat16
+        if not (self.use_tensor_cores and self.fold_norms and M > self.few_rows_max and parts > 0 and x.dtype == torch.bfloat16
                 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and residual.dtype == torch.float32
                 and residual.shape == (M, N) and out.shape == (M, N) and weight.shape == (N,)
                 and weight.is_contiguous() and weight.dtype in (torch.bfloat16, torch.float32)):
@@ -283,7 +286,7 @@ class CudaKernels:
         t = x.tensor
         M, K = t.shape
         N = w.shape[0]
-        if not (self.use_tensor_cores and M > 64 and N % 128 == 0 and w.dtype == torch.bfloat16
+        if not (self.use_tensor_cores and M > self.few_rows_max and N % 128 == 0 and w.dtype == torch.bfloat16
                 and out.dtype == torch.bfloat16 and w.shape[1] == K
                 and out.shape == (M, N // 2 if swiglu else N)):
             return False
@@ -304,7 +307,7 @@ class CudaKernels:
     # ---- the q | k | v product of many rows that finishes its heads itself
     def finishes_heads(self, rows: int, d: int, rotary_dim: int, dtype: torch.dtype) -> bool:
         """Whether ``linear_heads`` takes a step of so many rows with this head size."""
-        return bool(self.use_tensor_cores and self.fold_heads and rows > 64 and d == 128 and rotary_dim == d
+        return bool(self.use_tensor_cores and self.fold_heads and rows > self.few_rows_max and d == 128 and rotary_dim == d
                     and dtype == torch.bfloat16)
 
     def rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
@@ -534,8 +537,8 @@ class CudaKernels:
             raise KernelError("linear_swiglu: shapes or element types")
         if not self.use_tensor_cores:
             return False
-        if M <= 64:
-            pending = self.linear_partial(x, w_interleaved)
+        pending = self.linear_partial(x, w_interleaved) if M <= self.few_rows_max else None
+        if pending is not None or M <= 64:
             if pending is None:
                 # a shape whose K range is not split: the whole product, then the same kernel
                 # that otherwise adds up the splits (here: one) applies SwiGLU
@@ -636,7 +639,7 @@ class CudaKernels:
             pending = self.linear_partial(x, w)
             if pending is not None:
                 return pending
-            if self.use_tensor_cores and self.fold_norms and x.shape[0] > 64 and x.dtype == torch.bfloat16 \
+            if self.use_tensor_cores and self.fold_norms and x.shape[0] > self.few_rows_max and x.dtype == torch.bfloat16 \
                     and w.dtype == torch.bfloat16 and residual.dtype == torch.float32:
                 return DeferredProduct(self, x, w)
         _need_cuda(x, w, out, residual)

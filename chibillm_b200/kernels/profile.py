@@ -24,7 +24,7 @@ from typing import Callable, Dict, List, Optional, Tuple
 import torch
 
 # entry points that ask a question or set something and launch nothing
-_NOT_LAUNCHES = ("chibi_gemm_bf16_splits", "chibi_gemm_bf16_splits_capped", "chibi_gemm_bf16_norm_parts",
+_NOT_LAUNCHES = ("chibi_gemm_bf16_splits", "chibi_gemm_bf16_splits_capped", "chibi_gemm_bf16_norm_parts", "chibi_gemm_few_rows_max",
                  "chibi_gemm_set_stream_scratch", "chibi_gemm_reset_stream_counters",
                  "chibi_attention_mma_head_dim", "chibi_attention_tc_head_dim")
 
@@ -35,12 +35,13 @@ _PRODUCT_SIZES = {"chibi_gemm_bf16": (5, 6, 7), "chibi_gemm_bf16_rows": (5, 6, 7
 
 def launch_name(function: str, args: tuple) -> str:
     """The name a launch is filed under: the entry point and, for matrix
-    products, the weight's shape and whether few (<= 64) or many rows ran."""
+    products, the weight's shape and whether few (<= 64), up to 128 (where the narrow
+    products still run the few-row kernel) or many rows ran."""
     name = function[6:] if function.startswith("chibi_") else function
     where = _PRODUCT_SIZES.get(function)
     if where is not None:
         m, n, k = (int(args[i]) for i in where)
-        name += f" {n}x{k} {'few rows' if m <= 64 else 'many rows'}"
+        name += f" {n}x{k} {'few rows' if m <= 64 else ('up to 128 rows' if m <= 128 else 'many rows')}"
     return name
 
 

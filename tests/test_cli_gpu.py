@@ -60,12 +60,12 @@ def test_profile_mode_prints_a_table(tmp_path):
     cfg_path = tmp_path / "config.json"
     cfg_path.write_text(json.dumps(tiny_configs.get("D128")))
     done = run_module(["--random", str(cfg_path), "--context-length", "256", "--max-tokens", "5", "--ignore-eos",
-                       "--prompt-ids", ",".join(str(i) for i in range(1, 81)), "--profile-passes"])
+                       "--prompt-ids", ",".join(str(i) for i in range(1, 151)), "--profile-passes"])
     assert done.returncode == 0, done.stderr
     assert len(done.stdout.split()) == 5
     table = [l for l in done.stderr.splitlines() if l.startswith("[cuda-profile]")]
     passes = [l for l in done.stderr.splitlines() if l.startswith("[cuda-pass]")]
-    assert len(passes) == 5 and "tokens=80" in passes[0] and "tokens=1 " in passes[1]
+    assert len(passes) == 5 and "tokens=150" in passes[0] and "tokens=1 " in passes[1]
     assert table[-1].split()[1:4] == ["all", "instrumented", "work"]
     names = " ".join(table)
     for expected in ("gemm_bf16", "few rows", "many rows", "embed", "sample", "attention"):
@@ -75,5 +75,5 @@ def test_profile_mode_prints_a_table(tmp_path):
 
     # the same tokens without the profiling mode
     plain = run_module(["--random", str(cfg_path), "--context-length", "256", "--max-tokens", "5", "--ignore-eos",
-                        "--prompt-ids", ",".join(str(i) for i in range(1, 81))])
+                        "--prompt-ids", ",".join(str(i) for i in range(1, 151))])
     assert plain.returncode == 0 and plain.stdout.split() == done.stdout.split()

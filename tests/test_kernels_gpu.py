@@ -442,7 +442,7 @@ def test_linear_falls_back_when_unaligned(k, ref):
     close(out, exp, torch.float32, "fallback linear", rel=2e-5)
 
 
-@pytest.mark.parametrize("M", [1, 8, 33, 64])
+@pytest.mark.parametrize("M", [1, 8, 33, 64, 100, 128])
 def test_split_product_with_fused_consumers(k, ref, M):
     """A product whose K range is split over CTAs, finished by the kernels that
     add the partial sums together with what follows: residual + RMSNorm, SwiGLU,

@@ -103,6 +103,32 @@ def test_cutting_and_batching(folders, expected, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case,live", [("E128", 70), ("D128", 100), ("B", 130)])
+def test_many_sequences_decoded_together(folders, case, live, dtype):
+    """More than 64 sequences in one decode step (the products then run with 65 to
+    128 rows, or as many-row products beyond): all prompts in one step, then six
+    steps in which every sequence brings one token, against the plain implementation."""
+    cfg, page_size, _ = CASES[case]
+    vocab = tiny_configs.get(cfg)["vocab_size"]
+    lengths = [9 + (7 * i) % 23 for i in range(live)]
+    reqs = helpers.random_requests(vocab, lengths, seed=600)
+    ref = helpers.plain_logits(folders[case], reqs)
+    runner = make_runner(folders[case], dtype, page_size, pool_tokens=sum(helpers.round64(n) for n in lengths),
+                         max_requests=live)
+    tail = 6
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": ids[:-tail], "want": list(range(len(ids) - tail))}
+                                     for rid, ids in reqs.items()], "end": []}]
+    for j in range(tail):
+        steps.append({"step": 1 + j, "entries": [{"id": rid, "tokens": [ids[len(ids) - tail + j]], "want": [0]}
+                                                 for rid, ids in reqs.items()],
+                      "end": list(reqs) if j == tail - 1 else []})
+    got = helpers.run_trace(runner, steps)
+    helpers.assert_logits_close(got, ref, helpers.TOL[dtype], f"{case} {dtype} {live} sequences together")
+    runner.cache.check_invariants()
+    assert not runner.cache.requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_and_long_decoding(folders, expected, dtype):
     """Position 0 alone, then every further token one by one up to the model's
     limit of positions."""

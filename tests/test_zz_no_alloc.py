@@ -81,11 +81,11 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(lib):
 
 def test_the_call_allocates_nothing_and_forgets_the_call_before(lib):
     """Free device memory is the same before and after warmed calls, and a call
-    that does not split K (more than 64 rows) right after one that does gives
+    that does not split K (more than 128 rows) right after one that does gives
     the result of a call on its own: nothing of the array's old contents is read."""
     stream = torch.cuda.current_stream().cuda_stream
     error = torch.zeros(1, dtype=torch.int32, device="cuda")
-    shapes = [(8, 4096, 4096), (5, 1024, 8192), (96, 512, 1024)]
+    shapes = [(8, 4096, 4096), (5, 1024, 8192), (160, 512, 1024)]
     assert lib.chibi_gemm_bf16_splits(*shapes[0]) != lib.chibi_gemm_bf16_splits(*shapes[1]) > 1
     assert lib.chibi_gemm_bf16_splits(*shapes[2]) == 1
     cases = []
