@@ -1193,14 +1193,17 @@ static int sm_count()
 // that much better: 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy) or 128 of
 // 128.  Where the tiles of 256 columns leave a last round that is shared out by K blocks
 // (a quarter of the SMs or less), that is kept.
-static int many_rows_tile_width(int M, int N)
+static int many_rows_tile_width(int M, int N, int K)
 {
     if (N % 256 != 0)
         return N % 128 == 0 ? 128 : 0;
     const int sms = sm_count();
     const long long t256 = (long long)((M + TILE_A - 1) / TILE_A) * (N / 256);
     const long long rest = t256 % sms;
-    if (rest > 0 && rest * 4 <= sms)
+    // (a lone round of so few tiles is shared out only where K is long: with 64 K blocks, whole
+    // tiles of 128 columns are faster: o of Qwen3-8B at 160 / 192 / 256 rows 240 -> 372, 286 -> 445,
+    // 375 -> 590 TFLOP/s; down, 192 K blocks, 373 -> 361, 435 -> 425, 564 -> 558)
+    if (rest > 0 && rest * 4 <= sms && (t256 > sms || (K + TILE_K - 1) / TILE_K >= 128))
         return 256;
     auto fill = [sms](long long tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
     return fill(2 * t256) * 0.9 > fill(t256) ? 128 : 256;
@@ -1351,7 +1354,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         p.swap = 0;
         p.rows_a = M;
         p.rows_b = N;
-        const int chosen = many_rows_tile_width(M, N);       // 0: N is no multiple of 128
+        const int chosen = many_rows_tile_width(M, N, K);    // 0: N is no multiple of 128
         const int bn = chosen ? chosen : (N >= 256 ? 256 : (N > 64 ? 128 : 64));
         if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
             return CHIBI_ERR_UNSUPPORTED;
@@ -1458,7 +1461,7 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     p.swap = 0;
     p.rows_a = M;
     p.rows_b = N;
-    const int chosen = many_rows_tile_width(M, N);
+    const int chosen = many_rows_tile_width(M, N, K);
     const int bn = chosen ? chosen : (N >= 256 ? 256 : (N > 64 || p.swiglu ? 128 : 64));
     if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
         return CHIBI_ERR_UNSUPPORTED;
@@ -1497,9 +1500,9 @@ struct ChibiNormOut {
 
 // Sums of squares per row that a product of M rows with a norm output writes: one for each of its
 // column tiles (0: the kernel does not take the width).
-CHIBI_API int chibi_gemm_bf16_norm_parts(int M, int N)
+CHIBI_API int chibi_gemm_bf16_norm_parts(int M, int N, int K)
 {
-    const int bn = M > FEW_ROWS_MAX && N > 0 ? many_rows_tile_width(M, N) : 0;
+    const int bn = M > FEW_ROWS_MAX && N > 0 ? many_rows_tile_width(M, N, K) : 0;
     return bn ? N / bn : 0;
 }
 
@@ -1530,7 +1533,7 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
         || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
         return CHIBI_ERR_UNSUPPORTED;
-    const int bn = many_rows_tile_width(M, N);
+    const int bn = many_rows_tile_width(M, N, K);
     if (heads) {
         const bool caches = heads->k_cache != nullptr;
         if (epilogue != 0 || norm || residual)

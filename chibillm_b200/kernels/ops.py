@@ -246,7 +246,7 @@ class CudaKernels:
         many rows does not take these shapes; nothing has run then."""
         M, K = x.shape
         N = w.shape[0]
-        parts = self.lib.chibi_gemm_bf16_norm_parts(M, N)
+        parts = self.lib.chibi_gemm_bf16_norm_parts(M, N, K)
         if not (self.use_tensor_cores and self.fold_norms and M > self.few_rows_max and parts > 0 and x.dtype == torch.bfloat16
                 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and residual.dtype == torch.float32
                 and residual.shape == (M, N) and out.shape == (M, N) and weight.shape == (N,)
