@@ -1480,8 +1480,8 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
 // Many rows with an RMSNorm folded into the products around it (see GemmParams).  `scale`
 // (may be null) describes the factor that x lacks; `norm` (may be null) asks for the norm output of
 // the completed residual.  epilogue 1: SwiGLU as in chibi_gemm_bf16_fused.  Only the kernel for more
-// than 64 rows with whole 256-column tiles does this: CHIBI_ERR_UNSUPPORTED otherwise, and the caller
-// applies the norm or the factor with kernels of their own.
+// than FEW_ROWS_MAX rows with whole tiles of 128 or 256 columns does this: CHIBI_ERR_UNSUPPORTED
+// otherwise, and the caller applies the norm or the factor with kernels of their own.
 struct ChibiRowScale {
     const float* ssq;      // [M][parts] sums of squares
     int parts;
