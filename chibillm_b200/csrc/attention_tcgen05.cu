@@ -64,6 +64,13 @@ struct AttnTcParams {
     int window;
     int skip_single;
     int* error;
+    // The kernel with one query tile per CTA may cut the keys of a row tile into kv_splits ranges,
+    // one CTA each (few query rows over a long context would leave most SMs idle otherwise): every
+    // CTA then leaves its unnormalised output, maximum and sum per row, and
+    // attn_prefill_merge_kernel puts the ranges together.
+    int kv_splits;                 // 1: none
+    float* part_o;                 // [tokens][nq][kv_splits][D]
+    float* part_ml;                // [tokens][nq][kv_splits][2]
 };
 
 // Byte offset of element (row, col) of a [rows][64] bf16 tile laid out with the
@@ -119,7 +126,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     // CTAs start in the order of their linear index: the row tiles with the most keys come first,
     // for all kv heads, so that the long ones do not start last
-    const int seq = blockIdx.z;
+    const int seq = blockIdx.z / p.kv_splits, split = blockIdx.z - seq * p.kv_splits;
     const int linear = blockIdx.x + gridDim.x * blockIdx.y;
     const int kv_head = linear % gridDim.y, tile_rank = linear / gridDim.y;
     const int t0 = p.q_start[seq];
@@ -137,7 +144,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
     key_begin = key_begin / p.page_size * p.page_size;           // tiles start on a page
     const int key_end = max_pos + 1;
-    const int n_tiles = (key_end - key_begin + KEYS - 1) / KEYS;
+    int n_tiles = (key_end - key_begin + KEYS - 1) / KEYS;
+    if (p.kv_splits > 1) {
+        // this CTA's range of the row tile's key tiles (it may be empty)
+        const int per = (n_tiles + p.kv_splits - 1) / p.kv_splits;
+        const int lo = split * per;
+        n_tiles = max(0, min(per, n_tiles - lo));
+        key_begin += lo * KEYS;
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
@@ -385,6 +399,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, p.error, 30);
         tcgen05_fence_after();
         const int head = kv_head * p.group + (r - tok * p.group);
+        if (p.kv_splits > 1) {
+            // one of several key ranges: the row as it stands, with its maximum and sum
+            const size_t slot = ((size_t)(t0 + tok) * p.nq + head) * p.kv_splits + split;
+            float* dst = p.part_o + slot * D;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t ov[32];
+                if (n_tiles > 0) {
+                    tmem_load_32x32(lane_addr + TMEM_O + c0, ov);
+                    tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        ov[i] = 0;
+                }
+                if (live) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        reinterpret_cast<uint4*>(dst + c0)[c] = make_uint4(ov[4 * c], ov[4 * c + 1], ov[4 * c + 2], ov[4 * c + 3]);
+                }
+            }
+            if (live) {
+                p.part_ml[slot * 2] = m;
+                p.part_ml[slot * 2 + 1] = l;
+            }
+        } else {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst_row = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
 #pragma unroll
@@ -404,6 +444,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
             }
         }
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -411,6 +452,47 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+}
+
+// Puts the key ranges of attn_prefill_tc_kernel together: one block of D threads for each
+// (head, token of a sequence); ranges in order, eight at a time.
+__global__ void attn_prefill_merge_kernel(const AttnTcParams p)
+{
+    pdl_trigger();
+    const int seq = blockIdx.z, head = blockIdx.x, c = threadIdx.x;
+    const int t0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - t0;
+    if ((int)blockIdx.y >= q_len || (q_len == 1 && p.skip_single))
+        return;
+    pdl_wait();
+    const size_t slot0 = ((size_t)(t0 + blockIdx.y) * p.nq + head) * p.kv_splits;
+    float m_run = -INFINITY, acc = 0.f, lsum = 0.f;
+    for (int s0 = 0; s0 < p.kv_splits; s0 += 8) {
+        float mv[8], lv[8], ov[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool in = s0 + u < p.kv_splits;
+            mv[u] = in ? p.part_ml[(slot0 + s0 + u) * 2] : -INFINITY;
+            lv[u] = in ? p.part_ml[(slot0 + s0 + u) * 2 + 1] : 0.f;
+            ov[u] = in ? p.part_o[(slot0 + s0 + u) * D + c] : 0.f;
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            m_new = fmaxf(m_new, mv[u]);
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = exp2f(m_run - base);       // 0 while nothing has been seen
+        acc *= keep;
+        lsum *= keep;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float f = exp2f(mv[u] - base);
+            acc += ov[u] * f;
+            lsum += lv[u] * f;
+        }
+        m_run = m_new;
+    }
+    p.out[((size_t)(t0 + blockIdx.y) * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
 }
 
 
@@ -801,8 +883,9 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
                                          const int* block_table, int table_stride, const int* seq_rows,
                                          const int* q_start, const int* ctx_len, int seqs, int nq, int nkv,
                                          int page_size, int num_pages, float scale, int window,
-                                         int skip_single, int max_q_len, int variant, int* error,
-                                         cudaStream_t stream)
+                                         int skip_single, int max_q_len, int variant, int kv_splits,
+                                         float* scratch, long long scratch_floats, long long tokens,
+                                         int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
@@ -830,6 +913,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     p.window = window;
     p.skip_single = skip_single;
     p.error = error;
+    p.kv_splits = 1;
     CUtensorMap mk, mv;
     if (!tensor_map_2d(k_cache, p.cache_rows, D, D, page_size, &mk)
         || !tensor_map_2d(v_cache, p.cache_rows, D, D, page_size, &mv))
@@ -862,7 +946,21 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
         launch(attn_prefill_tc2_kernel, grid2, dim3(ATC2_THREADS), ATC2_SMEM, stream, mk, mv, p);
         return launch_status();
     }
-    const dim3 grid((unsigned)((rows + ROWS - 1) / ROWS), nkv, seqs);
+    if (kv_splits > 1) {
+        // key ranges: only this kernel (one query tile per CTA) has them
+        if (kv_splits > 64 || !scratch || tokens <= 0 || scratch_floats < tokens * nq * kv_splits * (long long)(D + 2)
+            || (long long)seqs * kv_splits > 65535)
+            return CHIBI_ERR_ARGUMENT;
+        p.kv_splits = kv_splits;
+        p.part_o = scratch;
+        p.part_ml = scratch + (size_t)tokens * nq * kv_splits * D;
+    }
+    const dim3 grid((unsigned)((rows + ROWS - 1) / ROWS), nkv, seqs * p.kv_splits);
     launch(attn_prefill_tc_kernel, grid, dim3(ATC_THREADS), ATC_SMEM, stream, mk, mv, p);
-    return launch_status();
+    int st = launch_status();
+    if (st == CHIBI_OK && p.kv_splits > 1) {
+        launch(attn_prefill_merge_kernel, dim3(nq, max_q_len, seqs), dim3(D), 0, stream, p);
+        st = launch_status();
+    }
+    return st;
 }

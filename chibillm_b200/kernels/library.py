@@ -48,7 +48,7 @@ _SIGNATURES = {
     },
     "chibi_attention_tc": {
         "chibi_attention_tc_head_dim": [],
-        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P],
+        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, L, P, P],
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],

@@ -784,6 +784,16 @@ class CudaKernels:
                 best, least = s, cost
         return best
 
+    def prompt_attention_key_ranges(self, seqs: int, nq: int, nkv: int, max_q_len: int, max_ctx_len: int) -> int:
+        """Key ranges per row tile of the tcgen05 prompt attention: 1 unless the step
+        has so few query rows that the CTAs (a tile of 128 rows for each kv head and
+        sequence) fill half the SMs or less while the context is long; then as many
+        ranges as fill the SMs, of at least 512 keys each, at most eight."""
+        ctas = -(-max_q_len * (nq // nkv) // 128) * nkv * seqs
+        if ctas * 2 > self.sm_count or max_ctx_len < 1024:
+            return 1
+        return max(1, min(8, self.sm_count // ctas, max_ctx_len // 512))
+
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:
         lib = self._attention_libs.get(d)
@@ -803,11 +813,14 @@ class CudaKernels:
                 if tc.chibi_attention_tc_head_dim() != d:
                     raise KernelError(f"the tcgen05 attention library for head size {d} was built for another size")
                 tc = self._attention_tc_libs[d] = self._profiled(tc)
+            kv_splits = self.prompt_attention_key_ranges(seqs, nq, nkv, max_q_len, max_ctx_len)
+            part = self._scratch(q.shape[0] * nq * kv_splits * (d + 2)) if kv_splits > 1 else None
             status = tc.chibi_attention_prefill_tc(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
                 float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len),
-                int(self.tcgen05_attention_variant), _ptr(self.error), self._stream())
+                int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
+                part.numel() if part is not None else 0, q.shape[0], _ptr(self.error), self._stream())
             if status == 0:
                 self.launches += 1
                 mode &= 1

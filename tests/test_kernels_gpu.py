@@ -534,6 +534,37 @@ def test_linear_swiglu(k, ref, M, inter, K):
     assert k.interleave_gate_up(gate[:40], up[:40]) is None
 
 
+@pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, None), (4, 1, 64, None), (8, 2, 128, 1500)])
+@pytest.mark.parametrize("seq_ctx,q_lens", [([3000], [130]), ([2600, 1100], [40, 3])])
+def test_prompt_attention_with_key_ranges(k, ref, nq, nkv, d, window, seq_ctx, q_lens):
+    """Few query rows over a long context: the tcgen05 kernel cuts the keys of a row
+    tile into ranges, one CTA each, and a second kernel puts the ranges together
+    (ranges may be empty for the tile with fewer keys); same result as the plain one."""
+    page = 16
+    assert k.prompt_attention_key_ranges(len(seq_ctx), nq, nkv, max(q_lens), max(seq_ctx)) > 1
+    assert k.prompt_attention_key_ranges(len(seq_ctx), nq, nkv, max(q_lens), 700) == 1
+    assert k.prompt_attention_key_ranges(40, nq, nkv, 512, 8192) == 1
+    pages = sum((c + page - 1) // page for c in seq_ctx) + 3
+    table, positions, seq_of_token, q_start, ctx_len = _paged_setup(seq_ctx, q_lens, page, pages, seed=70)
+    T = sum(q_lens)
+    q = rnd(T, nq * d, dtype=torch.bfloat16, seed=71)
+    kc = torch.full((pages, nkv, page, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    vc = torch.full((pages, nkv, page, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for s, c in enumerate(seq_ctx):
+        idx = torch.arange(c, device="cuda")
+        pg = table[s, idx // page].long()
+        kc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=torch.bfloat16, seed=2100 + s)
+        vc[pg, :, idx % page, :] = rnd(c, nkv, d, dtype=torch.bfloat16, seed=6100 + s)
+    args = (table, q_start, ctx_len, seq_of_token, positions, nq, nkv, d, page, 1.0 / math.sqrt(d), window,
+            max(q_lens), max(seq_ctx), min(q_lens))
+    exp = torch.empty(T, nq * d, dtype=torch.bfloat16, device="cuda")
+    ref.attention(q, kc, vc, exp, *args)
+    out = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k.attention(q, kc, vc, out, *args)
+    k.check_error_word()
+    close(out, exp, torch.bfloat16, "prompt attention with key ranges", rel=1.2e-2)
+
+
 @pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, None), (5, 1, 128, 200), (4, 4, 64, None), (6, 2, 64, 130)])
 @pytest.mark.parametrize("page", [8, 16, 64])
 def test_attention_tcgen05_prompts(k, ref, nq, nkv, d, window, page):
