@@ -822,7 +822,8 @@ class CudaKernels:
                 int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
                 part.numel() if part is not None else 0, q.shape[0], _ptr(self.error), self._stream())
             if status == 0:
-                self.launches += 1
+                # (key ranges belong to the kernel with one query tile per CTA, and bring a merge kernel)
+                self.launches += 2 if kv_splits > 1 and self.tcgen05_attention_variant != 2 else 1
                 mode &= 1
                 if mode == 0:
                     return
