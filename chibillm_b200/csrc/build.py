@@ -172,14 +172,14 @@ def find_cxx() -> str:
                      "of chibillm_b200 (cache manager, scheduler) cannot be compiled")
 
 
-def runtime_library(verbose: bool = True) -> str:
-    """The cache manager, the scheduler and the batch packing: plain C++, no CUDA."""
+def _host_library(stem: str, sources: Sequence[str], what: str, verbose: bool) -> str:
+    """A library of plain C++ (no CUDA), built with the host compiler when its current version is absent."""
     h = hashlib.sha256()
-    for name in HOST_SOURCES:
+    for name in sources:
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(f.read())
     h.update(" ".join(HOST_FLAGS).encode())
-    target = os.path.join(library_dir(), f"libchibi_runtime_{h.hexdigest()[:12]}.so")
+    target = os.path.join(library_dir(), f"lib{stem}_{h.hexdigest()[:12]}.so")
     if os.path.isfile(target):
         return target
     cxx = find_cxx()
@@ -187,22 +187,33 @@ def runtime_library(verbose: bool = True) -> str:
     fd, tmp = tempfile.mkstemp(suffix=".so", dir=os.path.dirname(target))
     os.close(fd)
     try:
-        _run([cxx] + HOST_FLAGS + [os.path.join(CSRC, s) for s in HOST_SOURCES] + ["-o", tmp])
+        _run([cxx] + HOST_FLAGS + [os.path.join(CSRC, s) for s in sources] + ["-o", tmp])
         os.chmod(tmp, 0o755)
         os.replace(tmp, target)
     finally:
         if os.path.exists(tmp):
             os.remove(tmp)
     if verbose:
-        _say(f"{os.path.basename(target)} (host runtime, {cxx}) ready in {time.time() - started:.1f} s")
+        _say(f"{os.path.basename(target)} ({what}, {cxx}) ready in {time.time() - started:.1f} s")
     for f in os.listdir(os.path.dirname(target)):
         full = os.path.join(os.path.dirname(target), f)
-        if f.startswith("libchibi_runtime_") and f.endswith(".so") and full != target:
+        if f.startswith(f"lib{stem}_") and f.endswith(".so") and full != target:
             try:
                 os.remove(full)
             except OSError:
                 pass
     return target
+
+
+def runtime_library(verbose: bool = True) -> str:
+    """The cache manager, the scheduler and the batch packing: plain C++, no CUDA."""
+    return _host_library("chibi_runtime", HOST_SOURCES, "host runtime", verbose)
+
+
+def reference_library(verbose: bool = True) -> str:
+    """Plain C++ restatements of the device operations (reference_ops.cc): what the tests compare
+    every kernel with.  Nothing on the path of generation loads it."""
+    return _host_library("chibi_reference", ["reference_ops.cc"], "plain C++ reference of the kernels", verbose)
 
 
 def attention_library(head_dim: int, verbose: bool = True) -> str:
@@ -214,7 +225,7 @@ def attention_tc_library(head_dim: int, verbose: bool = True) -> str:
 
 
 def build_all(verbose: bool = True) -> List[str]:
-    out = [runtime_library(verbose), ensure_library("chibi_kernels", verbose=verbose)]
+    out = [runtime_library(verbose), reference_library(verbose), ensure_library("chibi_kernels", verbose=verbose)]
     with ThreadPoolExecutor(max_workers=4) as pool:
         out += list(pool.map(lambda d: attention_library(d, verbose), PREBUILT_HEAD_DIMS))
         out += list(pool.map(lambda d: attention_tc_library(d, verbose), TCGEN05_ATTENTION_HEAD_DIMS))
