@@ -102,10 +102,12 @@ class CppReferenceKernels:
         qo = torch.zeros(T, nq * d, dtype=torch.float32)
         kc, vc = _host_f32(k_cache), _host_f32(v_cache)
         bt = _host_i32(block_table)
+        # every host copy keeps a name until the call returns: a temporary would be freed under the pointer
+        qw, kw, freq = _host_f32(q_norm_w), _host_f32(k_norm_w), _host_f32(inv_freq)
+        pos, seq = _host_i32(positions), _host_i32(seq_of_token)
         bad = self.lib.chibi_ref_qk_norm_rope_append(
-            _fp(qf), T, _fp(qo), _fp(kc), _fp(vc), _fp(_host_f32(q_norm_w)), _fp(_host_f32(k_norm_w)),
-            _fp(_host_f32(inv_freq)), rotary_dim, eps, norm_offset, _ip(_host_i32(positions)),
-            _ip(_host_i32(seq_of_token)), _ip(bt), 0 if bt is None else bt.shape[1], nq, nkv, d, page_size,
+            _fp(qf), T, _fp(qo), _fp(kc), _fp(vc), _fp(qw), _fp(kw), _fp(freq), rotary_dim, eps, norm_offset,
+            _ip(pos), _ip(seq), _ip(bt), 0 if bt is None else bt.shape[1], nq, nkv, d, page_size,
             0 if kc is None else kc.shape[0])
         assert bad == 0, f"{bad} tokens without a page"
         q_out.copy_(qo.to(q_out.dtype))
@@ -121,15 +123,15 @@ class CppReferenceKernels:
         qf, kc, vc = _host_f32(q), _host_f32(k_cache), _host_f32(v_cache)
         bt = _host_i32(block_table)
         res = torch.zeros(T, nq * d, dtype=torch.float32)
-        bad = self.lib.chibi_ref_attention(_fp(qf), _fp(kc), _fp(vc), _fp(res), _ip(bt), bt.shape[1],
-                                           _ip(_host_i32(positions)), _ip(_host_i32(seq_of_token)), T, nq, nkv, d,
-                                           page_size, kc.shape[0], scale, int(window or 0))
+        pos, seq = _host_i32(positions), _host_i32(seq_of_token)
+        bad = self.lib.chibi_ref_attention(_fp(qf), _fp(kc), _fp(vc), _fp(res), _ip(bt), bt.shape[1], _ip(pos),
+                                           _ip(seq), T, nq, nkv, d, page_size, kc.shape[0], scale, int(window or 0))
         assert bad == 0, f"{bad} rows read outside the pool"
         out.copy_(res.to(out.dtype))
 
     def sample(self, logits, temperature, uniform, out):
         lf = _host_f32(logits)
         res = torch.empty(lf.shape[0], dtype=torch.int32)
-        self.lib.chibi_ref_sample(_fp(lf), lf.shape[1], lf.shape[0], lf.shape[1], _fp(_host_f32(temperature)),
-                                  _fp(_host_f32(uniform)), _ip(res))
+        temp, uni = _host_f32(temperature), _host_f32(uniform)
+        self.lib.chibi_ref_sample(_fp(lf), lf.shape[1], lf.shape[0], lf.shape[1], _fp(temp), _fp(uni), _ip(res))
         out.copy_(res.to(out.dtype))
