@@ -1064,6 +1064,150 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 }
 
+// The same walk over output tiles by pairs of CTAs (a cluster of two, on the SMs of one TPC): a
+// tile is 256 rows x 256 columns, computed by tcgen05.mma of 256 rows that the even CTA issues for
+// both.  Each CTA fetches its 128 rows of x and its 128 of the tile's 256 rows of w (32 KB per K
+// block for as many sums as a CTA on its own gets from 48 KB), holds its 128 rows of the
+// accumulator in its own TMEM and runs the epilogue of those rows.  The barriers that count a
+// stage's bytes and the accumulators' release are the even CTA's; its commits arrive in both CTAs.
+// A wait that runs out ends the role's loop; every thread of both CTAs reaches the cluster
+// barrier at the end.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGE_BYTES = 2 * TILE_A * TILE_K * 2;
+template <int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p, int tiles_m, int tiles_total)
+{
+    pdl_trigger();
+    constexpr int BN = PAIR_BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * PAIR_STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;     // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;     // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    uint8_t* stage_base = reinterpret_cast<uint8_t*>(tmem_slot + 4);      // 16-byte aligned
+    float* head_w = reinterpret_cast<float*>(stage_base + 4 * EPILOGUE_STAGE_BYTES);   // [2][128]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    if (p.h_cos_sin && threadIdx.x < 128) {
+        head_w[threadIdx.x] = p.h_q_norm_w ? head_weight(p.h_q_norm_w, p.h_w_type, threadIdx.x, p.h_offset) : 1.f;
+        head_w[128 + threadIdx.x] = p.h_k_norm_w ? head_weight(p.h_k_norm_w, p.h_w_type, threadIdx.x, p.h_offset) : 1.f;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);               // the even CTA's arrival with both CTAs' bytes
+            mbar_init(&empty_bar[s], 1);              // a commit, in both CTAs
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full_bar[b], 1);          // a commit, in both CTAs
+            mbar_init(&tmem_empty_bar[b], 256);       // every epilogue thread of both CTAs, at the even CTA
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    cluster_sync();                                   // both CTAs' barriers exist before either is signalled
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            tma_prefetch_descriptor(&map_a);
+            tma_prefetch_descriptor(&map_b);
+            uint32_t it = 0;
+            bool waited = false, ok = true;
+            for (int t = pair; t < tiles_total && ok; t += pairs) {
+                int tile_a, tile_b;
+                tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
+                for (int kb = 0; kb < p.k_blocks_total; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 21)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = smem + s * PAIR_STAGE_BYTES;
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);
+                    const uint32_t bar = peer_smem_addr(smem_addr(&full_bar[s]), 0);
+                    tma_load_2d_pair(a_dst + TILE_A * TILE_K * 2, &map_b, bar, kb * TILE_K,
+                                     tile_b * BN + (int)rank * TILE_A);
+                    if (!waited) {
+                        pdl_wait();
+                        waited = true;
+                    }
+                    tma_load_2d_pair(a_dst, &map_a, bar, kb * TILE_K, (tile_a * 2 + (int)rank) * TILE_A);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = make_idesc_bf16_f32(2 * TILE_A, BN);
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int t = pair; t < tiles_total && ok; t += pairs, ++lt) {
+                const uint32_t buf = lt & 1, use = lt >> 1;
+                if (use > 0 && !mbar_wait(&tmem_empty_bar[buf], (use - 1) & 1, p.error, 24))
+                    break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.k_blocks_total; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (!mbar_wait(&full_bar[s], round & 1, p.error, 22)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_addr(smem + s * PAIR_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TILE_A * TILE_K * 2;
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                        const uint64_t a_desc = make_kmajor_sw128_desc(a_addr + k * UMMA_K * 2);
+                        const uint64_t b_desc = make_kmajor_sw128_desc(b_addr + k * UMMA_K * 2);
+                        tcgen05_mma_bf16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit_pair(&empty_bar[s], 3);
+                }
+                if (ok)
+                    tcgen05_commit_pair(&tmem_full_bar[buf], 3);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();
+        const uint32_t release = peer_smem_addr(smem_addr(&tmem_empty_bar[0]), 0);
+        uint32_t lt = 0;
+        for (int t = pair; t < tiles_total; t += pairs, ++lt) {
+            int tile_a, tile_b;
+            tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
+            const uint32_t buf = lt & 1, use = lt >> 1;
+            if (!mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 23))
+                break;
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+            epilogue_token_rows<BN>(p, taddr, (tile_a * 2 + (int)rank) * TILE_A + quarter * 32, lane, tile_b,
+                                    stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
+            tcgen05_fence_before();
+            mbar_arrive_cluster(release + buf * 8);
+        }
+    }
+    tcgen05_fence_before();
+    cluster_sync();                                   // nobody signals a CTA that has left
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 // out = (residual +) sum over splits, in split order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, void* out,
                                      int out_type, long long out_stride, const float* residual,
@@ -1167,9 +1311,42 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
     return launch_status();
 }
 
+// Pairs of CTAs on tiles of 256 x 256 (gemm_tcgen05_pair_kernel).
+static bool pair_tiles = false;
+template <int STAGES>
+static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_m,
+                             int tiles_n, cudaStream_t stream)
+{
+    constexpr size_t smem = STAGES * PAIR_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 4 * EPILOGUE_STAGE_BYTES
+        + 2 * 128 * sizeof(float) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<STAGES>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    const int tiles = tiles_m * tiles_n;
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    launch_cluster_x(gemm_tcgen05_pair_kernel<STAGES>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma, mb,
+                     p, tiles_m, tiles);
+    return launch_status();
+}
+
 } // namespace chibi
 
 using namespace chibi;
+
+// Whether the product of many rows works in pairs of CTAs on tiles of 256 x 256 where the shape allows.
+CHIBI_API int chibi_gemm_set_pair_tiles(int enabled)
+{
+    pair_tiles = enabled != 0;
+    return CHIBI_OK;
+}
 
 // How many K splits chibi_gemm_bf16 would use (0: it does not take the shape),
 // so that a caller can size the scratch array: splits * M * N floats.
@@ -1609,6 +1786,11 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         p.ssq_out_parts = parts;
     }
     CUtensorMap ma, mb;
+    if (pair_tiles && N % 256 == 0) {
+        if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
+            return CHIBI_ERR_UNSUPPORTED;
+        return launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
+    }
     if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
         return CHIBI_ERR_UNSUPPORTED;
     if (bn == 128)

@@ -269,6 +269,80 @@ __device__ __forceinline__ void tmem_load_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------------------------ two CTAs on one tile
+// A pair of CTAs (ranks 2k and 2k + 1 of a cluster, on the two SMs of one TPC) shares one
+// tcgen05.mma of 256 rows: the even CTA issues it, each CTA holds its 128 rows of A, its half
+// of B's rows and its 128 rows of the accumulator.  What follows are the pair forms of the
+// instructions above.
+
+// The address of `own_smem_addr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t peer_smem_addr(uint32_t own_smem_addr, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_smem_addr), "r"(rank));
+    return remote;
+}
+
+// One arrival on an mbarrier of any CTA of the cluster (address from peer_smem_addr).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// The tile goes to this CTA's shared memory; its bytes are counted on an mbarrier that may
+// belong to the other CTA of the pair (address from peer_smem_addr).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_addr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// Executed by one warp of each CTA of the pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_in_smem, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_addr(dst_in_smem)),
+                 "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+                 : "memory");
+}
+
+// One arrival on the mbarrier at this offset in every CTA of `cta_mask` when all tcgen05.mma
+// that this thread issued so far have completed.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+                 "[%0], %1;" ::"r"(smem_addr(bar)),
+                 "h"(cta_mask)
+                 : "memory");
+}
+
+// D (256 rows over the pair's TMEM) (+)= A * B^T with both CTAs' shared memory as operands.
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
 // (64 bf16) laid out by TMA with the 128-byte swizzle: start address >> 4 in
 // bits [0,14); leading byte offset (unused with this swizzle, 1) in [16,30);
