@@ -903,14 +903,15 @@ __device__ __forceinline__ void collect_partial_tiles(const GemmParams& p, uint3
 // the column blocks go by; without bands, with 64 row blocks and K = 8,192, x (134 MB) was
 // fetched from memory again for every pair of column blocks.
 constexpr int TILE_BAND = 16;
+template <int BAND = TILE_BAND>
 __device__ __forceinline__ void tile_of(int t, int tiles_m, int tiles_total, int& tile_a, int& tile_b)
 {
     const int tiles_n = tiles_total / tiles_m;
-    const int per_band = TILE_BAND * tiles_n;
+    const int per_band = BAND * tiles_n;
     const int band = t / per_band, within = t - band * per_band;
-    const int rows = min(TILE_BAND, tiles_m - band * TILE_BAND);
+    const int rows = min(BAND, tiles_m - band * BAND);
     tile_b = within / rows;
-    tile_a = band * TILE_BAND + (within - tile_b * rows);
+    tile_a = band * BAND + (within - tile_b * rows);
 }
 
 // x is the A operand (many rows).  One CTA per SM walks over the output tiles (tile_of above).
@@ -1126,7 +1127,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             bool waited = false, ok = true;
             for (int t = pair; t < tiles_total && ok; t += pairs) {
                 int tile_a, tile_b;
-                tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
+                tile_of<TILE_BAND / 2>(t, tiles_m, tiles_total, tile_a, tile_b);   // bands of 2,048 rows here too
                 for (int kb = 0; kb < p.k_blocks_total; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -1188,7 +1189,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         uint32_t lt = 0;
         for (int t = pair; t < tiles_total; t += pairs, ++lt) {
             int tile_a, tile_b;
-            tile_of(t, tiles_m, tiles_total, tile_a, tile_b);
+            tile_of<TILE_BAND / 2>(t, tiles_m, tiles_total, tile_a, tile_b);   // bands of 2,048 rows here too
             const uint32_t buf = lt & 1, use = lt >> 1;
             if (!mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 23))
                 break;
@@ -1312,7 +1313,6 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
 }
 
 // Pairs of CTAs on tiles of 256 x 256 (gemm_tcgen05_pair_kernel).
-static bool pair_tiles = false;
 template <int STAGES>
 static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_m,
                              int tiles_n, cudaStream_t stream)
@@ -1341,12 +1341,6 @@ static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const
 
 using namespace chibi;
 
-// Whether the product of many rows works in pairs of CTAs on tiles of 256 x 256 where the shape allows.
-CHIBI_API int chibi_gemm_set_pair_tiles(int enabled)
-{
-    pair_tiles = enabled != 0;
-    return CHIBI_OK;
-}
 
 // How many K splits chibi_gemm_bf16 would use (0: it does not take the shape),
 // so that a caller can size the scratch array: splits * M * N floats.
@@ -1364,26 +1358,62 @@ static int sm_count()
     return count;
 }
 
-// Tile width of the kernel for many rows: 256 columns, or 128 where that fills the rounds of
-// one CTA per SM better.  Tiles of 128 columns are about a tenth less efficient each (the rows
-// of x are fetched for half as many columns), so they are taken where they fill the SMs at least
-// that much better: 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy) or 128 of
-// 128.  Where the tiles of 256 columns leave a last round that is shared out by K blocks
+// How the kernel for many rows cuts the output.  Tiles of 256 columns by one CTA each (128 rows);
+// the same by pairs of CTAs (256 rows a tile: a tenth to a seventh faster where the rounds are
+// filled alike, measured at 512 to 8,192 rows of the Qwen3-8B products; slower below 512 rows); or
+// tiles of 128 columns where those fill the rounds of one CTA per SM so much better that it makes
+// up for their lower efficiency (about a tenth below single tiles of 256, the rows of x being fetched
+// for half as many columns): 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy)
+// or 128 of 128.  Where single tiles of 256 columns leave a last round that is shared out by K blocks
 // (a quarter of the SMs or less), that is kept.
-static int many_rows_tile_width(int M, int N, int K)
+static bool pair_tiles = true, pair_force = false;
+static int pair_min_rows = 512;
+struct ManyRowsPlan {
+    int bn;        // 0: N is no multiple of 128
+    bool pairs;
+};
+static ManyRowsPlan many_rows_plan(int M, int N, int K)
 {
     if (N % 256 != 0)
-        return N % 128 == 0 ? 128 : 0;
+        return { N % 128 == 0 ? 128 : 0, false };
+    if (pair_force && M >= 2 * TILE_A)
+        return { 256, true };
     const int sms = sm_count();
     const long long t256 = (long long)((M + TILE_A - 1) / TILE_A) * (N / 256);
     const long long rest = t256 % sms;
     // (a lone round of so few tiles is shared out only where K is long: with 64 K blocks, whole
     // tiles of 128 columns are faster: o of Qwen3-8B at 160 / 192 / 256 rows 240 -> 372, 286 -> 445,
     // 375 -> 590 TFLOP/s; down, 192 K blocks, 373 -> 361, 435 -> 425, 564 -> 558)
-    if (rest > 0 && rest * 4 <= sms && (t256 > sms || (K + TILE_K - 1) / TILE_K >= 128))
-        return 256;
-    auto fill = [sms](long long tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
-    return fill(2 * t256) * 0.9 > fill(t256) ? 128 : 256;
+    const bool shared = rest > 0 && rest * 4 <= sms && (t256 > sms || (K + TILE_K - 1) / TILE_K >= 128);
+    auto fill = [](long long tiles, long long slots) {
+        return (double)tiles / (double)(((tiles + slots - 1) / slots) * slots);
+    };
+    // Worth of each way against single tiles of 256 columns in full rounds.  A shared-out last
+    // round fills the SMs but adds the partial sums up (0.88); pairs gain 1.12 (measured 1.07 to
+    // 1.15) on their own rounds of 74: 4,096 x 6,144 x 4,096 takes 152 us shared out and 137 in
+    // pairs (six rounds, the last a fifth full), 2,048 x 5,120 x 17,408 258 and 285 (three rounds,
+    // the last a sixth full).
+    const double single = shared ? 0.88 : fill(t256, sms), narrow = shared ? 0.0 : fill(2 * t256, sms) * 0.9;
+    double paired = 0.0;
+    if (pair_tiles && M >= pair_min_rows)
+        paired = fill((long long)((M + 2 * TILE_A - 1) / (2 * TILE_A)) * (N / 256), sms / 2) * 1.12;
+    if (paired >= single && paired >= narrow)
+        return { 256, true };
+    return { narrow > single ? 128 : 256, false };
+}
+
+static int many_rows_tile_width(int M, int N, int K) { return many_rows_plan(M, N, K).bn; }
+
+static bool many_rows_in_pairs(int M, int N, int K) { return many_rows_plan(M, N, K).pairs; }
+
+// Whether the product of many rows works in pairs of CTAs on tiles of 256 x 256 where the shape allows.
+CHIBI_API int chibi_gemm_set_pair_tiles(int enabled, int min_rows)
+{
+    pair_tiles = enabled != 0;
+    pair_force = enabled == 2;
+    if (min_rows > 0)
+        pair_min_rows = min_rows;
+    return CHIBI_OK;
 }
 
 // 33 to 64 rows and so few tiles that two or more splits fit the SMs once: one CTA per SM with
@@ -1538,7 +1568,11 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
         if (grid.y > 65535)
             return CHIBI_ERR_UNSUPPORTED;
-        if (bn == 256)
+        if (many_rows_in_pairs(M, N, K)) {
+            if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
+                return CHIBI_ERR_UNSUPPORTED;
+            status = launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
+        } else if (bn == 256)
             status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream, share_last_round);
         else if (bn == 128 && chosen == 128)
             status = launch_gemm_persistent<128, 6>(ma, mb, p, grid.x, grid.y, stream, false);
@@ -1645,6 +1679,11 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
     if (grid.y > 65535)
         return CHIBI_ERR_UNSUPPORTED;
+    if (many_rows_in_pairs(M, N, K)) {
+        if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
+            return CHIBI_ERR_UNSUPPORTED;
+        return launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
+    }
     if (bn == 256)
         return launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
     if (bn == 128 && chosen == 128)
@@ -1786,7 +1825,7 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         p.ssq_out_parts = parts;
     }
     CUtensorMap ma, mb;
-    if (pair_tiles && N % 256 == 0) {
+    if (many_rows_in_pairs(M, N, K)) {
         if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
             return CHIBI_ERR_UNSUPPORTED;
         return launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);

@@ -430,6 +430,55 @@ def test_linear_folds_the_norm_that_follows(k, ref, M, hidden, K, wide, wdtype):
     k.check_error_word()
 
 
+@pytest.mark.parametrize("M,hidden,K,wide", [(256, 256, 64, 512), (300, 512, 1000, 768), (513, 1024, 520, 2560),
+                                             (1000, 768, 4096, 512), (2048 + 17, 512, 264, 1024)])
+def test_products_by_pairs_of_ctas(k, ref, M, hidden, K, wide):
+    """Tiles of 256 x 256 by two CTAs (one tcgen05.mma of 256 rows for both) against the same
+    products by single CTAs: the sums are added in the same order, so every output is the same
+    bit for bit -- plain, onto the residual with the next norm's output, of rows with a factor,
+    with SwiGLU; rows that end inside a tile's first or second half, one tile and many."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=60)
+    w = rnd(hidden, K, dtype=torch.bfloat16, seed=61, scale=0.05)
+    res0 = rnd(M, hidden, seed=62, scale=3.0)
+    nw = (1 + 0.1 * rnd(hidden, seed=63)).to(torch.bfloat16)
+    w2 = rnd(wide, hidden, dtype=torch.bfloat16, seed=64, scale=0.05)
+    gu = k.interleave_gate_up(rnd(wide // 2, hidden, dtype=torch.bfloat16, seed=65, scale=0.05),
+                              rnd(wide // 2, hidden, dtype=torch.bfloat16, seed=66, scale=0.05))
+    results = {}
+    try:
+        for mode in ("never", "always"):
+            k.pairs_of_ctas(mode)
+            plain = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+            k.linear(x, w, plain)
+            res = res0.clone()
+            normed = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+            scaled = k.linear_residual_norm(x, w, res, nw, 1e-5, 0.0, normed)
+            assert scaled is not None, "the kernel refused shapes it is made for"
+            out = torch.full((M, wide), float("nan"), dtype=torch.bfloat16, device="cuda")
+            k.linear(scaled, w2, out)
+            act = torch.full((M, wide // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+            assert k.linear_swiglu(scaled, gu, act)
+            k.check_error_word()
+            ssq = scaled.ssq[:M * scaled.parts].view(M, scaled.parts).sum(1)
+            results[mode] = (plain, res, normed.clone(), ssq, out, act)
+    finally:
+        k.pairs_of_ctas("policy")
+    names = ("plain", "residual", "norm output", "sums of squares", "of rows with a factor", "SwiGLU")
+    for i, (what, a, b) in enumerate(zip(names, results["never"], results["always"])):
+        assert torch.isfinite(a.float()).all(), what
+        if i < 3:
+            assert torch.equal(a, b), f"{what}: pairs of CTAs differ from single CTAs"
+        else:
+            # single CTAs may have cut the columns into tiles of 128: the parts of a row's sum of
+            # squares are then added in another order, and a factor may differ in its last bit
+            close(a, b, torch.float32 if i == 3 else torch.bfloat16, what, rel=1e-5 if i == 3 else 8e-3)
+            if i > 3:
+                assert (a == b).float().mean() > 0.995, f"{what}: pairs of CTAs differ from single CTAs"
+    exp = torch.empty(M, hidden, dtype=torch.float32, device="cuda")
+    ref.linear(x, w, exp)
+    close(results["always"][0], exp, torch.bfloat16, "plain product by pairs", rel=8e-3)
+
+
 def test_linear_falls_back_when_unaligned(k, ref):
     x = rnd(5, 100, dtype=torch.bfloat16, seed=34)      # K = 100 is no multiple of 8
     w = rnd(40, 100, dtype=torch.bfloat16, seed=35)
@@ -668,11 +717,21 @@ def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
                                                         (4, 2, True, torch.bfloat16, False)])
 @pytest.mark.parametrize("seq_ctx,q_lens,scaled", [([70, 8, 300], [40, 1, 133], False),
                                                    ([257, 130, 64, 90], [257, 2, 64, 77], True)])
-def test_product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled):
+@pytest.mark.parametrize("pairs", ["policy", "always"])
+def test_product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled, pairs):
     """The q | k | v product of many rows whose epilogue normalises and rotates the
     heads and writes q and the cache entries (head size 128), against the plain
     product followed by the plain norm + rotation + append; with and without a row
-    factor left by the norm before (``ScaledRows``); rows that end inside a tile."""
+    factor left by the norm before (``ScaledRows``); rows that end inside a tile; by single
+    CTAs and (400 rows, widths of whole tiles of 256) by pairs of CTAs."""
+    k.pairs_of_ctas(pairs)
+    try:
+        _product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled)
+    finally:
+        k.pairs_of_ctas("policy")
+
+
+def _product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled):
     from chibillm_b200.kernels.ops import ScaledRows
     d, page, K = 128, 16, 520
     T = sum(q_lens)
