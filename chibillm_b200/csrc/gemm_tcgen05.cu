@@ -1073,15 +1073,20 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 // stage's bytes and the accumulators' release are the even CTA's; its commits arrive in both CTAs.
 // A wait that runs out ends the role's loop; every thread of both CTAs reaches the cluster
 // barrier at the end.
-constexpr int PAIR_BN = 256;
-constexpr int PAIR_STAGE_BYTES = 2 * TILE_A * TILE_K * 2;
-template <int STAGES>
+template <int BN>
+struct PairSmem {
+    static constexpr int A_BYTES = TILE_A * TILE_K * 2;
+    static constexpr int B_BYTES = (BN / 2) * TILE_K * 2;       // this CTA's half of the tile's rows of w
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+};
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const GemmParams p, int tiles_m, int tiles_total)
 {
     pdl_trigger();
-    constexpr int BN = PAIR_BN;
+    using S = PairSmem<BN>;
+    constexpr int PAIR_STAGE_BYTES = S::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * PAIR_STAGE_BYTES);
@@ -1139,8 +1144,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     if (rank == 0)
                         mbar_arrive_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);
                     const uint32_t bar = peer_smem_addr(smem_addr(&full_bar[s]), 0);
-                    tma_load_2d_pair(a_dst + TILE_A * TILE_K * 2, &map_b, bar, kb * TILE_K,
-                                     tile_b * BN + (int)rank * TILE_A);
+                    tma_load_2d_pair(a_dst + S::A_BYTES, &map_b, bar, kb * TILE_K,
+                                     tile_b * BN + (int)rank * (BN / 2));
                     if (!waited) {
                         pdl_wait();
                         waited = true;
@@ -1169,7 +1174,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_addr(smem + s * PAIR_STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + TILE_A * TILE_K * 2;
+                    const uint32_t b_addr = a_addr + S::A_BYTES;
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; ++k) {
                         const uint64_t a_desc = make_kmajor_sw128_desc(a_addr + k * UMMA_K * 2);
@@ -1185,7 +1190,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else {
         const int quarter = warp & 3;
         pdl_wait();
-        const uint32_t release = peer_smem_addr(smem_addr(&tmem_empty_bar[0]), 0);
         uint32_t lt = 0;
         for (int t = pair; t < tiles_total; t += pairs, ++lt) {
             int tile_a, tile_b;
@@ -1198,7 +1202,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             epilogue_token_rows<BN>(p, taddr, (tile_a * 2 + (int)rank) * TILE_A + quarter * 32, lane, tile_b,
                                     stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
             tcgen05_fence_before();
-            mbar_arrive_cluster(release + buf * 8);
+            mbar_arrive_cluster(peer_smem_addr(smem_addr(&tmem_empty_bar[buf]), 0));     // the even CTA's
         }
     }
     tcgen05_fence_before();
@@ -1312,16 +1316,17 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
     return launch_status();
 }
 
-// Pairs of CTAs on tiles of 256 x 256 (gemm_tcgen05_pair_kernel).
-template <int STAGES>
+// Pairs of CTAs on tiles of 256 rows x BN columns (gemm_tcgen05_pair_kernel); tiles_m counts blocks of 256 rows.
+template <int BN, int STAGES>
 static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_m,
                              int tiles_n, cudaStream_t stream)
 {
-    constexpr size_t smem = STAGES * PAIR_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 4 * EPILOGUE_STAGE_BYTES
+    constexpr size_t smem = STAGES * PairSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 4 * EPILOGUE_STAGE_BYTES
         + 2 * 128 * sizeof(float) + 1024;
+    static_assert(smem <= 227 * 1024, "the stages must fit the shared memory of an SM");
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<STAGES>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN, STAGES>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess)
             return (int)e;
@@ -1332,9 +1337,22 @@ static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const
     if (cudaGetDevice(&device) == cudaSuccess)
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    launch_cluster_x(gemm_tcgen05_pair_kernel<STAGES>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma, mb,
-                     p, tiles_m, tiles);
+    launch_cluster_x(gemm_tcgen05_pair_kernel<BN, STAGES>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma,
+                     mb, p, tiles_m, tiles);
     return launch_status();
+}
+
+// x [M, K], w [N, K] -> the tensor maps of the pair kernel and its launch.
+static int launch_pairs(const void* x, const void* w, const GemmParams& p, int M, int N, int K, long long x_stride,
+                        long long w_stride, int bn, cudaStream_t stream)
+{
+    CUtensorMap ma, mb;
+    if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn / 2, &mb))
+        return CHIBI_ERR_UNSUPPORTED;
+    const int tiles_m = (M + 2 * TILE_A - 1) / (2 * TILE_A);
+    if (bn == 128)
+        return launch_gemm_pairs<128, 8>(ma, mb, p, tiles_m, N / 128, stream);
+    return launch_gemm_pairs<256, 6>(ma, mb, p, tiles_m, N / 256, stream);
 }
 
 } // namespace chibi
@@ -1360,13 +1378,16 @@ static int sm_count()
 
 // How the kernel for many rows cuts the output.  Tiles of 256 columns by one CTA each (128 rows);
 // the same by pairs of CTAs (256 rows a tile: a tenth to a seventh faster where the rounds are
-// filled alike, measured at 512 to 8,192 rows of the Qwen3-8B products; slower below 512 rows); or
+// filled alike, measured at 512 to 8,192 rows of the Qwen3-8B products; slower below 512 rows, where
+// only their tiles of 128 columns are used, from 256 rows on); or
 // tiles of 128 columns where those fill the rounds of one CTA per SM so much better that it makes
 // up for their lower efficiency (about a tenth below single tiles of 256, the rows of x being fetched
 // for half as many columns): 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy)
-// or 128 of 128.  Where single tiles of 256 columns leave a last round that is shared out by K blocks
-// (a quarter of the SMs or less), that is kept.
-static bool pair_tiles = true, pair_force = false;
+// or 128 of 128; or those by pairs of CTAs (256 rows x 128 columns).  Where single tiles of 256 columns
+// leave a last round that is shared out by K blocks (a quarter of the SMs or less), that competes
+// with the cost of adding its partial sums up.
+static bool pair_tiles = true;
+static int pair_force = 0;        // 128 or 256: that tile width in pairs wherever the shape allows
 static int pair_min_rows = 512;
 struct ManyRowsPlan {
     int bn;        // 0: N is no multiple of 128
@@ -1377,7 +1398,7 @@ static ManyRowsPlan many_rows_plan(int M, int N, int K)
     if (N % 256 != 0)
         return { N % 128 == 0 ? 128 : 0, false };
     if (pair_force && M >= 2 * TILE_A)
-        return { 256, true };
+        return { pair_force, true };
     const int sms = sm_count();
     const long long t256 = (long long)((M + TILE_A - 1) / TILE_A) * (N / 256);
     const long long rest = t256 % sms;
@@ -1388,17 +1409,27 @@ static ManyRowsPlan many_rows_plan(int M, int N, int K)
     auto fill = [](long long tiles, long long slots) {
         return (double)tiles / (double)(((tiles + slots - 1) / slots) * slots);
     };
-    // Worth of each way against single tiles of 256 columns in full rounds.  A shared-out last
-    // round fills the SMs but adds the partial sums up (0.88); pairs gain 1.12 (measured 1.07 to
-    // 1.15) on their own rounds of 74: 4,096 x 6,144 x 4,096 takes 152 us shared out and 137 in
-    // pairs (six rounds, the last a fifth full), 2,048 x 5,120 x 17,408 258 and 285 (three rounds,
-    // the last a sixth full).
-    const double single = shared ? 0.88 : fill(t256, sms), narrow = shared ? 0.0 : fill(2 * t256, sms) * 0.9;
-    double paired = 0.0;
-    if (pair_tiles && M >= pair_min_rows)
-        paired = fill((long long)((M + 2 * TILE_A - 1) / (2 * TILE_A)) * (N / 256), sms / 2) * 1.12;
-    if (paired >= single && paired >= narrow)
+    // Worth of each way against single tiles of 256 columns in full rounds (time = tiles / SMs / worth).
+    // A shared-out last round fills the SMs but adds the partial sums up: about 25 us, which is
+    // 62 K blocks of a tile (0.4 us each).  Pairs gain 1.12 (measured 1.07 to 1.15) on their own
+    // rounds of 74; pairs on tiles of 128 columns work like single CTAs on 256.  Measured: 4,096 x
+    // 6,144 x 4,096 takes 152 us shared out and 137 in pairs (six rounds, the last a fifth full);
+    // 2,048 x 5,120 with K = 17,408 258 shared out and 285 in pairs (three rounds, the last a
+    // sixth full), with K = 5,120 94 and 88.
+    const double k_blocks = (double)((K + TILE_K - 1) / TILE_K);
+    const double single = shared ? 1.0 / (1.0 + 62.5 * sms / (k_blocks * (double)t256)) : fill(t256, sms);
+    const double narrow = fill(2 * t256, sms) * 0.9;
+    double paired = 0.0, paired_narrow = 0.0;
+    if (pair_tiles && M >= 2 * TILE_A) {
+        const long long row_blocks = (M + 2 * TILE_A - 1) / (2 * TILE_A);
+        if (M >= pair_min_rows)
+            paired = fill(row_blocks * (N / 256), sms / 2) * 1.12;
+        paired_narrow = fill(row_blocks * (N / 128), sms / 2);
+    }
+    if (paired >= single && paired >= narrow && paired >= paired_narrow)
         return { 256, true };
+    if (paired_narrow > single && paired_narrow > narrow)
+        return { 128, true };
     return { narrow > single ? 128 : 256, false };
 }
 
@@ -1406,11 +1437,18 @@ static int many_rows_tile_width(int M, int N, int K) { return many_rows_plan(M, 
 
 static bool many_rows_in_pairs(int M, int N, int K) { return many_rows_plan(M, N, K).pairs; }
 
+// The cut of a product of many rows: the tile's columns (0: not taken), + 1 if pairs of CTAs compute it.
+CHIBI_API int chibi_gemm_many_rows_plan(int M, int N, int K)
+{
+    const ManyRowsPlan plan = many_rows_plan(M, N, K);
+    return plan.bn + (plan.pairs ? 1 : 0);
+}
+
 // Whether the product of many rows works in pairs of CTAs on tiles of 256 x 256 where the shape allows.
 CHIBI_API int chibi_gemm_set_pair_tiles(int enabled, int min_rows)
 {
     pair_tiles = enabled != 0;
-    pair_force = enabled == 2;
+    pair_force = enabled == 2 ? 256 : (enabled == 3 ? 128 : 0);
     if (min_rows > 0)
         pair_min_rows = min_rows;
     return CHIBI_OK;
@@ -1569,9 +1607,7 @@ static int gemm_bf16_impl(const void* x, const void* w, void* out, int out_type,
         if (grid.y > 65535)
             return CHIBI_ERR_UNSUPPORTED;
         if (many_rows_in_pairs(M, N, K)) {
-            if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
-                return CHIBI_ERR_UNSUPPORTED;
-            status = launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
+            status = launch_pairs(x, w, p, M, N, K, x_stride, w_stride, bn, stream);
         } else if (bn == 256)
             status = launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream, share_last_round);
         else if (bn == 128 && chosen == 128)
@@ -1679,11 +1715,8 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     const dim3 grid((M + TILE_A - 1) / TILE_A, (N + bn - 1) / bn, 1);
     if (grid.y > 65535)
         return CHIBI_ERR_UNSUPPORTED;
-    if (many_rows_in_pairs(M, N, K)) {
-        if (!tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
-            return CHIBI_ERR_UNSUPPORTED;
-        return launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
-    }
+    if (many_rows_in_pairs(M, N, K))
+        return launch_pairs(x, w, p, M, N, K, x_stride, w_stride, bn, stream);
     if (bn == 256)
         return launch_gemm_persistent<256, 4>(ma, mb, p, grid.x, grid.y, stream);
     if (bn == 128 && chosen == 128)
@@ -1825,11 +1858,8 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         p.ssq_out_parts = parts;
     }
     CUtensorMap ma, mb;
-    if (many_rows_in_pairs(M, N, K)) {
-        if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, TILE_A, &mb))
-            return CHIBI_ERR_UNSUPPORTED;
-        return launch_gemm_pairs<6>(ma, mb, p, (M + 2 * TILE_A - 1) / (2 * TILE_A), N / 256, stream);
-    }
+    if (many_rows_in_pairs(M, N, K))
+        return launch_pairs(x, w, p, M, N, K, x_stride, w_stride, bn, stream);
     if (!tensor_map_2d(x, M, K, x_stride, TILE_A, &ma) || !tensor_map_2d(w, N, K, w_stride, bn, &mb))
         return CHIBI_ERR_UNSUPPORTED;
     if (bn == 128)

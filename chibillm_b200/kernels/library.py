@@ -31,6 +31,7 @@ _SIGNATURES = {
         "chibi_gemm_bf16": [P, P, P, I, P, I, I, I, L, L, L, L, P, L, P, P],
         "chibi_gemm_set_stream_scratch": [P, L],
         "chibi_gemm_set_pair_tiles": [I, I],
+        "chibi_gemm_many_rows_plan": [I, I, I],
         "chibi_gemm_reset_stream_counters": [P],
         "chibi_gemm_bf16_norm_parts": [I, I, I],
         "chibi_gemm_few_rows_max": [],

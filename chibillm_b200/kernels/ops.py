@@ -235,7 +235,7 @@ class CudaKernels:
         rows issued by one CTA for both): "policy" where that is the fastest cut of the output
         (the default, from ``min_rows`` rows on), "never", or "always" (from 256 rows on, whenever
         the columns come in whole tiles of 256)."""
-        _check(self.lib.chibi_gemm_set_pair_tiles({"never": 0, "policy": 1, "always": 2}[mode], int(min_rows)),
+        _check(self.lib.chibi_gemm_set_pair_tiles({"never": 0, "policy": 1, "always": 2, "always narrow": 3}[mode], int(min_rows)),
                "pairs of CTAs")
 
     def scale_rows(self, rows: ScaledRows) -> None:

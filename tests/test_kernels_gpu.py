@@ -433,7 +433,7 @@ def test_linear_folds_the_norm_that_follows(k, ref, M, hidden, K, wide, wdtype):
 @pytest.mark.parametrize("M,hidden,K,wide", [(256, 256, 64, 512), (300, 512, 1000, 768), (513, 1024, 520, 2560),
                                              (1000, 768, 4096, 512), (2048 + 17, 512, 264, 1024)])
 def test_products_by_pairs_of_ctas(k, ref, M, hidden, K, wide):
-    """Tiles of 256 x 256 by two CTAs (one tcgen05.mma of 256 rows for both) against the same
+    """Tiles of 256 x 256 and 256 x 128 by two CTAs (one tcgen05.mma of 256 rows for both) against the same
     products by single CTAs: the sums are added in the same order, so every output is the same
     bit for bit -- plain, onto the residual with the next norm's output, of rows with a factor,
     with SwiGLU; rows that end inside a tile's first or second half, one tile and many."""
@@ -446,7 +446,7 @@ def test_products_by_pairs_of_ctas(k, ref, M, hidden, K, wide):
                               rnd(wide // 2, hidden, dtype=torch.bfloat16, seed=66, scale=0.05))
     results = {}
     try:
-        for mode in ("never", "always"):
+        for mode in ("never", "always", "always narrow"):
             k.pairs_of_ctas(mode)
             plain = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
             k.linear(x, w, plain)
@@ -464,16 +464,17 @@ def test_products_by_pairs_of_ctas(k, ref, M, hidden, K, wide):
     finally:
         k.pairs_of_ctas("policy")
     names = ("plain", "residual", "norm output", "sums of squares", "of rows with a factor", "SwiGLU")
-    for i, (what, a, b) in enumerate(zip(names, results["never"], results["always"])):
-        assert torch.isfinite(a.float()).all(), what
-        if i < 3:
-            assert torch.equal(a, b), f"{what}: pairs of CTAs differ from single CTAs"
-        else:
-            # single CTAs may have cut the columns into tiles of 128: the parts of a row's sum of
-            # squares are then added in another order, and a factor may differ in its last bit
-            close(a, b, torch.float32 if i == 3 else torch.bfloat16, what, rel=1e-5 if i == 3 else 8e-3)
-            if i > 3:
-                assert (a == b).float().mean() > 0.995, f"{what}: pairs of CTAs differ from single CTAs"
+    for mode in ("always", "always narrow"):
+        for i, (what, a, b) in enumerate(zip(names, results["never"], results[mode])):
+            assert torch.isfinite(a.float()).all(), what
+            if i < 3:
+                assert torch.equal(a, b), f"{what}: pairs of CTAs ({mode}) differ from single CTAs"
+            else:
+                # tiles of 128 or of 256 columns: the parts of a row's sum of squares are then added
+                # in another order, and a factor may differ in its last bit
+                close(a, b, torch.float32 if i == 3 else torch.bfloat16, what, rel=1e-5 if i == 3 else 8e-3)
+                if i > 3:
+                    assert (a == b).float().mean() > 0.995, f"{what}: pairs of CTAs ({mode}) differ from single CTAs"
     exp = torch.empty(M, hidden, dtype=torch.float32, device="cuda")
     ref.linear(x, w, exp)
     close(results["always"][0], exp, torch.bfloat16, "plain product by pairs", rel=8e-3)
@@ -717,7 +718,7 @@ def test_decode_attention_from_partial_sums(k, ref, nq, nkv, window, append):
                                                         (4, 2, True, torch.bfloat16, False)])
 @pytest.mark.parametrize("seq_ctx,q_lens,scaled", [([70, 8, 300], [40, 1, 133], False),
                                                    ([257, 130, 64, 90], [257, 2, 64, 77], True)])
-@pytest.mark.parametrize("pairs", ["policy", "always"])
+@pytest.mark.parametrize("pairs", ["policy", "always", "always narrow"])
 def test_product_that_finishes_its_heads(k, ref, nq, nkv, norms, wdtype, append, seq_ctx, q_lens, scaled, pairs):
     """The q | k | v product of many rows whose epilogue normalises and rotates the
     heads and writes q and the cache entries (head size 128), against the plain
