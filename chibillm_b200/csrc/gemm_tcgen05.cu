@@ -1066,10 +1066,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 }
 
 // The same walk over output tiles by pairs of CTAs (a cluster of two, on the SMs of one TPC): a
-// tile is 256 rows x 256 columns, computed by tcgen05.mma of 256 rows that the even CTA issues for
-// both.  Each CTA fetches its 128 rows of x and its 128 of the tile's 256 rows of w (32 KB per K
-// block for as many sums as a CTA on its own gets from 48 KB), holds its 128 rows of the
-// accumulator in its own TMEM and runs the epilogue of those rows.  The barriers that count a
+// tile is 256 rows x BN columns (256 or 128), computed by tcgen05.mma of 256 rows that the even CTA
+// issues for both.  Each CTA fetches its 128 rows of x and its half of the tile's BN rows of w (with
+// BN = 256: 32 KB per K block for as many sums as a CTA on its own gets from 48 KB), holds its 128
+// rows of the accumulator in its own TMEM and runs the epilogue of those rows.  The barriers that count a
 // stage's bytes and the accumulators' release are the even CTA's; its commits arrive in both CTAs.
 // A wait that runs out ends the role's loop; every thread of both CTAs reaches the cluster
 // barrier at the end.
