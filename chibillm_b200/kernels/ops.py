@@ -779,16 +779,18 @@ class CudaKernels:
         # More CTAs than slots even with one range each: a last round with a few CTAs in it
         # costs as much as a full one (38 sequences x 8 kv heads = 304 CTAs on 296 slots: 21 %
         # of a step more than 36 sequences).  With s ranges there are ceil(ctas * s / slots)
-        # rounds of 1 / s of the keys each, and every CTA pays for its prologue and for its
-        # share of the merge what about 550 keys take (fitted to steps of 12 layers at 38 to 64
-        # sequences of 2,048 and 8,192 keys): the s that makes rounds * (1 / s + 550 / keys) least.
-        prologue = min(1.0, 550.0 / max(max_ctx_len, 1))
-        best, least = 1, None
-        for s in range(1, 9):
-            if s > 1 and max_ctx_len // s < 256:
+        # rounds of 1 / s of the keys each, and every CTA pays for its start and for its share
+        # of the merge what 0.03 of the keys + 200 keys take (fitted to steps of 12 layers at 38
+        # to 128 sequences of 2,048 keys and of 6 layers at 40 to 96 sequences of 8,192, the query
+        # rows ready in memory): the s that makes rounds * (1 / s + that) least, more ranges only
+        # where they gain a twentieth, at most four, of 512 keys or more.
+        start = 0.03 + 200.0 / max(max_ctx_len, 1)
+        best, least = 1, -(-ctas // slots) * (1.0 + start)
+        for s in range(2, 5):
+            if max_ctx_len // s < 512:
                 break
-            cost = -(-ctas * s // slots) * (1.0 / s + prologue)
-            if least is None or cost < least - 1e-9:
+            cost = -(-ctas * s // slots) * (1.0 / s + start)
+            if cost < 0.95 * least:
                 best, least = s, cost
         return best
 
@@ -864,6 +866,14 @@ class CudaKernels:
         runs ``qk_norm_rope_append_partial`` and ``attention``)."""
         if not (self.use_tensor_cores and d == 128 and rotary_dim == d and nq // nkv <= 6
                 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16):
+            return False
+        # More CTAs than are resident at once (from 38 sequences of 8 kv heads on): the sequences are
+        # then cut into key ranges so that the rounds come out even, and every range's CTA would add
+        # up, normalise and rotate the same query rows again; one kernel that leaves them in memory
+        # and the attention kernel after it are 1 to 6 % of a step faster (12 layers, 2,048 keys,
+        # 38 / 48 / 64 / 96 / 128 sequences: 2.39 / 2.50 / 2.68 / 3.47 / 4.17 -> 2.29 / 2.39 /
+        # 2.65 / 3.40 / 4.09 ms).
+        if ctx_len.numel() * nkv * ((nq // nkv + 15) // 16) > 2 * self.sm_count:
             return False
         for w in (q_norm_w, k_norm_w):
             if w is not None and w.dtype != torch.bfloat16:
