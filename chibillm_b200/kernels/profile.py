@@ -25,7 +25,8 @@ import torch
 
 # entry points that ask a question or set something and launch nothing
 _NOT_LAUNCHES = ("chibi_gemm_bf16_splits", "chibi_gemm_bf16_splits_capped", "chibi_gemm_bf16_norm_parts", "chibi_gemm_few_rows_max",
-                 "chibi_gemm_set_stream_scratch", "chibi_gemm_reset_stream_counters",
+                 "chibi_gemm_set_stream_scratch", "chibi_gemm_reset_stream_counters", "chibi_gemm_set_pair_tiles",
+                 "chibi_gemm_many_rows_plan",
                  "chibi_attention_mma_head_dim", "chibi_attention_tc_head_dim")
 
 # where M, N, K stand among the arguments of the matrix products
