@@ -224,6 +224,23 @@ def attention_tc_library(head_dim: int, verbose: bool = True) -> str:
     return ensure_library("chibi_attention_tc", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
 
 
+def prepare(head_dims: Sequence[int] = (), bfloat16: bool = True, verbose: bool = True) -> None:
+    """Builds side by side what a model with these head sizes will load and is not there yet: the
+    kernel library, the host runtime and, for bfloat16, the attention libraries of each head size
+    that the tensor-core kernels take.  Loading them one after the other, each built when first
+    asked for, took 17 s from a fresh checkout; together they take as long as the slowest."""
+    jobs = [lambda: runtime_library(verbose), lambda: ensure_library("chibi_kernels", verbose=verbose)]
+    if bfloat16:
+        for d in sorted(set(int(d) for d in head_dims)):
+            if d % 16 == 0 and 0 < d <= 256:
+                jobs.append(lambda d=d: attention_library(d, verbose))
+            if d in TCGEN05_ATTENTION_HEAD_DIMS:
+                jobs.append(lambda d=d: attention_tc_library(d, verbose))
+    with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+        for done in [pool.submit(job) for job in jobs]:
+            done.result()
+
+
 def build_all(verbose: bool = True) -> List[str]:
     out = [runtime_library(verbose), reference_library(verbose), ensure_library("chibi_kernels", verbose=verbose)]
     with ThreadPoolExecutor(max_workers=4) as pool:

@@ -41,12 +41,17 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype '{name}' is not supported (bfloat16 or float32)") from None
 
 
-def make_runtime(dtype, device="cuda:0", kernels=None) -> Runtime:
+def make_runtime(dtype, device="cuda:0", kernels=None, spec=None) -> Runtime:
     """The product's runtime: a CUDA device and this package's kernels.  A test
-    may pass a stand-in for the kernels (then any device is allowed)."""
+    may pass a stand-in for the kernels (then any device is allowed).  With the
+    model's ``spec`` the libraries it will load are built together first."""
     device = torch.device(device)
     if kernels is None:
         from ..kernels.ops import CudaKernels
+        if spec is not None:
+            from ..csrc import build
+            head_dims = {getattr(layer.mixer, "head_dim", 0) for layer in spec.layers}
+            build.prepare(head_dims, bfloat16=parse_dtype(dtype) == torch.bfloat16)
         kernels = CudaKernels(device)
     return Runtime(device=device, dtype=parse_dtype(dtype), kernels=kernels)
 
@@ -93,7 +98,7 @@ class ModelRunner:
     def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0", page_size: int = 16,
                     pool_tokens: int = 4096, max_requests: int = 4, kernels=None) -> "ModelRunner":
         _, _, spec = load_config(model_dir)
-        runtime = make_runtime(dtype, device, kernels)
+        runtime = make_runtime(dtype, device, kernels, spec)
         model = DecoderModel(spec, runtime)
         load_weights(model, model_dir, runtime)
         return cls(model, runtime, page_size, pool_tokens, max_requests)
@@ -112,7 +117,7 @@ class ModelRunner:
             config_object = dict(config_object, num_hidden_layers=num_layers)
         arch = find_architecture(config_object)
         spec = arch.model_spec(arch.read_config(config_object))
-        runtime = make_runtime(dtype, device, kernels)
+        runtime = make_runtime(dtype, device, kernels, spec)
         model = DecoderModel(spec, runtime)
         bind_random_weights(model, seed, runtime)
         return cls(model, runtime, page_size, pool_tokens, max_requests)
