@@ -1136,7 +1136,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 for (int kb = 0; kb < p.k_blocks_total; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
-                    if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 21)) {
+                    if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error, 17)) {
                         ok = false;
                         break;
                     }
@@ -1161,14 +1161,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             bool ok = true;
             for (int t = pair; t < tiles_total && ok; t += pairs, ++lt) {
                 const uint32_t buf = lt & 1, use = lt >> 1;
-                if (use > 0 && !mbar_wait(&tmem_empty_bar[buf], (use - 1) & 1, p.error, 24))
+                if (use > 0 && !mbar_wait(&tmem_empty_bar[buf], (use - 1) & 1, p.error, 20))
                     break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < p.k_blocks_total; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
-                    if (!mbar_wait(&full_bar[s], round & 1, p.error, 22)) {
+                    if (!mbar_wait(&full_bar[s], round & 1, p.error, 18)) {
                         ok = false;
                         break;
                     }
@@ -1195,7 +1195,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             int tile_a, tile_b;
             tile_of<TILE_BAND / 2>(t, tiles_m, tiles_total, tile_a, tile_b);   // bands of 2,048 rows here too
             const uint32_t buf = lt & 1, use = lt >> 1;
-            if (!mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 23))
+            if (!mbar_wait(&tmem_full_bar[buf], use & 1, p.error, 19))
                 break;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);

@@ -441,6 +441,10 @@ class CudaKernels:
                     14: "a wait that ran out (matrix product: accumulator hand-over)",
                     15: "a wait that ran out (matrix product: partial sums of a shared tile)",
                     16: "a wait that ran out (matrix product: slot of a shared tile)",
+                    17: "a wait that ran out (matrix product by pairs of CTAs: loader)",
+                    18: "a wait that ran out (matrix product by pairs of CTAs: tensor-core issuer)",
+                    19: "a wait that ran out (matrix product by pairs of CTAs: epilogue)",
+                    20: "a wait that ran out (matrix product by pairs of CTAs: accumulator hand-over)",
                     **{c: f"a wait that ran out (tcgen05 attention, point {c})" for c in range(21, 30)}}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
