@@ -1333,10 +1333,31 @@ static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const
         configured = true;
     }
     const int tiles = tiles_m * tiles_n;
-    int device = 0, sms = 148;
-    if (cudaGetDevice(&device) == cudaSuccess)
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    // as many pairs as are resident at once (74 on 148 SMs: every TPC one), asked of the driver once
+    static int resident_pairs = 0;
+    if (resident_pairs == 0) {
+        int device = 0, sms = 148, clusters = 0;
+        if (cudaGetDevice(&device) == cudaSuccess)
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (sms / 2));
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<BN, STAGES>, &cfg) != cudaSuccess
+            || clusters < 1) {
+            cudaGetLastError();
+            clusters = sms / 2;
+        }
+        resident_pairs = clusters < sms / 2 ? clusters : sms / 2;
+    }
+    const int pairs = tiles < resident_pairs ? tiles : resident_pairs;
     launch_cluster_x(gemm_tcgen05_pair_kernel<BN, STAGES>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma,
                      mb, p, tiles_m, tiles);
     return launch_status();
