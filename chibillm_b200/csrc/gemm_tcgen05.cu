@@ -1465,7 +1465,10 @@ CHIBI_API int chibi_gemm_many_rows_plan(int M, int N, int K)
     return plan.bn + (plan.pairs ? 1 : 0);
 }
 
-// Whether the product of many rows works in pairs of CTAs on tiles of 256 x 256 where the shape allows.
+// How the product of many rows uses pairs of CTAs: 0 never, 1 where the plan above prefers them
+// (the default; tiles of 256 x 256 from `min_rows` rows on, 512 unless given), 2 / 3 tiles of
+// 256 x 256 / 256 x 128 wherever the columns come in whole tiles and there are 256 rows or more
+// (for tests and measurements).
 CHIBI_API int chibi_gemm_set_pair_tiles(int enabled, int min_rows)
 {
     pair_tiles = enabled != 0;
