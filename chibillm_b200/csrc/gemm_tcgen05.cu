@@ -1399,8 +1399,8 @@ static int sm_count()
 
 // How the kernel for many rows cuts the output.  Tiles of 256 columns by one CTA each (128 rows);
 // the same by pairs of CTAs (256 rows a tile: a tenth to a seventh faster where the rounds are
-// filled alike, measured at 512 to 8,192 rows of the Qwen3-8B products; slower below 512 rows, where
-// only their tiles of 128 columns are used, from 256 rows on); or
+// filled alike, measured at 448 to 8,192 rows of the Qwen3-8B products; from 256 rows on, with
+// what their last block of 256 rows leaves empty counted against them); or
 // tiles of 128 columns where those fill the rounds of one CTA per SM so much better that it makes
 // up for their lower efficiency (about a tenth below single tiles of 256, the rows of x being fetched
 // for half as many columns): 512 rows x 4,096 columns are 64 tiles of 256 (64 of 148 SMs busy)
@@ -1409,7 +1409,7 @@ static int sm_count()
 // with the cost of adding its partial sums up.
 static bool pair_tiles = true;
 static int pair_force = 0;        // 128 or 256: that tile width in pairs wherever the shape allows
-static int pair_min_rows = 512;
+static int pair_min_rows = 256;
 struct ManyRowsPlan {
     int bn;        // 0: N is no multiple of 128
     bool pairs;
@@ -1443,9 +1443,13 @@ static ManyRowsPlan many_rows_plan(int M, int N, int K)
     double paired = 0.0, paired_narrow = 0.0;
     if (pair_tiles && M >= 2 * TILE_A) {
         const long long row_blocks = (M + 2 * TILE_A - 1) / (2 * TILE_A);
+        // rows past the end in a pair's last block of 256 against those in a single CTA's last 128:
+        // 384 rows are three full blocks of 128 or two of 256 a quarter empty (gate|up 73.8 us by
+        // single CTAs, 80.0 by pairs), 448 rows fill both alike (92.2 and 79.9)
+        const double rows_used = (double)(((M + TILE_A - 1) / TILE_A) * TILE_A) / (double)(row_blocks * 2 * TILE_A);
         if (M >= pair_min_rows)
-            paired = fill(row_blocks * (N / 256), sms / 2) * 1.12;
-        paired_narrow = fill(row_blocks * (N / 128), sms / 2);
+            paired = fill(row_blocks * (N / 256), sms / 2) * 1.12 * rows_used;
+        paired_narrow = fill(row_blocks * (N / 128), sms / 2) * rows_used;
     }
     if (paired >= single && paired >= narrow && paired >= paired_narrow)
         return { 256, true };
@@ -1466,7 +1470,7 @@ CHIBI_API int chibi_gemm_many_rows_plan(int M, int N, int K)
 }
 
 // How the product of many rows uses pairs of CTAs: 0 never, 1 where the plan above prefers them
-// (the default; tiles of 256 x 256 from `min_rows` rows on, 512 unless given), 2 / 3 tiles of
+// (the default; tiles of 256 x 256 from `min_rows` rows on, 256 unless given), 2 / 3 tiles of
 // 256 x 256 / 256 x 128 wherever the columns come in whole tiles and there are 256 rows or more
 // (for tests and measurements).
 CHIBI_API int chibi_gemm_set_pair_tiles(int enabled, int min_rows)

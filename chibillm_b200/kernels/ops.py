@@ -230,7 +230,7 @@ class CudaKernels:
         _check(self.lib.chibi_gemm_set_stream_scratch(_ptr(scratch), scratch.numel() if enabled else 0),
                "stream scratch")
 
-    def pairs_of_ctas(self, mode: str = "policy", min_rows: int = 512) -> None:
+    def pairs_of_ctas(self, mode: str = "policy", min_rows: int = 256) -> None:
         """How the many-row product uses pairs of CTAs on tiles of 256 x 256 (tcgen05.mma of 256
         rows issued by one CTA for both): "policy" where that is the fastest cut of the output
         (the default, from ``min_rows`` rows on), "never", or "always" (from 256 rows on, whenever

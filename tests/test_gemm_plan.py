@@ -19,7 +19,7 @@ def plan():
     lib.chibi_gemm_many_rows_plan.restype = ctypes.c_int
     lib.chibi_gemm_many_rows_plan.argtypes = [ctypes.c_int] * 3
     lib.chibi_gemm_set_pair_tiles.argtypes = [ctypes.c_int] * 2
-    lib.chibi_gemm_set_pair_tiles(1, 512)
+    lib.chibi_gemm_set_pair_tiles(1, 256)
     return lambda m, n, k: lib.chibi_gemm_many_rows_plan(m, n, k)
 
 
@@ -34,8 +34,8 @@ SINGLE_256, SINGLE_128, PAIRS_256, PAIRS_128 = 256, 128, 257, 129
     (1024, 6144, 4096, PAIRS_128),
     # 512 rows of o: 64 tiles of 256 columns, or 128 of 128 by pairs
     (512, 4096, 4096, PAIRS_128),
-    # below 512 rows no tiles of 256 x 256 by pairs
-    (384, 24576, 4096, SINGLE_256),
+    # 384 rows: two blocks of 256 would be a quarter empty, three of 128 are full; 448 rows fill both alike
+    (384, 24576, 4096, SINGLE_256), (448, 24576, 4096, PAIRS_256),
     # Qwen3-14B down at 2,048 rows: a last round of 24 tiles, K long: shared out by single CTAs
     (2048, 5120, 17408, SINGLE_256),
     # the same tiles with K short: adding the shared-out round up would cost more than pairs lose
